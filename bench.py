@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""Benchmark of the scan hot path: forward + backward over one batch of synthetic input.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--algo auto]
+    python bench.py --impl reference ...      # the reference's CPU loop on the host cores
+
+One JSON line on stdout (rank 0).  A *step* is one forward scan plus one backward scan of the
+workload; ``value`` is elements (batch*seq*d_model, summed over ranks) per second with all
+tensors resident in HBM, ``e2e`` the same through ``scan_cu`` + ``.backward`` from pinned host
+buffers with the copies inside the timed region.  With N > 1 every rank owns a full-size channel
+shard of a d_model*N problem (weak scaling, no collective on the data path).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "scan fwd+bwd elems/s"
+UNIT = "elems/s"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=200)
+    p.add_argument("--warmup", type=int, default=20)
+    p.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    p.add_argument("--workload", default="c2")
+    p.add_argument("--algo", default="auto", choices=["auto", "chunked", "lookback"])
+    p.add_argument("--mode", default="shard", choices=["shard", "seqpar"])
+    p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-cpu", action="store_true")
+    p.add_argument("--cpu-seconds", type=float, default=12.0)
+    return p.parse_args()
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ CPU legs
+def cpu_reference_leg(w, seconds: float, threads: int):
+    """The reference's own C++ loop (oracle/_ref) on the host cores, else the C restatement.
+    Returns (elems_per_s, kind, cores, sample_text)."""
+    import numpy as np
+    import torch
+    from oracle import oracle
+    from fast_sequential_scan_b200.workloads import make_inputs
+
+    a, b, g = (x.float().numpy() for x in make_inputs(w, "cpu", 0))
+    job = None
+    if oracle.RefLib.available():
+        job = oracle.RefLib().job(w.batch, w.seq, w.d_model)
+    reps, t_total = 0, 0.0
+    if job is not None:
+        threads = max(1, min(threads, w.batch))
+        job.set(job.ALPHA, a); job.set(job.BETA, b); job.set(job.G, g)
+        job.forward(threads); job.backward(threads)          # warm-up
+        while t_total < seconds and reps < 50:
+            t0 = time.perf_counter()
+            job.forward(threads); job.backward(threads)
+            t_total += time.perf_counter() - t0
+            reps += 1
+        job.close()
+        kind = "reference"
+        sample = (f"{reps} x full {w.name} workload fwd+bwd, fp32, reference_scan_fwd/bwd<1,{w.seq},{w.d_model}> "
+                  f"per batch row on {threads} threads")
+    else:
+        threads = 1
+        h = oracle.scan_forward_f32(a, b)
+        while t_total < seconds and reps < 50:
+            t0 = time.perf_counter()
+            h = oracle.scan_forward_f32(a, b)
+            oracle.scan_backward_f32(a, h, g)
+            t_total += time.perf_counter() - t0
+            reps += 1
+        kind = "port"
+        sample = f"{reps} x full {w.name} workload fwd+bwd, fp32, C restatement, 1 thread"
+    return w.elems * reps / t_total, kind, threads, sample, t_total / reps
+
+
+def run_reference_arm(args):
+    from fast_sequential_scan_b200.workloads import CONFIGS
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = CONFIGS[args.workload]
+    cores = os.cpu_count() or 1
+    # each step = one bounded fwd+bwd sample; warm-up steps are run and discarded
+    per_step_seconds = 0.0
+    from oracle import oracle
+    import numpy as np
+    from fast_sequential_scan_b200.workloads import make_inputs
+    a, b, g = (x.float().numpy() for x in make_inputs(w, "cpu", 0))
+    job = oracle.RefLib().job(w.batch, w.seq, w.d_model) if oracle.RefLib.available() else None
+    threads = max(1, min(cores, w.batch)) if job is not None else 1
+    if job is not None:
+        job.set(job.ALPHA, a); job.set(job.BETA, b); job.set(job.G, g)
+        step = lambda: (job.forward(threads), job.backward(threads))
+        kind = "reference"
+        how = f"reference_scan_fwd/bwd<1,{w.seq},{w.d_model}> per batch row, {threads} threads"
+    else:
+        def step():
+            h = oracle.scan_forward_f32(a, b)
+            oracle.scan_backward_f32(a, h, g)
+        kind = "port"
+        how = "C restatement, 1 thread"
+    steps = min(args.steps, 30)
+    warm = min(args.warmup, 3)
+    for _ in range(warm):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    value = w.elems / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{w.name}: B{w.batch} T{w.seq} D{w.d_model} {w.gates} gates, fp32 on CPU",
+                   "note": "CPU arm runs the single-GPU workload once regardless of --gpus"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind,
+                         "sample": f"{steps} x full {w.name} workload fwd+bwd ({how})"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ GPU arm
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import fast_sequential_scan_b200 as pkg
+    from fast_sequential_scan_b200 import _lib, sequential_scan_cuda as native
+    from fast_sequential_scan_b200.workloads import CONFIGS, make_inputs
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.mode == "seqpar":
+        from fast_sequential_scan_b200 import bench_seqpar
+        bench_seqpar.run(args, world, rank, dev)
+        return
+
+    w = CONFIGS[args.workload]
+    algo = _lib.ALGO_BY_NAME[args.algo]
+    dt = w.torch_dtype
+    esize = 2 if w.dtype == "bf16" else 4
+    tensor_bytes = w.elems * esize
+    # rotate enough disjoint buffer sets that no step finds its inputs in L2
+    sets = max(2, -(-3 * L2_BYTES // (6 * tensor_bytes)))
+    sets = min(sets, 16)
+    bufs = []
+    for s in range(sets):
+        a, b, g = make_inputs(w, dev, seed=1000 * rank + s)
+        bufs.append(dict(a=a, b=b, g=g, h=torch.empty_like(a), da=torch.empty_like(a), db=torch.empty_like(a)))
+
+    def fwd(s):
+        x = bufs[s % sets]
+        native.forward_into(x["a"], x["b"], x["h"], algo=algo)
+
+    def bwd(s):
+        x = bufs[s % sets]
+        native.backward_into(x["a"], x["h"], x["g"], x["da"], x["db"], algo=algo)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    # which kernels a step launches (for gpu_launches): probe the algorithm actually taken
+    took_lookback = True
+    try:
+        native.forward_into(bufs[0]["a"], bufs[0]["b"], bufs[0]["h"], algo=_lib.ALGO_LOOKBACK)
+    except _lib.FssError:
+        took_lookback = False
+    if args.algo == "chunked":
+        took_lookback = False
+    launches_per_step = 2 if took_lookback else 6
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms_step = timed(lambda i: (fwd(i), bwd(i)), args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    ms_fwd = timed(fwd, args.steps, max(3, args.warmup // 4))
+    for s in range(sets):
+        fwd(s)
+    ms_bwd = timed(bwd, args.steps, max(3, args.warmup // 4))
+    pkg.check_status()
+
+    total_elems = w.elems * world
+    value = total_elems / (ms_step * 1e-3)
+    peak, peak_kind = peaks()
+    bwd_bytes = w.elems * w.bytes_per_elem(backward=True, forward=False)
+    fwd_bytes = w.elems * w.bytes_per_elem(backward=False, forward=True)
+    ach_bwd = bwd_bytes / (ms_bwd * 1e-3) / 1e9
+    ach_fwd = fwd_bytes / (ms_fwd * 1e-3) / 1e9
+    ach_step = (bwd_bytes + fwd_bytes) / (ms_step * 1e-3) / 1e9
+    kernel_bwd = "fss::lookback::scan_backward_kernel" if took_lookback else "fss::chunked::chunk_scan_backward (+summary, compose)"
+    roofline = {"bound": "hbm", "kernel": kernel_bwd, "achieved": ach_bwd, "peak": peak, "unit": "GB/s",
+                "frac": ach_bwd / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                "ms_per_launch": ms_bwd,
+                "forward": {"achieved": ach_fwd, "frac": ach_fwd / peak, "ms_per_launch": ms_fwd},
+                "step": {"achieved": ach_step, "frac": ach_step / peak}}
+
+    # ---- end to end through the public autograd API, from pinned host memory ----
+    e2e = None
+    if not args.no_e2e:
+        ha, hb, hg = (x.cpu().pin_memory() for x in (bufs[0]["a"], bufs[0]["b"], bufs[0]["g"]))
+        out_da = torch.empty(ha.shape, dtype=dt).pin_memory()
+        out_db = torch.empty(ha.shape, dtype=dt).pin_memory()
+        out_h = torch.empty(ha.shape, dtype=dt).pin_memory()
+
+        def e2e_step(i):
+            a = ha.to(dev, non_blocking=True).requires_grad_(True)
+            b = hb.to(dev, non_blocking=True).requires_grad_(True)
+            g = hg.to(dev, non_blocking=True)
+            h = (pkg.scan_cu if w.dtype == "bf16" else pkg.scan_cu_single)(a, b)
+            h.backward(g)
+            out_h.copy_(h.detach(), non_blocking=True)
+            out_da.copy_(a.grad, non_blocking=True)
+            out_db.copy_(b.grad, non_blocking=True)
+
+        e_steps = max(3, min(args.steps, 20))
+        ms_e2e = timed(e2e_step, e_steps, 3)
+        e2e = {"value": total_elems / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e, "steps": e_steps,
+               "h2d_bytes_per_step": 3 * tensor_bytes, "d2h_bytes_per_step": 3 * tensor_bytes,
+               "api": "scan_cu(alpha, beta); h.backward(grad) on tensors copied from pinned host memory; "
+                      "h, dalpha, dbeta copied back"}
+        pkg.check_status()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, kind, cores, sample, _ = cpu_reference_leg(w, args.cpu_seconds, os.cpu_count() or 1)
+        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample,
+               "host_cpus": os.cpu_count()}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+            "config": {"workload": f"{w.name}: fwd+bwd scan, B{w.batch} T{w.seq} D{w.d_model} per GPU, {w.gates} gates",
+                       "algo": "lookback" if took_lookback else "chunked",
+                       "parallelism": f"channel-sharded x{world} (d_model {w.d_model * world} total), no collective",
+                       "l2": f"rotating {sets} disjoint buffer sets ({sets * 6 * tensor_bytes / 1e6:.0f} MB > 126 MB L2)"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": launches_per_step * args.steps,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

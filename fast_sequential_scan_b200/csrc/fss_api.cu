@@ -1,0 +1,365 @@
+// C ABI of the library (see include/fss_b200.h): argument checks, algorithm choice, launches.
+// Nothing here allocates or frees device memory, and nothing synchronises the device.
+#include <cstdio>
+#include <cstring>
+#include <initializer_list>
+#include <string>
+
+#include "fss_chunked.cuh"
+#include "fss_common.cuh"
+#include "fss_lookback.cuh"
+#include "fss_seqpar.cuh"
+
+#define FSS_API extern "C" __attribute__((visibility("default")))
+
+namespace fss {
+
+thread_local std::string g_cuda_error;
+
+static int cuda_fail(cudaError_t e, const char *what, int code = FSS_E_LAUNCH) {
+    g_cuda_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+    return code;
+}
+
+#define FSS_CUDA(call, what)                                      \
+    do {                                                          \
+        cudaError_t e_ = (call);                                  \
+        if (e_ != cudaSuccess) return cuda_fail(e_, what);        \
+    } while (0)
+
+// Makes ctx->device current for the duration of a call and puts the previous one back.
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    int error = FSS_OK;
+    int device = -1;
+    explicit DeviceGuard(int want) {
+        cudaError_t e = cudaGetDevice(&prev);
+        if (e != cudaSuccess) { error = cuda_fail(e, "cudaGetDevice", FSS_E_DEVICE); return; }
+        device = prev;
+        if (want >= 0 && want != prev) {
+            e = cudaSetDevice(want);
+            if (e != cudaSuccess) { error = cuda_fail(e, "cudaSetDevice", FSS_E_DEVICE); return; }
+            switched = true;
+            device = want;
+        }
+    }
+    ~DeviceGuard() { if (switched) cudaSetDevice(prev); }
+};
+
+// Workspace: a 256-byte header the look-back kernels keep their epoch in, then algorithm scratch.
+constexpr size_t kHeaderBytes = 256;
+
+static int check_ctx(const fss_scan_ctx *ctx) {
+    if (!ctx) return FSS_E_NULL;
+    if (ctx->struct_bytes != sizeof(fss_scan_ctx)) return FSS_E_ARGS;
+    if (ctx->algo < FSS_ALGO_AUTO || ctx->algo > FSS_ALGO_LOOKBACK) return FSS_E_ALGO;
+    return FSS_OK;
+}
+
+static int check_view(const fss_view *v, int64_t B, int64_t T, int64_t D) {
+    if (!v || !v->ptr) return FSS_E_NULL;
+    if (v->stride_t < D) return FSS_E_SHAPE;
+    if (B > 1 && v->stride_b < (T - 1) * v->stride_t + D) return FSS_E_SHAPE;
+    return FSS_OK;
+}
+
+static int check_shape(int dtype, int64_t B, int64_t T, int64_t D) {
+    if (dtype != FSS_DTYPE_BF16 && dtype != FSS_DTYPE_F32) return FSS_E_DTYPE;
+    if (B < 0 || T < 0 || D < 0) return FSS_E_SHAPE;
+    return FSS_OK;
+}
+
+static int need_workspace(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D, int dtype) {
+    if (!ctx->workspace || ctx->workspace_bytes < fss_workspace_bytes(B, T, D, dtype)) return FSS_E_WORKSPACE;
+    if (!aligned16(ctx->workspace)) return FSS_E_WORKSPACE;
+    return FSS_OK;
+}
+
+static int launch_check(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FSS_OK : cuda_fail(e, what);
+}
+
+// ------------------------------------------------------------------ chunked path
+template <typename T, int V>
+static int chunked_forward(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D,
+                           const fss_view *alpha, const fss_view *beta, const fss_view *h,
+                           const fss_forward_state *st) {
+    using namespace chunked;
+    cudaStream_t stream = (cudaStream_t)ctx->stream;
+    const Geometry g = make_geometry(B, Tn, D, V);
+    float *wsP = reinterpret_cast<float *>((char *)ctx->workspace + kHeaderBytes);
+    float *wsC = reinterpret_cast<float *>((char *)wsP + align_up((size_t)(B * g.S * D) * sizeof(float), 256));
+    const bool cont = ctx->flags & FSS_FLAG_CONTINUATION;
+    const unsigned blocks = (unsigned)(g.vblocks * g.S * B);
+    auto a = make_view<const T>(alpha);
+    auto b = make_view<const T>(beta);
+    auto out = make_view<T>(h);
+    chunk_summary<T, V, false><<<blocks, kThreads, 0, stream>>>(g, a, b, wsP, wsC, cont);
+    const int64_t cols = B * D;
+    chunk_compose<false><<<(unsigned)ceil_div(cols, 128), 128, 0, stream>>>(
+        g, wsP, wsC, (st && cont) ? st->h_in : nullptr, st ? st->h_last : nullptr,
+        st ? st->prod : nullptr, st ? st->block_prod : nullptr);
+    chunk_scan_forward<T, V><<<blocks, kThreads, 0, stream>>>(g, a, b, out, wsC, cont);
+    return launch_check("chunked forward launch");
+}
+
+template <typename T, int V>
+static int chunked_backward(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D,
+                            const fss_view *alpha, const fss_view *h, const fss_view *grad,
+                            const fss_view *dalpha, const fss_view *dbeta,
+                            const fss_backward_state *st) {
+    using namespace chunked;
+    cudaStream_t stream = (cudaStream_t)ctx->stream;
+    const Geometry g = make_geometry(B, Tn, D, V);
+    float *wsP = reinterpret_cast<float *>((char *)ctx->workspace + kHeaderBytes);
+    float *wsC = reinterpret_cast<float *>((char *)wsP + align_up((size_t)(B * g.S * D) * sizeof(float), 256));
+    const bool cont = ctx->flags & FSS_FLAG_CONTINUATION;
+    const unsigned blocks = (unsigned)(g.vblocks * g.S * B);
+    auto a = make_view<const T>(alpha);
+    auto hh = make_view<const T>(h);
+    auto gr = make_view<const T>(grad);
+    chunk_summary<T, V, true><<<blocks, kThreads, 0, stream>>>(g, a, gr, wsP, wsC, cont);
+    const int64_t cols = B * D;
+    chunk_compose<true><<<(unsigned)ceil_div(cols, 128), 128, 0, stream>>>(
+        g, wsP, wsC, st ? st->u_in : nullptr, st ? st->u_out : nullptr, nullptr,
+        st ? st->block_prod : nullptr);
+    chunk_scan_backward<T, V><<<blocks, kThreads, 0, stream>>>(
+        g, a, hh, gr, make_view<T>(dalpha), make_view<T>(dbeta), wsC,
+        (st && cont) ? st->h_prev : nullptr, cont);
+    return launch_check("chunked backward launch");
+}
+
+template <typename T>
+static int forward_typed(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t Tn, int64_t D,
+                         const fss_view *alpha, const fss_view *beta, const fss_view *h,
+                         const fss_forward_state *st) {
+    int algo = ctx->algo;
+    if (algo != FSS_ALGO_CHUNKED) {
+        const bool ok = lookback::layout_ok<T>(B, Tn, D, {alpha, beta, h});
+        if (!ok && algo == FSS_ALGO_LOOKBACK) return FSS_E_LAYOUT;
+        algo = ok ? FSS_ALGO_LOOKBACK : FSS_ALGO_CHUNKED;
+    }
+    if (algo == FSS_ALGO_LOOKBACK)
+        return lookback::forward<T>(ctx, (char *)ctx->workspace, kHeaderBytes, B, Tn, D, alpha, beta, h, st);
+    constexpr int V = VecWidth<T>::value;
+    if (chunked::vector_ok<T>(D, {alpha, beta, h}))
+        return chunked_forward<T, V>(ctx, B, Tn, D, alpha, beta, h, st);
+    return chunked_forward<T, 1>(ctx, B, Tn, D, alpha, beta, h, st);
+}
+
+template <typename T>
+static int backward_typed(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t Tn, int64_t D,
+                          const fss_view *alpha, const fss_view *h, const fss_view *grad,
+                          const fss_view *dalpha, const fss_view *dbeta,
+                          const fss_backward_state *st) {
+    int algo = ctx->algo;
+    if (algo != FSS_ALGO_CHUNKED) {
+        const bool ok = lookback::layout_ok<T>(B, Tn, D, {alpha, h, grad, dalpha, dbeta});
+        if (!ok && algo == FSS_ALGO_LOOKBACK) return FSS_E_LAYOUT;
+        algo = ok ? FSS_ALGO_LOOKBACK : FSS_ALGO_CHUNKED;
+    }
+    if (algo == FSS_ALGO_LOOKBACK)
+        return lookback::backward<T>(ctx, (char *)ctx->workspace, kHeaderBytes, B, Tn, D, alpha, h, grad,
+                                     dalpha, dbeta, st);
+    constexpr int V = VecWidth<T>::value;
+    if (chunked::vector_ok<T>(D, {alpha, h, grad, dalpha, dbeta}))
+        return chunked_backward<T, V>(ctx, B, Tn, D, alpha, h, grad, dalpha, dbeta, st);
+    return chunked_backward<T, 1>(ctx, B, Tn, D, alpha, h, grad, dalpha, dbeta, st);
+}
+
+}  // namespace fss
+
+using namespace fss;
+
+// ====================================================================== exported functions
+
+FSS_API int fss_abi_version(void) { return FSS_ABI_VERSION; }
+
+FSS_API const char *fss_strerror(int code) {
+    switch (code) {
+    case FSS_OK: return "ok";
+    case FSS_E_NULL: return "a required pointer is NULL";
+    case FSS_E_SHAPE: return "bad shape or stride";
+    case FSS_E_DTYPE: return "unknown dtype";
+    case FSS_E_WORKSPACE: return "workspace missing, misaligned or too small";
+    case FSS_E_LAYOUT: return "layout not usable by the look-back (TMA) kernels";
+    case FSS_E_LAUNCH: return "CUDA launch failed";
+    case FSS_E_ALGO: return "unknown algorithm";
+    case FSS_E_DEVICE: return "CUDA device selection failed";
+    case FSS_E_TENSORMAP: return "TMA descriptor rejected by the driver";
+    case FSS_E_ARGS: return "struct_bytes does not match this library";
+    case FSS_E_TOO_LARGE: return "problem larger than this entry point's fixed capacity";
+    }
+    return "unknown error code";
+}
+
+FSS_API const char *fss_last_cuda_error(void) { return g_cuda_error.c_str(); }
+
+FSS_API size_t fss_workspace_bytes(int64_t B, int64_t T, int64_t D, int dtype) {
+    if (B <= 0 || T <= 0 || D <= 0) return kHeaderBytes;
+    size_t a = chunked::workspace_bytes(B, T, D);
+    size_t b = lookback::workspace_bytes(B, T, D, dtype);
+    return kHeaderBytes + (a > b ? a : b);
+}
+
+FSS_API int fss_workspace_init(void *workspace, size_t bytes, void *stream) {
+    if (!workspace) return FSS_E_NULL;
+    FSS_CUDA(cudaMemsetAsync(workspace, 0, bytes, (cudaStream_t)stream), "cudaMemsetAsync(workspace)");
+    return FSS_OK;
+}
+
+FSS_API int64_t fss_block_rows(int dtype, int64_t B, int64_t T, int64_t D, int algo) {
+    if (B <= 0 || T <= 0 || D <= 0) return 1;
+    if (algo == FSS_ALGO_CHUNKED) return chunked::make_geometry(B, T, D, 1).L;
+    return lookback::block_rows(dtype, B, T, D);
+}
+
+FSS_API int fss_scan_forward_ex(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                                const fss_view *alpha, const fss_view *beta, const fss_view *h,
+                                const fss_forward_state *state) {
+    int rc;
+    if ((rc = check_ctx(ctx))) return rc;
+    if ((rc = check_shape(dtype, B, T, D))) return rc;
+    if (B == 0 || T == 0 || D == 0) return FSS_OK;
+    if ((rc = check_view(alpha, B, T, D)) || (rc = check_view(beta, B, T, D)) || (rc = check_view(h, B, T, D)))
+        return rc;
+    if ((rc = need_workspace(ctx, B, T, D, dtype))) return rc;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    return dtype == FSS_DTYPE_BF16
+               ? forward_typed<bf16>(ctx, dtype, B, T, D, alpha, beta, h, state)
+               : forward_typed<float>(ctx, dtype, B, T, D, alpha, beta, h, state);
+}
+
+FSS_API int fss_scan_backward_ex(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                                 const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
+                                 const fss_view *grad_alpha, const fss_view *grad_beta,
+                                 const fss_backward_state *state) {
+    int rc;
+    if ((rc = check_ctx(ctx))) return rc;
+    if ((rc = check_shape(dtype, B, T, D))) return rc;
+    if (B == 0 || T == 0 || D == 0) return FSS_OK;
+    for (const fss_view *v : {alpha, h, grad_out, grad_alpha, grad_beta})
+        if ((rc = check_view(v, B, T, D))) return rc;
+    if ((rc = need_workspace(ctx, B, T, D, dtype))) return rc;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    return dtype == FSS_DTYPE_BF16
+               ? backward_typed<bf16>(ctx, dtype, B, T, D, alpha, h, grad_out, grad_alpha, grad_beta, state)
+               : backward_typed<float>(ctx, dtype, B, T, D, alpha, h, grad_out, grad_alpha, grad_beta, state);
+}
+
+FSS_API int fss_scan_forward(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
+                             const fss_view *alpha, const fss_view *beta, const fss_view *h) {
+    return fss_scan_forward_ex(ctx, FSS_DTYPE_F32, B, T, D, alpha, beta, h, nullptr);
+}
+
+FSS_API int fss_scan_backward(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
+                              const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
+                              const fss_view *grad_alpha, const fss_view *grad_beta) {
+    return fss_scan_backward_ex(ctx, FSS_DTYPE_F32, B, T, D, alpha, h, grad_out, grad_alpha, grad_beta, nullptr);
+}
+
+FSS_API int fss_scan_forward_half(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
+                                  const fss_view *alpha, const fss_view *beta, const fss_view *h) {
+    return fss_scan_forward_ex(ctx, FSS_DTYPE_BF16, B, T, D, alpha, beta, h, nullptr);
+}
+
+FSS_API int fss_scan_backward_half(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
+                                   const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
+                                   const fss_view *grad_alpha, const fss_view *grad_beta) {
+    return fss_scan_backward_ex(ctx, FSS_DTYPE_BF16, B, T, D, alpha, h, grad_out, grad_alpha, grad_beta, nullptr);
+}
+
+// ---------------------------------------------------------------------- sequence-parallel
+FSS_API int fss_seqpar_compose(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n,
+                               const float *pc, float *carry_in) {
+    int rc;
+    if ((rc = check_ctx(ctx))) return rc;
+    if (!pc || !carry_in) return FSS_E_NULL;
+    if (world < 1 || rank < 0 || rank >= world || n < 0) return FSS_E_SHAPE;
+    if (n == 0) return FSS_OK;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    seqpar::compose<<<(unsigned)ceil_div(n, 256), 256, 0, (cudaStream_t)ctx->stream>>>(
+        backward, world, rank, n, pc, carry_in);
+    return launch_check("seqpar compose launch");
+}
+
+namespace fss {
+static seqpar::Geometry fixup_geometry(int64_t B, int64_t T, int64_t D, int64_t R, int V) {
+    seqpar::Geometry g;
+    g.B = B; g.T = T; g.D = D; g.R = R;
+    g.NB = ceil_div(T, R);
+    g.nvec = D / V;
+    g.vblocks = ceil_div(g.nvec, seqpar::kThreads);
+    return g;
+}
+
+template <typename T, int V>
+static int fixup_forward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *alpha,
+                                const fss_view *h, const float *carry_in, const float *bp, int64_t R) {
+    const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
+    seqpar::fixup_forward<T, V><<<(unsigned)(g.vblocks * g.NB * B), seqpar::kThreads, 0, (cudaStream_t)ctx->stream>>>(
+        g, make_view<const T>(alpha), make_view<T>(h), carry_in, bp);
+    return launch_check("seqpar forward fix-up launch");
+}
+
+template <typename T, int V>
+static int fixup_backward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *alpha,
+                                 const fss_view *h, const fss_view *da, const fss_view *db, const float *u_in,
+                                 const float *h_prev, const float *bp, int64_t R) {
+    const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
+    seqpar::fixup_backward<T, V><<<(unsigned)(g.vblocks * g.NB * B), seqpar::kThreads, 0, (cudaStream_t)ctx->stream>>>(
+        g, make_view<const T>(alpha), make_view<const T>(h), make_view<T>(da), make_view<T>(db), u_in, h_prev, bp);
+    return launch_check("seqpar backward fix-up launch");
+}
+}  // namespace fss
+
+FSS_API int fss_seqpar_fixup_forward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                                     const fss_view *alpha, const fss_view *h, const float *carry_in,
+                                     const float *block_prod, int64_t block_rows) {
+    int rc;
+    if ((rc = check_ctx(ctx))) return rc;
+    if ((rc = check_shape(dtype, B, T, D))) return rc;
+    if (B == 0 || T == 0 || D == 0) return FSS_OK;
+    if ((rc = check_view(alpha, B, T, D)) || (rc = check_view(h, B, T, D))) return rc;
+    if (!carry_in || !block_prod) return FSS_E_NULL;
+    if (block_rows < 1) return FSS_E_SHAPE;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    if (dtype == FSS_DTYPE_BF16) {
+        if (chunked::vector_ok<bf16>(D, {alpha, h}))
+            return fixup_forward_launch<bf16, 8>(ctx, B, T, D, alpha, h, carry_in, block_prod, block_rows);
+        return fixup_forward_launch<bf16, 1>(ctx, B, T, D, alpha, h, carry_in, block_prod, block_rows);
+    }
+    if (chunked::vector_ok<float>(D, {alpha, h}))
+        return fixup_forward_launch<float, 4>(ctx, B, T, D, alpha, h, carry_in, block_prod, block_rows);
+    return fixup_forward_launch<float, 1>(ctx, B, T, D, alpha, h, carry_in, block_prod, block_rows);
+}
+
+FSS_API int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                                      const fss_view *alpha, const fss_view *h, const fss_view *grad_alpha,
+                                      const fss_view *grad_beta, const float *u_in, const float *h_prev,
+                                      const float *block_prod, int64_t block_rows) {
+    int rc;
+    if ((rc = check_ctx(ctx))) return rc;
+    if ((rc = check_shape(dtype, B, T, D))) return rc;
+    if (B == 0 || T == 0 || D == 0) return FSS_OK;
+    for (const fss_view *v : {alpha, h, grad_alpha, grad_beta})
+        if ((rc = check_view(v, B, T, D))) return rc;
+    if (!u_in || !block_prod) return FSS_E_NULL;
+    if (block_rows < 1) return FSS_E_SHAPE;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    if (dtype == FSS_DTYPE_BF16) {
+        if (chunked::vector_ok<bf16>(D, {alpha, h, grad_alpha, grad_beta}))
+            return fixup_backward_launch<bf16, 8>(ctx, B, T, D, alpha, h, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_rows);
+        return fixup_backward_launch<bf16, 1>(ctx, B, T, D, alpha, h, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_rows);
+    }
+    if (chunked::vector_ok<float>(D, {alpha, h, grad_alpha, grad_beta}))
+        return fixup_backward_launch<float, 4>(ctx, B, T, D, alpha, h, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_rows);
+    return fixup_backward_launch<float, 1>(ctx, B, T, D, alpha, h, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_rows);
+}

@@ -1,0 +1,187 @@
+"""Tensor-level face of the native library: the four functions of the reference's extension
+module ``sequential_scan_cuda`` (csrc/sequential_scan.cpp:13-22), same names, same arguments,
+same returns -- ``scan_forward(alpha, beta) -> h`` and
+``scan_backward(alpha_saved, h_saved, grad_out) -> [grad_alpha, grad_beta]`` in fp32, and the
+``*_half`` pair in bf16 -- implemented over the C ABI in ``include/fss_b200.h``.
+
+Behaviour kept from the reference: outputs are freshly allocated with the inputs' shape and
+dtype; a wrong dtype raises (the reference's ``data_ptr<T>()`` throws).  Behaviour changed on
+purpose: any ``d_model`` and any ``seq`` are accepted (the reference raises ``RuntimeError`` outside
+five widths, csrc/sequential_scan_kernel.cu:54); ``grad_beta`` is its own tensor (the reference's
+bf16 backward returns the saved ``h`` storage, csrc/sequential_scan_kernel.cu:197); launches go to
+torch's current stream; shapes, devices and layouts are validated.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import List, Optional
+
+import torch
+
+from . import _lib, workspace
+
+_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_F32}
+
+
+def default_algo() -> int:
+    """Kernel family: ``FSS_B200_ALGO`` = auto | chunked | lookback (default auto)."""
+    name = os.environ.get("FSS_B200_ALGO", "auto").lower()
+    if name not in _lib.ALGO_BY_NAME:
+        raise ValueError(f"FSS_B200_ALGO={name!r}: expected one of {sorted(_lib.ALGO_BY_NAME)}")
+    return _lib.ALGO_BY_NAME[name]
+
+
+def _check_tensor(name: str, t: torch.Tensor, like: Optional[torch.Tensor], dtype: torch.dtype) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name}: expected dtype {dtype}, got {t.dtype}")
+    if t.dim() != 3:
+        raise RuntimeError(f"{name}: expected a [batch, seq, d_model] tensor, got {tuple(t.shape)}")
+    if like is not None:
+        if t.shape != like.shape:
+            raise RuntimeError(f"{name}: shape {tuple(t.shape)} differs from {tuple(like.shape)}")
+        if t.device != like.device:
+            raise RuntimeError(f"{name}: on {t.device}, expected {like.device}")
+
+
+def _rowwise(t: torch.Tensor) -> torch.Tensor:
+    """A tensor the kernels can address: unit channel stride, rows and batches not overlapping."""
+    B, T, D = t.shape
+    if t.numel() == 0:
+        return t
+    ok = (D == 1 or t.stride(2) == 1) and (T == 1 or t.stride(1) >= D) and \
+         (B == 1 or t.stride(0) >= (T - 1) * t.stride(1) + D)
+    return t if ok else t.contiguous()
+
+
+def _view(t: torch.Tensor) -> _lib.View:
+    B, T, D = t.shape
+    st = t.stride(1) if T > 1 else D
+    sb = t.stride(0) if B > 1 else max(st * T, 1)
+    return _lib.View(t.data_ptr(), sb, st)
+
+
+def _ctx(device: torch.device, ws: workspace.Workspace, algo: Optional[int], flags: int = 0) -> _lib.ScanCtx:
+    return _lib.ScanCtx(ctypes.sizeof(_lib.ScanCtx), device.index, ws.stream_handle,
+                        ws.buf.data_ptr(), ws.buf.numel(), ws.status.data_ptr(),
+                        default_algo() if algo is None else algo, flags)
+
+
+def _vec(t: Optional[torch.Tensor], B: int, D: int, name: str) -> Optional[int]:
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous() or t.numel() != B * D:
+        raise RuntimeError(f"{name}: expected a contiguous fp32 CUDA tensor of {B}x{D} elements")
+    return t.data_ptr()
+
+
+def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_last=None,
+                 prod=None, block_prod=None) -> None:
+    """h <- scan(alpha, beta) into a caller-owned tensor, with the optional boundary state."""
+    dtype = alpha.dtype
+    if dtype not in _DTYPES:
+        raise RuntimeError(f"alpha: unsupported dtype {dtype} (bf16 or fp32)")
+    _check_tensor("alpha", alpha, None, dtype)
+    _check_tensor("beta", beta, alpha, dtype)
+    _check_tensor("h", h, alpha, dtype)
+    B, T, D = alpha.shape
+    if alpha.numel() == 0:
+        return
+    a, b = _rowwise(alpha), _rowwise(beta)
+    if _rowwise(h) is not h:
+        raise RuntimeError("h: output must have unit channel stride and non-overlapping rows")
+    L = _lib.lib()
+    with torch.cuda.device(alpha.device):
+        ws = workspace.get(alpha.device, L.fss_workspace_bytes(B, T, D, _DTYPES[dtype]))
+        ctx = _ctx(alpha.device, ws, algo, _lib.FLAG_CONTINUATION if continuation else 0)
+        state = None
+        if any(x is not None for x in (h_in, h_last, prod, block_prod)):
+            bp = None
+            if block_prod is not None:
+                if block_prod.dtype != torch.float32 or not block_prod.is_contiguous():
+                    raise RuntimeError("block_prod: expected contiguous fp32")
+                bp = block_prod.data_ptr()
+            state = _lib.ForwardState(_vec(h_in, B, D, "h_in"), _vec(h_last, B, D, "h_last"),
+                                      _vec(prod, B, D, "prod"), bp)
+        va, vb, vh = _view(a), _view(b), _view(h)
+        rc = L.fss_scan_forward_ex(ctypes.byref(ctx), _DTYPES[dtype], B, T, D, ctypes.byref(va),
+                                   ctypes.byref(vb), ctypes.byref(vh),
+                                   ctypes.byref(state) if state is not None else None)
+    _lib.check(rc, "fss_scan_forward_ex")
+
+
+def backward_into(alpha, h, grad_out, grad_alpha, grad_beta, *, algo=None, continuation=False,
+                  u_in=None, h_prev=None, u_out=None, block_prod=None) -> None:
+    dtype = alpha.dtype
+    if dtype not in _DTYPES:
+        raise RuntimeError(f"alpha_saved: unsupported dtype {dtype} (bf16 or fp32)")
+    _check_tensor("alpha_saved", alpha, None, dtype)
+    _check_tensor("h_saved", h, alpha, dtype)
+    _check_tensor("grad_out", grad_out, alpha, dtype)
+    _check_tensor("grad_alpha", grad_alpha, alpha, dtype)
+    _check_tensor("grad_beta", grad_beta, alpha, dtype)
+    B, T, D = alpha.shape
+    if alpha.numel() == 0:
+        return
+    a, hh, g = _rowwise(alpha), _rowwise(h), _rowwise(grad_out)
+    for name, t in (("grad_alpha", grad_alpha), ("grad_beta", grad_beta)):
+        if _rowwise(t) is not t:
+            raise RuntimeError(f"{name}: output must have unit channel stride and non-overlapping rows")
+    L = _lib.lib()
+    with torch.cuda.device(alpha.device):
+        ws = workspace.get(alpha.device, L.fss_workspace_bytes(B, T, D, _DTYPES[dtype]))
+        ctx = _ctx(alpha.device, ws, algo, _lib.FLAG_CONTINUATION if continuation else 0)
+        state = None
+        if any(x is not None for x in (u_in, h_prev, u_out, block_prod)):
+            bp = None
+            if block_prod is not None:
+                if block_prod.dtype != torch.float32 or not block_prod.is_contiguous():
+                    raise RuntimeError("block_prod: expected contiguous fp32")
+                bp = block_prod.data_ptr()
+            state = _lib.BackwardState(_vec(u_in, B, D, "u_in"), _vec(h_prev, B, D, "h_prev"),
+                                       _vec(u_out, B, D, "u_out"), bp)
+        views = [_view(t) for t in (a, hh, g, grad_alpha, grad_beta)]
+        rc = L.fss_scan_backward_ex(ctypes.byref(ctx), _DTYPES[dtype], B, T, D,
+                                    *[ctypes.byref(v) for v in views],
+                                    ctypes.byref(state) if state is not None else None)
+    _lib.check(rc, "fss_scan_backward_ex")
+
+
+def _forward(alpha: torch.Tensor, beta: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    _check_tensor("alpha", alpha, None, dtype)
+    _check_tensor("beta", beta, alpha, dtype)
+    h = torch.empty(alpha.shape, dtype=dtype, device=alpha.device)
+    forward_into(alpha, beta, h)
+    return h
+
+
+def _backward(alpha_saved, h_saved, grad_out, dtype) -> List[torch.Tensor]:
+    _check_tensor("alpha_saved", alpha_saved, None, dtype)
+    grad_alpha = torch.empty(alpha_saved.shape, dtype=dtype, device=alpha_saved.device)
+    grad_beta = torch.empty(alpha_saved.shape, dtype=dtype, device=alpha_saved.device)
+    backward_into(alpha_saved, h_saved, grad_out, grad_alpha, grad_beta)
+    return [grad_alpha, grad_beta]
+
+
+def scan_forward(alpha: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
+    """fp32 forward scan (reference: csrc/sequential_scan_kernel.cu:7-58)."""
+    return _forward(alpha, beta, torch.float32)
+
+
+def scan_backward(alpha_saved, h_saved, grad_out) -> List[torch.Tensor]:
+    """fp32 backward, ``[grad_alpha, grad_beta]`` (reference: csrc/sequential_scan_kernel.cu:60-124)."""
+    return _backward(alpha_saved, h_saved, grad_out, torch.float32)
+
+
+def scan_forward_half(alpha: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
+    """bf16 forward scan, fp32 state (reference: csrc/sequential_scan_kernel.cu:126-187)."""
+    return _forward(alpha, beta, torch.bfloat16)
+
+
+def scan_backward_half(alpha_saved, h_saved, grad_out) -> List[torch.Tensor]:
+    """bf16 backward (reference: csrc/sequential_scan_kernel.cu:189-268)."""
+    return _backward(alpha_saved, h_saved, grad_out, torch.bfloat16)

@@ -1,0 +1,180 @@
+/*
+ * fss_b200 -- C ABI of the B200 (sm_100a) sequential-scan library.
+ *
+ * The library computes the first-order diagonal linear recurrence
+ *
+ *     h_0 = b_0 ;  h_t = a_t * h_{t-1} + b_t                (forward)
+ *     dh_{T-1} = g_{T-1} ;  dh_t = g_t + a_{t+1} * dh_{t+1}
+ *     db_t = dh_t ;  da_t = dh_t * h_{t-1} (t>=1) ;  da_0 = 0 (backward)
+ *
+ * over tensors [B, T, D] (D fastest) of bf16 or fp32 with fp32 state.  It is the native side
+ * of the reference project's torch extension `sequential_scan_cuda`
+ * (csrc/sequential_scan.cpp:3-23): the four reference functions map to the four functions of
+ * the same name below.  Differences from that boundary, on purpose:
+ *   - plain C: raw device pointers, sizes, a stream handle in; an int status out
+ *     (the reference takes and returns torch::Tensor);
+ *   - the caller owns every buffer: outputs and workspace are passed in, nothing is allocated
+ *     or freed here (the reference allocates with torch::empty_like, and its bf16 backward
+ *     writes grad_beta over the saved forward output, csrc/sequential_scan_kernel.cu:196-197);
+ *   - any D >= 1, any T >= 1, 64-bit offsets, row/batch strides, the caller's stream
+ *     (the reference accepts five d_model values and launches on the legacy stream,
+ *     csrc/sequential_scan_kernel.cu:17-55).
+ *
+ * All functions return FSS_OK (0) or a negative FSS_E_* code; fss_strerror() names it.  They
+ * only enqueue work on `stream`; device-side give-ups (a bounded wait that ran out) are
+ * reported through the status word, see fss_scan_ctx.status.
+ */
+#ifndef FSS_B200_H
+#define FSS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FSS_ABI_VERSION 1
+
+/* element types of the [B,T,D] tensors */
+#define FSS_DTYPE_BF16 0
+#define FSS_DTYPE_F32 1
+
+/* kernel families */
+#define FSS_ALGO_AUTO 0     /* single-pass TMA kernel when the layout allows it, else chunked   */
+#define FSS_ALGO_CHUNKED 1  /* three launches: chunk summaries, carry composition, chunk re-scan */
+#define FSS_ALGO_LOOKBACK 2 /* one persistent launch: TMA tiles + decoupled look-back of carries */
+
+/* return codes */
+#define FSS_OK 0
+#define FSS_E_NULL (-1)       /* a required pointer is NULL                                  */
+#define FSS_E_SHAPE (-2)      /* B, T or D < 0, or a stride smaller than the extent it spans  */
+#define FSS_E_DTYPE (-3)      /* dtype is not one of FSS_DTYPE_*                              */
+#define FSS_E_WORKSPACE (-4)  /* workspace missing or smaller than fss_workspace_bytes()       */
+#define FSS_E_LAYOUT (-5)     /* FSS_ALGO_LOOKBACK asked for a layout it cannot take          */
+#define FSS_E_LAUNCH (-6)     /* the CUDA runtime refused a launch (see fss_last_cuda_error)  */
+#define FSS_E_ALGO (-7)       /* unknown algorithm id                                         */
+#define FSS_E_DEVICE (-8)     /* device query / cudaSetDevice failed                          */
+#define FSS_E_TENSORMAP (-9)  /* the driver refused a TMA descriptor                          */
+#define FSS_E_ARGS (-10)      /* struct_bytes does not match this header                      */
+#define FSS_E_TOO_LARGE (-11) /* problem exceeds a fixed-capacity entry point                 */
+
+/* values the kernels write to the status word (0 = nothing to report) */
+#define FSS_STATUS_OK 0
+#define FSS_STATUS_LOOKBACK_TIMEOUT 1 /* a tile gave up waiting for its predecessor's carry  */
+#define FSS_STATUS_TMA_TIMEOUT 2      /* a tile gave up waiting for its own TMA loads        */
+
+/* One [B, T, D] tensor: element (b,t,d) lives at ptr + (b*stride_b + t*stride_t + d) elements. */
+typedef struct fss_view {
+    void *ptr;
+    int64_t stride_b; /* in elements */
+    int64_t stride_t; /* in elements; >= D */
+} fss_view;
+
+/* What every call needs besides its tensors. */
+typedef struct fss_scan_ctx {
+    uint32_t struct_bytes; /* sizeof(fss_scan_ctx): guards against header/library skew          */
+    int32_t device;        /* CUDA ordinal the buffers live on; -1 = the thread's current device */
+    void *stream;          /* cudaStream_t; NULL = legacy default stream                         */
+    void *workspace;       /* device scratch, >= fss_workspace_bytes(); zeroed once by           */
+    size_t workspace_bytes; /*   fss_workspace_init() and then reused by consecutive launches on
+                                ONE stream (two launches sharing it must not overlap)            */
+    int32_t *status;       /* device-visible int (device memory or pinned host memory) that a
+                              kernel sets to FSS_STATUS_* when it gives up; may be NULL          */
+    int32_t algo;          /* FSS_ALGO_*                                                         */
+    int32_t flags;         /* FSS_FLAG_*                                                         */
+} fss_scan_ctx;
+
+/* Treat the tensors as rows s..s+T-1 of a longer sequence: row 0 DOES read alpha_0 (forward
+ * h_0 = a_0*h_in + b_0; the returned product includes a_0) instead of the h_0 = b_0 rule.      */
+#define FSS_FLAG_CONTINUATION 1
+
+/* Optional per-column state vectors, all fp32, contiguous [B, D]; any may be NULL. */
+typedef struct fss_forward_state {
+    const float *h_in; /* state entering row 0 (needs FSS_FLAG_CONTINUATION); NULL = 0          */
+    float *h_last;     /* out: unrounded state after the last row                               */
+    float *prod;       /* out: product of alpha over all rows (0 without FSS_FLAG_CONTINUATION) */
+    float *block_prod; /* out, [B, nblocks, D]: product of alpha over rows 0..(j+1)*R-1 for every
+                          block j of R = fss_block_rows() rows; feeds fss_seqpar_fixup_forward  */
+} fss_forward_state;
+
+typedef struct fss_backward_state {
+    const float *u_in;   /* a_T*dh_T arriving from the rows after this tensor; NULL = 0         */
+    const float *h_prev; /* h_{-1} for dalpha_0 (needs FSS_FLAG_CONTINUATION); NULL = dalpha_0=0 */
+    float *u_out;        /* out: a_0*dh_0, what these rows hand to the rows before them         */
+    float *block_prod;   /* out, [B, nblocks, D]: product of alpha over rows j*R..T-1 for every
+                            block j of R = fss_block_rows() rows; feeds fss_seqpar_fixup_backward */
+} fss_backward_state;
+
+/* ---- library information ------------------------------------------------------------- */
+int fss_abi_version(void);
+const char *fss_strerror(int code);
+/* text of the last CUDA runtime error seen by the calling thread in this library */
+const char *fss_last_cuda_error(void);
+
+/* ---- workspace ------------------------------------------------------------------------ */
+/* Bytes of scratch a forward or backward call on [B,T,D] of `dtype` may use (any algorithm). */
+size_t fss_workspace_bytes(int64_t B, int64_t T, int64_t D, int dtype);
+/* Zero a freshly allocated workspace (enqueued on `stream`).  Needed once per allocation. */
+int fss_workspace_init(void *workspace, size_t bytes, void *stream);
+
+/* ---- the reference's four entry points -------------------------------------------------- */
+/* fp32 forward.  Replaces scan_forward (csrc/sequential_scan.cpp:3,13;
+ * csrc/sequential_scan_kernel.cu:7-58).  h may not alias alpha or beta. */
+int fss_scan_forward(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
+                     const fss_view *alpha, const fss_view *beta, const fss_view *h);
+/* fp32 backward.  Replaces scan_backward (csrc/sequential_scan.cpp:4-6,15;
+ * csrc/sequential_scan_kernel.cu:60-124).  h is the saved forward output. */
+int fss_scan_backward(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
+                      const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
+                      const fss_view *grad_alpha, const fss_view *grad_beta);
+/* bf16 forward.  Replaces scan_forward_half (csrc/sequential_scan.cpp:8,19;
+ * csrc/sequential_scan_kernel.cu:126-187). */
+int fss_scan_forward_half(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
+                          const fss_view *alpha, const fss_view *beta, const fss_view *h);
+/* bf16 backward.  Replaces scan_backward_half (csrc/sequential_scan.cpp:9-11,21;
+ * csrc/sequential_scan_kernel.cu:189-268).  grad_beta is its own buffer here. */
+int fss_scan_backward_half(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
+                           const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
+                           const fss_view *grad_alpha, const fss_view *grad_beta);
+
+/* ---- the same scans with explicit dtype and boundary state ------------------------------ */
+/* Generalise the four functions above (which call these with state == NULL); the reference has
+ * no counterpart for the state vectors -- its kernels always start from h_0 = b_0
+ * (csrc/include/sequential_scan_kernel_bf16.cuh:91-100). */
+int fss_scan_forward_ex(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                        const fss_view *alpha, const fss_view *beta, const fss_view *h,
+                        const fss_forward_state *state);
+int fss_scan_backward_ex(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                         const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
+                         const fss_view *grad_alpha, const fss_view *grad_beta,
+                         const fss_backward_state *state);
+
+/* ---- sequence-parallel pieces (no counterpart in the reference, which never splits T) ---- */
+/* Rows per block of the block_prod outputs for this problem and algorithm (> 0). */
+int64_t fss_block_rows(int dtype, int64_t B, int64_t T, int64_t D, int algo);
+/* Fold the gathered per-rank summaries into what enters rank `rank`:
+ *   forward : pc = [world][2][B*D] fp32 holding (prod_r, h_last_r) of each rank's zero-state scan;
+ *             carry_in[B*D] = state after ranks 0..rank-1.
+ *   backward: pc = [world][2][B*D] holding (prod_r, u_out_r); carry_in = u entering from
+ *             ranks rank+1..world-1.  One small launch on ctx->stream. */
+int fss_seqpar_compose(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n,
+                       const float *pc, float *carry_in);
+/* Add the effect of carry_in to a zero-state forward scan:  h_t += (a_0*...*a_t) * carry_in.
+ * block_prod / block_rows are what the zero-state scan wrote; a block whose entering product has
+ * underflowed to exactly zero is skipped, which changes no bit of the result. */
+int fss_seqpar_fixup_forward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                             const fss_view *alpha, const fss_view *h, const float *carry_in,
+                             const float *block_prod, int64_t block_rows);
+/* Add the effect of u_in (entering after the last row) to a zero-state backward scan:
+ *   dbeta_t += R_t*u_in ; dalpha_t += R_t*u_in*h_{t-1},  R_t = a_{t+1}*...*a_{T-1}.
+ * h_prev is h_{-1} (NULL = 0). */
+int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                              const fss_view *alpha, const fss_view *h, const fss_view *grad_alpha,
+                              const fss_view *grad_beta, const float *u_in, const float *h_prev,
+                              const float *block_prod, int64_t block_rows);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FSS_B200_H */

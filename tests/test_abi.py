@@ -1,0 +1,88 @@
+"""CPU-side checks of the boundary: the library loads, exports every symbol the header
+declares, and rejects bad arguments before touching a device."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "fss_b200.h"
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(fss_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from fast_sequential_scan_b200 import _lib
+    L = _lib.lib()
+    names = declared_functions()
+    assert len(names) >= 15
+    for name in names:
+        assert hasattr(L, name), f"{name} declared in include/fss_b200.h but not exported"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes table and header disagree"
+    assert L.fss_abi_version() == 1
+
+
+def test_struct_layouts_match_the_header():
+    from fast_sequential_scan_b200 import _lib
+    assert ctypes.sizeof(_lib.View) == 24
+    assert ctypes.sizeof(_lib.ScanCtx) == 48
+    assert ctypes.sizeof(_lib.ForwardState) == 32 and ctypes.sizeof(_lib.BackwardState) == 32
+
+
+def test_error_strings_and_argument_checks_need_no_device():
+    from fast_sequential_scan_b200 import _lib
+    L = _lib.lib()
+    assert L.fss_strerror(0) == b"ok"
+    for code in range(-11, 0):
+        assert L.fss_strerror(code) != b"unknown error code"
+    v = _lib.View(0, 0, 0)
+    ctx = _lib.ScanCtx(ctypes.sizeof(_lib.ScanCtx), -1, None, None, 0, None, 0, 0)
+    call = lambda c, B, T, D, *views: L.fss_scan_forward_half(ctypes.byref(c), B, T, D, *[ctypes.byref(x) for x in views])
+    assert call(ctx, 2, 4, 8, v, v, v) == -1                       # NULL tensor
+    assert call(ctx, -1, 4, 8, v, v, v) == -2                      # negative extent
+    assert call(ctx, 0, 4, 8, v, v, v) == 0                        # empty problem: nothing to do
+    bad = _lib.ScanCtx(8, -1, None, None, 0, None, 0, 0)
+    assert call(bad, 2, 4, 8, v, v, v) == -10                      # struct size skew
+    ctx.algo = 9
+    assert call(ctx, 2, 4, 8, v, v, v) == -7
+    ctx.algo = 0
+    buf = (ctypes.c_uint16 * 64)()
+    p = _lib.View(ctypes.addressof(buf), 32, 4)                    # row stride 4 < D = 8
+    assert call(ctx, 2, 4, 8, p, p, p) == -2
+    ok = _lib.View(ctypes.addressof(buf), 32, 8)
+    assert call(ctx, 2, 4, 8, ok, ok, ok) == -4                    # no workspace
+    assert L.fss_workspace_bytes(8, 2048, 1024, 0) > 256
+    assert L.fss_workspace_bytes(0, 0, 0, 0) == 256
+    assert L.fss_block_rows(0, 1, 65536, 4096, 1) >= 1
+
+
+def test_package_has_no_fallback_when_library_is_missing(monkeypatch, tmp_path):
+    from fast_sequential_scan_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setenv("FSS_B200_LIB", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError):
+        _lib.lib()
+    monkeypatch.delenv("FSS_B200_LIB")
+    monkeypatch.setattr(_lib, "_lib", None)
+    _lib.lib()
+
+
+def test_product_never_imports_the_oracle():
+    pkg = ROOT / "fast_sequential_scan_b200"
+    for path in list(pkg.rglob("*.py")) + list(pkg.rglob("*.cu*")):
+        text = path.read_text()
+        assert "oracle" not in text.replace("# oracle", ""), f"{path} mentions the oracle"
+
+
+def test_python_surface_mirrors_the_reference_names():
+    import fast_sequential_scan_b200 as pkg
+    from fast_sequential_scan_b200 import scan_cuda, sequential_scan_cuda as native
+    assert callable(pkg.scan_cu) and callable(pkg.scan_cu_single)
+    for name in ("SequentialScan", "SequentialScanSingle", "scan", "scan_single"):
+        assert hasattr(scan_cuda, name)
+    for name in ("scan_forward", "scan_backward", "scan_forward_half", "scan_backward_half"):
+        assert callable(getattr(native, name))

@@ -1,0 +1,253 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU checker.
+
+Tolerances (mixed absolute/relative, torch.allclose style):
+    bf16 I/O : |x - ref| <= 1e-2 + 1e-2*|ref|
+    fp32     : |x - ref| <= 1e-5 + 1e-5*|ref|
+where ref is the fp32 sequential scan of the same (already rounded) inputs.  The reference's
+own metric -- relative L2 error counted in digits, 7 for fp32 and 2 for bf16
+(sequential_scan/test_scan_cuda.py:18-19) -- is asserted on its own test grid as well.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_cases, load_golden
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL, F32_TOL = 1e-2, 1e-5
+ALGOS = ["chunked", "lookback", "auto"]
+
+
+def _mods():
+    import fast_sequential_scan_b200 as pkg
+    from fast_sequential_scan_b200 import _lib, sequential_scan_cuda as native
+    return pkg, native, _lib
+
+
+def _algo_id(name):
+    from fast_sequential_scan_b200 import _lib
+    return _lib.ALGO_BY_NAME[name]
+
+
+def run_native(a, b, g, algo):
+    """forward + backward through the C ABI; returns (h, dalpha, dbeta) on the GPU."""
+    _, native, _lib = _mods()
+    h = torch.empty_like(a)
+    try:
+        native.forward_into(a, b, h, algo=_algo_id(algo))
+    except _lib.FssError as e:
+        if e.code == -5 and algo == "lookback":
+            pytest.skip("layout not eligible for the single-pass kernels")
+        raise
+    da, db = torch.empty_like(a), torch.empty_like(a)
+    native.backward_into(a, h, g, da, db, algo=_algo_id(algo))
+    import fast_sequential_scan_b200 as pkg
+    pkg.check_status()
+    return h, da, db
+
+
+def assert_parity(got, ref, tol, what):
+    r = oracle.mixed_error_ratio(got, ref, tol)
+    assert r <= 1.0, f"{what}: max |x-ref|/(tol+tol|ref|) = {r:.3f} at tol {tol}"
+
+
+@pytest.mark.parametrize("algo", ALGOS)
+@pytest.mark.parametrize("name", golden_cases())
+def test_golden_vectors(name, algo):
+    z = load_golden(name)
+    bf16 = str(z["io"]) == "bf16"
+    dt = torch.bfloat16 if bf16 else torch.float32
+    a, b, g = (torch.from_numpy(z[k]).to(dt).cuda() for k in ("alpha", "beta", "grad"))
+    h, da, db = run_native(a, b, g, algo)
+    tol = BF16_TOL if bf16 else F32_TOL
+    assert_parity(h, torch.from_numpy(z["h"]), tol, "h")
+    # gradients are defined from the SAVED h (rounded for bf16): compare with the oracle's
+    # backward on that h, and -- looser chain -- with the golden autograd values
+    h_ref, da_ref, db_ref = oracle.reference_values(a, b, g)
+    assert_parity(db, db_ref, tol, "dbeta")
+    assert_parity(da, da_ref, tol, "dalpha")
+    assert_parity(db, torch.from_numpy(z["dbeta"]), tol, "dbeta(golden)")
+    assert_parity(da, torch.from_numpy(z["dalpha"]), tol, "dalpha(golden)")
+    assert not da[:, 0].any(), "dalpha_0 must be exactly 0"
+
+
+@pytest.mark.parametrize("algo", ALGOS)
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(1, 1, 8), (2, 2, 8), (3, 3, 16), (2, 5, 24), (1, 17, 7), (2, 33, 13),
+                                   (2, 129, 1000), (1, 300, 72), (3, 64, 520), (2, 65, 64), (1, 1025, 8)])
+def test_edge_shapes(shape, dtype, algo):
+    dt = torch.float32 if dtype == "f32" else torch.bfloat16
+    gen = torch.Generator().manual_seed(hash(shape) % 1000)
+    a = torch.sigmoid(torch.randn(shape, generator=gen)).to(dt).cuda()
+    b = torch.randn(shape, generator=gen).to(dt).cuda()
+    g = torch.randn(shape, generator=gen).to(dt).cuda()
+    h, da, db = run_native(a, b, g, algo)
+    tol = F32_TOL if dtype == "f32" else BF16_TOL
+    h_ref, _, _ = oracle.reference_values(a, b, None)
+    assert_parity(h, h_ref, tol, "h")
+    # gradients against the oracle's backward run on the h the kernel saved
+    da_ref, db_ref = oracle.scan_backward_f32(a.float().cpu().numpy(), h.float().cpu().numpy(),
+                                              g.float().cpu().numpy())
+    assert_parity(db, torch.from_numpy(db_ref), tol, "dbeta")
+    assert_parity(da, torch.from_numpy(da_ref), tol, "dalpha")
+
+
+def test_empty_inputs():
+    pkg, native, _ = _mods()
+    for shape in [(0, 4, 8), (2, 0, 8), (2, 4, 0)]:
+        a = torch.empty(shape, dtype=torch.bfloat16, device="cuda")
+        assert native.scan_forward_half(a, a).shape == shape
+        da, db = native.scan_backward_half(a, a, a)
+        assert da.shape == shape and db.shape == shape
+
+
+@pytest.mark.parametrize("algo", ALGOS)
+def test_strided_views_channel_shards(algo):
+    """Channel-sharded views of a wider tensor (row stride > D) are taken without a copy."""
+    gen = torch.Generator().manual_seed(4)
+    full = (2, 200, 256)
+    a = torch.sigmoid(torch.randn(full, generator=gen)).bfloat16().cuda()
+    b = torch.randn(full, generator=gen).bfloat16().cuda()
+    g = torch.randn(full, generator=gen).bfloat16().cuda()
+    h_full, da_full, db_full = run_native(a, b, g, algo)
+    for lo, hi in [(0, 128), (128, 256), (64, 72)]:
+        h, da, db = run_native(a[..., lo:hi], b[..., lo:hi], g[..., lo:hi], algo)
+        assert torch.equal(h, h_full[..., lo:hi])
+        assert torch.equal(da, da_full[..., lo:hi]) and torch.equal(db, db_full[..., lo:hi])
+
+
+# ---- the reference's own test grid and metric (sequential_scan/test_scan_cuda.py:27-124) ----
+@pytest.mark.parametrize("bs", [2, 9])
+@pytest.mark.parametrize("sq", [128, 1024])
+@pytest.mark.parametrize("d", [512, 768, 1024])
+def test_reference_grid_single(bs, sq, d):
+    pkg, _, _ = _mods()
+    torch.manual_seed(0)
+    alpha = torch.randn(bs, sq, d, device="cuda", requires_grad=True)
+    beta = torch.randn(bs, sq, d, device="cuda", requires_grad=True)
+    out = pkg.scan_cu_single(alpha, beta)
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    h_ref, da_ref, db_ref = oracle.reference_values(alpha, beta, dy)
+    for got, ref, what in ((out, h_ref, "h"), (alpha.grad, da_ref, "dalpha"), (beta.grad, db_ref, "dbeta")):
+        err = oracle.relative_l2(got, ref)
+        assert oracle.digits(err) >= 7, (what, err)      # SINGLE_TOL = 7 digits
+
+
+@pytest.mark.parametrize("bs", [1, 7, 15])
+@pytest.mark.parametrize("sq", [128, 512])
+@pytest.mark.parametrize("d", [512, 768, 1024])
+def test_reference_grid_half(bs, sq, d):
+    pkg, _, _ = _mods()
+    torch.manual_seed(0)
+    alpha = torch.randn(bs, sq, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    beta = torch.randn(bs, sq, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = pkg.scan_cu(alpha, beta)
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    a, b, g = alpha.detach(), beta.detach(), dy
+    # the reference compares with its loop run IN bf16; the fp32 scan is the stricter target
+    h_ref, _, _ = oracle.reference_values(a, b, None)
+    da_ref, db_ref = oracle.scan_backward_f32(a.float().cpu().numpy(), out.detach().float().cpu().numpy(),
+                                              g.float().cpu().numpy())
+    for got, ref, what in ((out, h_ref, "h"), (alpha.grad, torch.from_numpy(da_ref), "dalpha"),
+                           (beta.grad, torch.from_numpy(db_ref), "dbeta")):
+        err = oracle.relative_l2(got, ref)
+        assert oracle.digits(err) >= 2, (what, err)      # BFLOAT16_TOL = 2 digits
+
+
+# ---- benchmark configurations at full size ----
+def _subset_check(w, a, b, g, h, da, db, tol, channels=48):
+    """Oracle on a channel subset (channels are independent), all rows, all batches."""
+    D = a.shape[-1]
+    idx = torch.linspace(0, D - 1, channels).long().unique().cuda()
+    sub = lambda t: t.index_select(2, idx).contiguous()
+    h_ref, _, _ = oracle.reference_values(sub(a), sub(b), None)
+    assert_parity(sub(h), h_ref, tol, f"{w.name} h")
+    da_ref, db_ref = oracle.scan_backward_f32(sub(a).float().cpu().numpy(), sub(h).float().cpu().numpy(),
+                                              sub(g).float().cpu().numpy())
+    assert_parity(sub(db), torch.from_numpy(db_ref), tol, f"{w.name} dbeta")
+    assert_parity(sub(da), torch.from_numpy(da_ref), tol, f"{w.name} dalpha")
+
+
+@pytest.mark.parametrize("algo", ["chunked", "auto"])
+@pytest.mark.parametrize("cfg", ["c1", "c2", "c3_512", "c3_1000", "c3_3000", "c3_4096", "c3_8192",
+                                 "c4_bf16", "c4_f32"])
+def test_benchmark_configurations(cfg, algo):
+    from fast_sequential_scan_b200.workloads import CONFIGS, make_inputs
+    w = CONFIGS[cfg]
+    a, b, g = make_inputs(w, device="cuda", seed=0)
+    h, da, db = run_native(a, b, g, algo)
+    tol = BF16_TOL if w.dtype == "bf16" else F32_TOL
+    _subset_check(w, a, b, g, h, da, db, tol)
+    # size-independent property: the scan is linear in beta for fixed alpha
+    h2 = torch.empty_like(h)
+    _, native, _ = _mods()
+    native.forward_into(a, (b.float() * 2).to(b.dtype), h2, algo=_algo_id(algo))
+    lin = oracle.mixed_error_ratio(h2, h.float() * 2, tol * 2)
+    assert lin <= 1.0, f"linearity in beta violated: {lin}"
+
+
+def test_c1_full_against_oracle_through_autograd():
+    """Configuration 1 end to end through the public autograd API, every element checked."""
+    pkg, _, _ = _mods()
+    from fast_sequential_scan_b200.workloads import CONFIGS, make_inputs
+    a, b, g = make_inputs(CONFIGS["c1"], device="cuda", seed=0)
+    a.requires_grad_(True); b.requires_grad_(True)
+    h = pkg.scan_cu(a, b)
+    h.backward(g)
+    h_ref, da_ref, db_ref = oracle.reference_values(a, b, g)
+    assert_parity(h, h_ref, BF16_TOL, "h")
+    assert_parity(b.grad, db_ref, BF16_TOL, "dbeta")
+    assert_parity(a.grad, da_ref, BF16_TOL, "dalpha")
+    # and bit-level agreement with the exact bf16-storage model, up to rare one-ulp flips
+    hb, _, _ = oracle.bf16_storage_values(a, b, None)
+    mism = (hb.cuda().view(torch.int16) != h.detach().view(torch.int16)).float().mean().item()
+    assert mism < 0.02, f"{mism:.4f} of h differs from the exact bf16-storage scan"
+
+
+def test_autocast_casts_to_bf16_and_fp32_api_keeps_fp32():
+    pkg, _, _ = _mods()
+    a = torch.rand(2, 64, 64, device="cuda", requires_grad=True)
+    b = torch.randn(2, 64, 64, device="cuda", requires_grad=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        h = pkg.scan_cu(a, b)
+    assert h.dtype == torch.bfloat16
+    h.float().sum().backward()
+    assert a.grad.dtype == torch.float32 and b.grad.shape == b.shape
+    h32 = pkg.scan_cu_single(a.detach(), b.detach())
+    assert h32.dtype == torch.float32
+
+
+def test_wrong_arguments_raise():
+    pkg, native, _ = _mods()
+    a = torch.zeros(2, 4, 8, device="cuda")
+    with pytest.raises(RuntimeError):
+        native.scan_forward_half(a, a)                       # fp32 into the bf16 entry point
+    with pytest.raises(RuntimeError):
+        native.scan_forward(a, a[:, :2])                     # shape mismatch
+    with pytest.raises(RuntimeError):
+        native.scan_forward(a.cpu(), a.cpu())                # no CPU path
+    with pytest.raises(RuntimeError):
+        native.scan_forward(a[0], a[0])                      # not 3-D
+
+
+def test_non_default_stream_and_saved_output_untouched():
+    """Launches follow torch's current stream; backward leaves the saved h intact."""
+    pkg, _, _ = _mods()
+    s = torch.cuda.Stream()
+    a = torch.rand(2, 256, 128, device="cuda").bfloat16().requires_grad_(True)
+    b = torch.randn(2, 256, 128, device="cuda").bfloat16().requires_grad_(True)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        h = pkg.scan_cu(a, b)
+        keep = h.detach().clone()
+        h.backward(torch.ones_like(h))
+    s.synchronize()
+    assert torch.equal(h.detach(), keep)
+    h_ref, _, _ = oracle.reference_values(a, b, None)
+    assert_parity(h, h_ref, BF16_TOL, "h on side stream")

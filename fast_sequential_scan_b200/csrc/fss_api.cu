@@ -47,9 +47,6 @@ struct DeviceGuard {
     ~DeviceGuard() { if (switched) cudaSetDevice(prev); }
 };
 
-// Workspace: a 256-byte header the look-back kernels keep their epoch in, then algorithm scratch.
-constexpr size_t kHeaderBytes = 256;
-
 static int check_ctx(const fss_scan_ctx *ctx) {
     if (!ctx) return FSS_E_NULL;
     if (ctx->struct_bytes != sizeof(fss_scan_ctx)) return FSS_E_ARGS;
@@ -89,7 +86,7 @@ static int chunked_forward(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64
     using namespace chunked;
     cudaStream_t stream = (cudaStream_t)ctx->stream;
     const Geometry g = make_geometry(B, Tn, D, V);
-    float *wsP = reinterpret_cast<float *>((char *)ctx->workspace + kHeaderBytes);
+    float *wsP = reinterpret_cast<float *>(plan_workspace(ctx->workspace, ctx->workspace_bytes).floats);
     float *wsC = reinterpret_cast<float *>((char *)wsP + align_up((size_t)(B * g.S * D) * sizeof(float), 256));
     const bool cont = ctx->flags & FSS_FLAG_CONTINUATION;
     const unsigned blocks = (unsigned)(g.vblocks * g.S * B);
@@ -113,7 +110,7 @@ static int chunked_backward(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int6
     using namespace chunked;
     cudaStream_t stream = (cudaStream_t)ctx->stream;
     const Geometry g = make_geometry(B, Tn, D, V);
-    float *wsP = reinterpret_cast<float *>((char *)ctx->workspace + kHeaderBytes);
+    float *wsP = reinterpret_cast<float *>(plan_workspace(ctx->workspace, ctx->workspace_bytes).floats);
     float *wsC = reinterpret_cast<float *>((char *)wsP + align_up((size_t)(B * g.S * D) * sizeof(float), 256));
     const bool cont = ctx->flags & FSS_FLAG_CONTINUATION;
     const unsigned blocks = (unsigned)(g.vblocks * g.S * B);
@@ -142,7 +139,7 @@ static int forward_typed(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t 
         algo = ok ? FSS_ALGO_LOOKBACK : FSS_ALGO_CHUNKED;
     }
     if (algo == FSS_ALGO_LOOKBACK)
-        return lookback::forward<T>(ctx, (char *)ctx->workspace, kHeaderBytes, B, Tn, D, alpha, beta, h, st);
+        return lookback::forward<T>(ctx, plan_workspace(ctx->workspace, ctx->workspace_bytes), B, Tn, D, alpha, beta, h, st, &g_cuda_error);
     constexpr int V = VecWidth<T>::value;
     if (chunked::vector_ok<T>(D, {alpha, beta, h}))
         return chunked_forward<T, V>(ctx, B, Tn, D, alpha, beta, h, st);
@@ -161,8 +158,8 @@ static int backward_typed(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t
         algo = ok ? FSS_ALGO_LOOKBACK : FSS_ALGO_CHUNKED;
     }
     if (algo == FSS_ALGO_LOOKBACK)
-        return lookback::backward<T>(ctx, (char *)ctx->workspace, kHeaderBytes, B, Tn, D, alpha, h, grad,
-                                     dalpha, dbeta, st);
+        return lookback::backward<T>(ctx, plan_workspace(ctx->workspace, ctx->workspace_bytes), B, Tn, D, alpha, h, grad,
+                                     dalpha, dbeta, st, &g_cuda_error);
     constexpr int V = VecWidth<T>::value;
     if (chunked::vector_ok<T>(D, {alpha, h, grad, dalpha, dbeta}))
         return chunked_backward<T, V>(ctx, B, Tn, D, alpha, h, grad, dalpha, dbeta, st);
@@ -198,10 +195,10 @@ FSS_API const char *fss_strerror(int code) {
 FSS_API const char *fss_last_cuda_error(void) { return g_cuda_error.c_str(); }
 
 FSS_API size_t fss_workspace_bytes(int64_t B, int64_t T, int64_t D, int dtype) {
-    if (B <= 0 || T <= 0 || D <= 0) return kHeaderBytes;
+    if (B <= 0 || T <= 0 || D <= 0) return workspace_total(0);
     size_t a = chunked::workspace_bytes(B, T, D);
     size_t b = lookback::workspace_bytes(B, T, D, dtype);
-    return kHeaderBytes + (a > b ? a : b);
+    return workspace_total(a > b ? a : b);
 }
 
 FSS_API int fss_workspace_init(void *workspace, size_t bytes, void *stream) {

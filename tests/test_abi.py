@@ -56,7 +56,7 @@ def test_error_strings_and_argument_checks_need_no_device():
     ok = _lib.View(ctypes.addressof(buf), 32, 8)
     assert call(ctx, 2, 4, 8, ok, ok, ok) == -4                    # no workspace
     assert L.fss_workspace_bytes(8, 2048, 1024, 0) > 256
-    assert L.fss_workspace_bytes(0, 0, 0, 0) == 256
+    assert L.fss_workspace_bytes(0, 0, 0, 0) >= 256
     assert L.fss_block_rows(0, 1, 65536, 4096, 1) >= 1
 
 

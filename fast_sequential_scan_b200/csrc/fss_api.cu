@@ -27,21 +27,25 @@ static int cuda_fail(cudaError_t e, const char *what, int code = FSS_E_LAUNCH) {
         if (e_ != cudaSuccess) return cuda_fail(e_, what);        \
     } while (0)
 
-// Makes ctx->device current for the duration of a call and puts the previous one back.
+// Makes ctx->device current for the duration of a call and puts the previous one back.  The
+// first call of a thread always binds the device, so that driver entry points used later (TMA
+// descriptor encoding) find a current context even on threads that never touched CUDA through
+// this library (autograd worker threads, for instance).
 struct DeviceGuard {
     int prev = -1;
     bool switched = false;
     int error = FSS_OK;
     int device = -1;
     explicit DeviceGuard(int want) {
+        static thread_local int bound = -1;
         cudaError_t e = cudaGetDevice(&prev);
         if (e != cudaSuccess) { error = cuda_fail(e, "cudaGetDevice", FSS_E_DEVICE); return; }
-        device = prev;
-        if (want >= 0 && want != prev) {
-            e = cudaSetDevice(want);
+        device = want >= 0 ? want : prev;
+        if (device != prev || bound != device) {
+            e = cudaSetDevice(device);
             if (e != cudaSuccess) { error = cuda_fail(e, "cudaSetDevice", FSS_E_DEVICE); return; }
-            switched = true;
-            device = want;
+            bound = device;
+            switched = device != prev;
         }
     }
     ~DeviceGuard() { if (switched) cudaSetDevice(prev); }

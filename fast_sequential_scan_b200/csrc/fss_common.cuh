@@ -118,28 +118,26 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Workspace plan.  [256-byte header | flag words | float scratch].  The split depends only on the
-// workspace's total size, so for one allocation the flag words always sit at the same place and
-// are never overwritten with float data (a stale float could otherwise pass for a flag).
+// Workspace plan: [256-byte header | descriptor packets | float scratch].  The split depends only
+// on the workspace's total size, so for one allocation the packet area always sits at the same
+// place and only ever holds 16-byte packets whose fourth word is a tag: a stale float can never
+// pass for a tag of the current launch.
 constexpr size_t kWsHeaderBytes = 256;
 struct WsPlan {
-    char *hdr, *flags, *floats;
-    size_t flag_bytes, float_bytes;
+    char *hdr, *packets, *floats;
+    size_t packet_bytes, float_bytes;
 };
 inline WsPlan plan_workspace(void *ws, size_t bytes) {
     WsPlan w{};
-    if (bytes < kWsHeaderBytes + 512) return w;
+    if (bytes < kWsHeaderBytes + 1024) return w;
     w.hdr = static_cast<char *>(ws);
-    w.flag_bytes = align_up((bytes - kWsHeaderBytes) / 32, 256);
-    w.flags = w.hdr + kWsHeaderBytes;
-    w.floats = w.flags + w.flag_bytes;
-    w.float_bytes = bytes - kWsHeaderBytes - w.flag_bytes;
+    w.packet_bytes = (bytes - kWsHeaderBytes) / 2 / 256 * 256;
+    w.packets = w.hdr + kWsHeaderBytes;
+    w.floats = w.packets + w.packet_bytes;
+    w.float_bytes = bytes - kWsHeaderBytes - w.packet_bytes;
     return w;
 }
-// total size whose plan leaves at least `float_need` bytes of float scratch
-inline size_t workspace_total(size_t float_need) {
-    const size_t m = align_up((float_need + 512) / 31 * 32 + 1024, 256);
-    return kWsHeaderBytes + m;
-}
+// total size whose plan leaves at least `need` bytes in each of the two areas
+inline size_t workspace_total(size_t need) { return kWsHeaderBytes + 2 * align_up(need + 256, 256) + 1024; }
 
 }  // namespace fss

@@ -18,9 +18,13 @@
 //                             so the carry resolution below is off the critical path.
 //   look-back warp            folds the 8 warp summaries into the tile summary, resolves the
 //                             state entering the tile by decoupled look-back over the global
-//                             tile descriptors of its predecessors (aggregate / inclusive flags,
-//                             release/acquire at gpu scope), publishes its own, and hands every
-//                             consumer warp its entering state.
+//                             descriptors of its predecessors, hands every consumer warp its
+//                             entering state and publishes the tile's own descriptors.
+//                             A descriptor is a set of 16-byte packets {3 floats, tag}; each packet
+//                             is written and read with ONE 128-bit relaxed gpu-scope access, so a
+//                             packet whose tag carries this launch's epoch is complete by itself:
+//                             no flag word, no fence, one L2 round trip per look-back step, and
+//                             several predecessors can be read at once.
 // Every wait is bounded; a wait that runs out records a status, raises the abort flag that all
 // other waits poll, and the CTA drains its copies and leaves.
 #pragma once
@@ -43,13 +47,17 @@ constexpr int kRowBytes = 256;                // bytes of one tile row
 constexpr int kLaneBytes = 8;
 constexpr int kTileBytes = kTc * kRowBytes;   // 16 KiB per tensor and stage
 constexpr int kProducerWarp = kW;
-constexpr int kLookbackWarp = kW + 1;
-constexpr int kThreads = (kW + 2) * 32;
+constexpr int kLookbackWarp0 = kW + 1;        // first of the look-back warps
+constexpr int kLookbackWarps = 2;
+constexpr int kGens = 4;                      // generations of summary buffers (units in flight)
+constexpr int kLead = 2;                      // pass 1 runs this many units ahead of pass 2
+constexpr int kThreads = (kW + 1 + kLookbackWarps) * 32;
 constexpr int kStagesFwd = 6;                 // 6 x 32 KiB
 constexpr int kStagesBwd = 4;                 // 4 x 48 KiB
 constexpr uint32_t kMaxSpins = 1u << 21;      // per wait; ~a second before giving up
 
 constexpr uint32_t kStateAggregate = 1, kStateInclusive = 2;
+constexpr int kWindow = 4;                    // predecessors inspected per look-back round trip
 
 template <typename T> struct Cfg {
     static constexpr int V = kLaneBytes / (int)sizeof(T);   // channels per lane
@@ -69,8 +77,7 @@ struct Params {
     int64_t ncols;    // B * ncg
     int64_t S;        // row blocks per column
     int64_t ntiles;
-    uint32_t *flags;  // [ntiles]
-    float *desc;      // [ntiles][4][Dc]: aggregate P, aggregate C, inclusive C, inclusive P
+    uint4 *packets;   // [ntiles][packets per tile][32 lanes]
     Header *hdr;
     int32_t *status;
     const float *state_in;   // forward h_in / backward u_in, [B, D] or null
@@ -79,6 +86,8 @@ struct Params {
     float *block_prod;       // [B, S, D]
     const float *h_prev;     // backward only
     int continuation;
+    int64_t grid;            // CTAs of the launch, and grid = grid_q * ncols + grid_r
+    int32_t grid_q, grid_r;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -123,62 +132,83 @@ __device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commi
 __device__ __forceinline__ void tma_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-__device__ __forceinline__ uint32_t ld_acquire(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ uint32_t ld_volatile(const uint32_t *p) {
     return *reinterpret_cast<const volatile uint32_t *>(p);
 }
 
+// 16-byte descriptor packets: three floats and a tag, moved as one 128-bit access
+__device__ __forceinline__ void st_packet(uint4 *p, float x, float y, float z, uint32_t tag) {
+    const unsigned long long lo = (unsigned long long)__float_as_uint(x) | ((unsigned long long)__float_as_uint(y) << 32);
+    const unsigned long long hi = (unsigned long long)__float_as_uint(z) | ((unsigned long long)tag << 32);
+    asm volatile("{\n\t.reg .b128 t;\n\tmov.b128 t, {%1, %2};\n\tst.relaxed.gpu.global.b128 [%0], t;\n\t}"
+                 ::"l"(p), "l"(lo), "l"(hi) : "memory");
+}
+__device__ __forceinline__ void ld_packet(const uint4 *p, float &x, float &y, float &z, uint32_t &tag) {
+    unsigned long long lo, hi;
+    asm volatile("{\n\t.reg .b128 t;\n\tld.relaxed.gpu.global.b128 t, [%2];\n\tmov.b128 {%0, %1}, t;\n\t}"
+                 : "=l"(lo), "=l"(hi) : "l"(p) : "memory");
+    x = __uint_as_float((uint32_t)lo); y = __uint_as_float((uint32_t)(lo >> 32));
+    z = __uint_as_float((uint32_t)hi); tag = (uint32_t)(hi >> 32);
+}
+// N floats as ceil(N/3) packets, packet j of a tile's group at p[j*32]
+template <int N> struct PacketGroup {
+    static constexpr int kPackets = (N + 2) / 3;
+    static __device__ __forceinline__ void store(uint4 *p, const float (&v)[N], uint32_t tag) {
+#pragma unroll
+        for (int j = 0; j < kPackets; ++j) {
+            const float x = v[3 * j];
+            const float y = (3 * j + 1 < N) ? v[3 * j + 1] : 0.0f;
+            const float z = (3 * j + 2 < N) ? v[3 * j + 2] : 0.0f;
+            st_packet(p + j * 32, x, y, z, tag);
+        }
+    }
+    // returns true when every packet of the group carries `tag`
+    static __device__ __forceinline__ bool load(const uint4 *p, float (&v)[N], uint32_t tag) {
+        bool ok = true;
+#pragma unroll
+        for (int j = 0; j < kPackets; ++j) {
+            float x, y, z; uint32_t t;
+            ld_packet(p + j * 32, x, y, z, t);
+            v[3 * j] = x;
+            if (3 * j + 1 < N) v[3 * j + 1] = y;
+            if (3 * j + 2 < N) v[3 * j + 2] = z;
+            ok &= (t == tag);
+        }
+        return ok;
+    }
+};
+
 // ------------------------------------------------------------------ 8-byte lane fragments
+// What one lane owns of a tile row: 8 bytes = 4 bf16 or 2 fp32 channels.
+__device__ __forceinline__ float vec_get(const float4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+__device__ __forceinline__ float vec_get(const float2 &v, int i) { return i == 0 ? v.x : v.y; }
+__device__ __forceinline__ void vec_set(float4 &v, int i, float f) { if (i == 0) v.x = f; else if (i == 1) v.y = f; else if (i == 2) v.z = f; else v.w = f; }
+__device__ __forceinline__ void vec_set(float2 &v, int i, float f) { if (i == 0) v.x = f; else v.y = f; }
+
 template <typename T> struct Lane;
 template <> struct Lane<bf16> {
     static constexpr int V = 4;
-    static __device__ __forceinline__ void load(uint32_t addr, float (&x)[4]) {
-        uint32_t w0, w1;
-        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1) : "r"(addr));
-        x[0] = __uint_as_float(w0 << 16); x[1] = __uint_as_float(w0 & 0xffff0000u);
-        x[2] = __uint_as_float(w1 << 16); x[3] = __uint_as_float(w1 & 0xffff0000u);
+    using Raw = uint2;
+    using VecF = float4;
+    static __device__ __forceinline__ Raw zero() { return make_uint2(0u, 0u); }
+    static __device__ __forceinline__ void unpack(const Raw &r, float (&x)[4]) {
+        x[0] = __uint_as_float(r.x << 16); x[1] = __uint_as_float(r.x & 0xffff0000u);
+        x[2] = __uint_as_float(r.y << 16); x[3] = __uint_as_float(r.y & 0xffff0000u);
     }
-    static __device__ __forceinline__ void store(uint32_t addr, const float (&x)[4]) {
+    static __device__ __forceinline__ Raw pack(const float (&x)[4]) {
         __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]);
         __nv_bfloat162 hi = __floats2bfloat162_rn(x[2], x[3]);
-        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(*reinterpret_cast<uint32_t *>(&lo)),
-                     "r"(*reinterpret_cast<uint32_t *>(&hi)) : "memory");
+        return make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
     }
 };
 template <> struct Lane<float> {
     static constexpr int V = 2;
-    static __device__ __forceinline__ void load(uint32_t addr, float (&x)[2]) {
-        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(x[0]), "=f"(x[1]) : "r"(addr));
-    }
-    static __device__ __forceinline__ void store(uint32_t addr, const float (&x)[2]) {
-        asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(x[0]), "f"(x[1]) : "memory");
-    }
+    using Raw = float2;
+    using VecF = float2;
+    static __device__ __forceinline__ Raw zero() { return make_float2(0.0f, 0.0f); }
+    static __device__ __forceinline__ void unpack(const Raw &r, float (&x)[2]) { x[0] = r.x; x[1] = r.y; }
+    static __device__ __forceinline__ Raw pack(const float (&x)[2]) { return make_float2(x[0], x[1]); }
 };
-
-// V consecutive floats of a global fp32 vector (descriptor / state arrays), L2-coherent
-template <int V> __device__ __forceinline__ void ldg_vec(const float *p, float (&x)[V]) {
-    if constexpr (V == 4) {
-        const float4 r = __ldcg(reinterpret_cast<const float4 *>(p));
-        x[0] = r.x; x[1] = r.y; x[2] = r.z; x[3] = r.w;
-    } else {
-        const float2 r = __ldcg(reinterpret_cast<const float2 *>(p));
-        x[0] = r.x; x[1] = r.y;
-    }
-}
-template <int V> __device__ __forceinline__ void stg_vec(float *p, const float (&x)[V]) {
-    if constexpr (V == 4) {
-        __stcg(reinterpret_cast<float4 *>(p), make_float4(x[0], x[1], x[2], x[3]));
-    } else {
-        __stcg(reinterpret_cast<float2 *>(p), make_float2(x[0], x[1]));
-    }
-}
 
 // ------------------------------------------------------------------ bounded waits
 struct Ctl {
@@ -208,30 +238,39 @@ struct Ctl {
 // ------------------------------------------------------------------ shared-memory plan
 template <int kTensors, int kStages> struct Smem {
     static constexpr int kStageBytes = kTensors * kTileBytes;
-    static constexpr int kAggFloats = 2 * kW * 2 * 128;    // [2 generations][warp][P|C][<=128 channels]
-    static constexpr int kBarriers = 2 * kStages + 4;
-    static constexpr int kBytes = 128 /* alignment slack */ + kStages * kStageBytes + kAggFloats * 4 + kBarriers * 8 + 16;
+    // summaries: [generation][warp][P|C][lane] as 8-byte (fp32 x2) or 16-byte (fp32 x4) entries
+    static constexpr int kAggBytes = kGens * kW * 2 * 32 * 16;
+    static constexpr int kBarriers = 2 * kStages + 2 * kGens;
+    static constexpr int kBytes = 128 /* alignment slack */ + kStages * kStageBytes + kAggBytes + kBarriers * 8 + 16;
 };
 
-struct Tile { int64_t k, s, col, b, cg, row0; };
-
-template <bool kBackward>
-__device__ __forceinline__ Tile decode_tile(const Params &p, int64_t k) {
-    Tile t;
-    t.k = k;
-    t.s = k / p.ncols;
-    t.col = k - t.s * p.ncols;
-    t.b = t.col / p.ncg;
-    t.cg = t.col - t.b * p.ncg;
-    t.row0 = (kBackward ? (p.S - 1 - t.s) : t.s) * (int64_t)kTc;
-    return t;
-}
+// Position of a CTA's current work unit; advances by one grid stride without 64-bit division.
+struct TileIter {
+    int64_t k;        // linear tile number
+    int32_t s, col;   // row block in processing order, column (batch * channel group)
+    __device__ __forceinline__ void init(const Params &p, int64_t first) {
+        k = first;
+        s = (int32_t)(first / p.ncols);
+        col = (int32_t)(first - (int64_t)s * p.ncols);
+    }
+    __device__ __forceinline__ void advance(const Params &p) {
+        k += p.grid;
+        s += p.grid_q;
+        col += p.grid_r;
+        if (col >= (int32_t)p.ncols) { col -= (int32_t)p.ncols; s += 1; }
+    }
+    __device__ __forceinline__ int32_t batch(const Params &p) const { return col / (int32_t)p.ncg; }
+    __device__ __forceinline__ int32_t cgroup(const Params &p) const { return col % (int32_t)p.ncg; }
+    template <bool kBackward> __device__ __forceinline__ int32_t row0(const Params &p) const {
+        return (kBackward ? ((int32_t)p.S - 1 - s) : s) * kTc;
+    }
+};
 
 // ------------------------------------------------------------------ the kernel
 // Forward: tensors (alpha, beta) are loaded, h is stored from beta's stage slot.
 // Backward: (alpha, grad, h shifted one row down) are loaded; dbeta is stored from grad's slot,
 // dalpha from h's slot.
-template <typename T, bool kBackward>
+template <typename T, bool kBackward, bool kProd>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant__ CUtensorMap map_x,
             const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_out0,
@@ -241,32 +280,31 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     using SM = Smem<kTensors, kStages>;
     constexpr int V = Cfg<T>::V;
     constexpr int Dc = Cfg<T>::Dc;
+    using VecF = typename Lane<T>::VecF;          // V floats as one shared-memory word group
 
     // TMA tiles want 128-byte aligned shared addresses: align the dynamic window by hand
     extern __shared__ unsigned char smem_dyn[];
     unsigned char *smem_raw = smem_dyn + ((128u - (smem_u32(smem_dyn) & 127u)) & 127u);
     const uint32_t smem_base = smem_u32(smem_raw);
-    float *agg = reinterpret_cast<float *>(smem_raw + kStages * SM::kStageBytes);
-    const uint32_t agg_u32 = smem_base + kStages * SM::kStageBytes;
-    const uint32_t bars = agg_u32 + SM::kAggFloats * 4;
+    VecF *agg = reinterpret_cast<VecF *>(smem_raw + kStages * SM::kStageBytes);
+    const uint32_t bars = smem_base + kStages * SM::kStageBytes + SM::kAggBytes;
     volatile int *cta_abort = reinterpret_cast<volatile int *>(smem_raw + kStages * SM::kStageBytes +
-                                                               SM::kAggFloats * 4 + SM::kBarriers * 8);
+                                                               SM::kAggBytes + SM::kBarriers * 8);
     volatile uint32_t *epoch_s = reinterpret_cast<volatile uint32_t *>(const_cast<int *>(cta_abort) + 1);
     auto bar_full = [&](int s) { return bars + 8u * s; };
     auto bar_done = [&](int s) { return bars + 8u * (kStages + s); };
     auto bar_agg = [&](int g) { return bars + 8u * (2 * kStages + g); };
-    auto bar_carry = [&](int g) { return bars + 8u * (2 * kStages + 2 + g); };
-    // agg[g][w][0|1][channel]
-    auto agg_off = [&](int g, int w, int which) { return ((g * kW + w) * 2 + which) * 128; };
+    auto bar_carry = [&](int g) { return bars + 8u * (2 * kStages + kGens + g); };
+    // agg[(g, w, P|C)][lane]
+    auto agg_at = [&](int g, int w, int which, int ln) -> VecF & { return agg[((g * kW + w) * 2 + which) * 32 + ln]; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t G = gridDim.x;
     const int64_t first = blockIdx.x;
-    const int64_t n_my = first < p.ntiles ? (p.ntiles - first + G - 1) / G : 0;
+    const int64_t n_my = first < p.ntiles ? (p.ntiles - first + p.grid - 1) / p.grid : 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_done(s), kW); }
-        for (int g = 0; g < 2; ++g) { mbar_init(bar_agg(g), kW); mbar_init(bar_carry(g), 1); }
+        for (int g = 0; g < kGens; ++g) { mbar_init(bar_agg(g), kW); mbar_init(bar_carry(g), 1); }
         *cta_abort = 0;
         *epoch_s = ld_volatile(&p.hdr->epoch) + 1u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -279,15 +317,18 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     if (warp == kProducerWarp) {
         // ============================================================ producer
         if (lane == 0) {
+            TileIter ld_it, st_it;
+            ld_it.init(p, first);
+            st_it.init(p, first);
             auto issue = [&](int64_t i) {
-                const Tile t = decode_tile<kBackward>(p, first + i * G);
                 const int st = (int)(i % kStages);
                 const uint32_t base = smem_base + st * SM::kStageBytes;
-                const int32_t c0 = (int32_t)(t.cg * Dc), c1 = (int32_t)t.row0, c2 = (int32_t)t.b;
+                const int32_t c0 = ld_it.cgroup(p) * Dc, c1 = ld_it.template row0<kBackward>(p), c2 = ld_it.batch(p);
                 mbar_arrive_expect_tx(bar_full(st), SM::kStageBytes);
                 tma_load_3d(base, &map_alpha, bar_full(st), c0, c1, c2);
                 tma_load_3d(base + kTileBytes, &map_x, bar_full(st), c0, c1, c2);
                 if (kBackward) tma_load_3d(base + 2 * kTileBytes, &map_h, bar_full(st), c0, c1 - 1, c2);
+                ld_it.advance(p);
             };
             int64_t issued = 0;
             for (; issued < n_my && issued < kStages; ++issued) issue(issued);
@@ -295,9 +336,9 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             for (; i < n_my; ++i) {
                 const int st = (int)(i % kStages);
                 if (!ctl.wait(bar_done(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
-                const Tile t = decode_tile<kBackward>(p, first + i * G);
                 const uint32_t base = smem_base + st * SM::kStageBytes;
-                const int32_t c0 = (int32_t)(t.cg * Dc), c1 = (int32_t)t.row0, c2 = (int32_t)t.b;
+                const int32_t c0 = st_it.cgroup(p) * Dc, c1 = st_it.template row0<kBackward>(p), c2 = st_it.batch(p);
+                st_it.advance(p);
                 if (!kBackward) {
                     tma_store_3d(&map_out0, base + kTileBytes, c0, c1, c2);          // h
                 } else {
@@ -321,140 +362,207 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             }
             tma_wait_all();
         }
-    } else if (warp == kLookbackWarp) {
+    } else if (warp >= kLookbackWarp0) {
         // ============================================================ look-back
+        // kLookbackWarps warps share the work units round-robin, so several carry resolutions
+        // (each a few L2 round trips) are in flight per CTA.
+        constexpr int NI = kProd ? 2 * V : V;          // floats of an inclusive descriptor
+        using AggPk = PacketGroup<2 * V>;              // (P, C) of the tile scanned from zero
+        using IncPk = PacketGroup<NI>;                 // state after the tile (and product up to it)
+        constexpr int kTilePackets = (AggPk::kPackets + IncPk::kPackets) * 32;
+        const uint32_t tag_agg = (epoch << 2) | kStateAggregate;
+        const uint32_t tag_inc = (epoch << 2) | kStateInclusive;
+        const int lb = warp - kLookbackWarp0;
         const int ch = lane * V;    // first channel of this lane inside the tile
-        for (int64_t i = 0; i < n_my; ++i) {
-            const Tile t = decode_tile<kBackward>(p, first + i * G);
-            const int g = (int)(i & 1);
-            const int64_t dch = t.cg * Dc + ch;          // channel in the tensor
+        auto agg_packets = [&](int64_t k) { return p.packets + k * kTilePackets + lane; };
+        auto inc_packets = [&](int64_t k) { return p.packets + k * kTilePackets + AggPk::kPackets * 32 + lane; };
+
+        TileIter it;
+        it.init(p, first);
+        for (int j = 0; j < lb; ++j) it.advance(p);
+
+        // the predecessor's inclusive descriptor is fetched one of this warp's units ahead of its
+        // use and, if it was not there yet, once more when the unit starts
+        float pre[NI];
+        bool pre_ok = false;
+        {
+            if (lb < n_my && it.s > 0) pre_ok = IncPk::load(inc_packets(it.k - p.ncols), pre, tag_inc);
+        }
+
+        for (int64_t i = lb; i < n_my; i += kLookbackWarps) {
+            const int g = (int)(i % kGens);
+            const int64_t k = it.k;
+            const int32_t s = it.s, b = it.batch(p);
+            const int64_t dch = (int64_t)it.cgroup(p) * Dc + ch;     // channel in the tensor
             const bool ch_ok = dch < p.D;
-            float *my_desc = p.desc + t.k * (4 * Dc) + ch;
+            for (int j = 0; j < kLookbackWarps; ++j) it.advance(p);  // -> this warp's next unit
 
-            // early, non-blocking peek at the predecessor (overlaps the consumers' pass 1)
-            // (every lane issues its own acquire load; the decision is taken by vote so that the
-            // warp stays converged even if lanes were to observe the flag at different moments)
-            uint32_t peek = 0;
-            if (t.s > 0) peek = ld_acquire(p.flags + (t.k - p.ncols));
-            float pre_c[V], pre_p[V];
-            const bool peek_hit = __all_sync(0xffffffffu, (t.s > 0) && (peek == ((epoch << 2) | kStateInclusive)));
-            if (peek_hit) {
-                const float *pd = p.desc + (t.k - p.ncols) * (4 * Dc) + ch;
-                ldg_vec<V>(pd + 2 * Dc, pre_c);
-                ldg_vec<V>(pd + 3 * Dc, pre_p);
-            }
+            float cur[NI];
+#pragma unroll
+            for (int v = 0; v < NI; ++v) cur[v] = pre[v];
+            bool hit = __all_sync(0xffffffffu, pre_ok);
+            float late[NI];
+            bool late_ok = false;
+            if (s > 0 && !hit) late_ok = IncPk::load(inc_packets(k - p.ncols), late, tag_inc);
+            pre_ok = false;
+            if (i + kLookbackWarps < n_my && it.s > 0) pre_ok = IncPk::load(inc_packets(it.k - p.ncols), pre, tag_inc);
 
-            if (!ctl.wait(bar_agg(g), (uint32_t)((i >> 1) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
+            if (!ctl.wait(bar_agg(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
 
-            // fold the warp summaries in scan order; keep the exclusive prefixes for hand-out
-            float Pex[kW][V], Cex[kW][V], Pt[V], Ct[V];
+            // fold the warp summaries in scan order into the tile summary
+            float Pt[V], Ct[V];
 #pragma unroll
             for (int v = 0; v < V; ++v) { Pt[v] = 1.0f; Ct[v] = 0.0f; }
+            {
+                VecF aP[kW], aC[kW];
 #pragma unroll
-            for (int j = 0; j < kW; ++j) {
-                const int w = kBackward ? kW - 1 - j : j;
+                for (int w = 0; w < kW; ++w) { aP[w] = agg_at(g, w, 0, lane); aC[w] = agg_at(g, w, 1, lane); }
 #pragma unroll
-                for (int v = 0; v < V; ++v) {
-                    Pex[w][v] = Pt[v]; Cex[w][v] = Ct[v];
-                    const float pw = agg[agg_off(g, w, 0) + ch + v];
-                    const float cw = agg[agg_off(g, w, 1) + ch + v];
-                    Ct[v] = fmaf(pw, Ct[v], cw);
-                    Pt[v] *= pw;
+                for (int j = 0; j < kW; ++j) {
+                    const int w = kBackward ? kW - 1 - j : j;
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        Ct[v] = fmaf(vec_get(aP[w], v), Ct[v], vec_get(aC[w], v));
+                        Pt[v] *= vec_get(aP[w], v);
+                    }
                 }
             }
 
-            // ---- the state entering this tile, and the product of alpha before it
+            // ---- the state entering this tile (cin) and the product of alpha before it (pin)
             float cin[V], pin[V];
             bool ok = true;
-            if (t.s == 0) {
+            auto state0 = [&](int v) {
+                return (p.state_in && ch_ok) ? p.state_in[(int64_t)b * p.D + dch + v] : 0.0f;
+            };
+            if (s > 0 && !hit && __all_sync(0xffffffffu, late_ok)) {
+                hit = true;
 #pragma unroll
-                for (int v = 0; v < V; ++v) {
-                    cin[v] = (p.state_in && ch_ok) ? p.state_in[t.b * p.D + dch + v] : 0.0f;
-                    pin[v] = 1.0f;
-                }
-            } else if (peek_hit) {
+                for (int v = 0; v < NI; ++v) cur[v] = late[v];
+            }
+            if (s == 0) {
 #pragma unroll
-                for (int v = 0; v < V; ++v) { cin[v] = pre_c[v]; pin[v] = pre_p[v]; }
+                for (int v = 0; v < V; ++v) { cin[v] = state0(v); pin[v] = 1.0f; }
+            } else if (hit) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) { cin[v] = cur[v]; pin[v] = kProd ? cur[kProd ? V + v : v] : 1.0f; }
             } else {
-                // publish the aggregate so successors need not wait for this tile's own look-back
-                stg_vec<V>(my_desc, Pt);
-                stg_vec<V>(my_desc + Dc, Ct);
-                __syncwarp();
-                if (lane == 0) st_release(p.flags + t.k, (epoch << 2) | kStateAggregate);
-                float Pa[V], Ca[V];
+                // publish the summary first: successors can fold it without waiting for this
+                // tile's own look-back
+                {
+                    float pc[2 * V];
+#pragma unroll
+                    for (int v = 0; v < V; ++v) { pc[v] = Pt[v]; pc[V + v] = Ct[v]; }
+                    AggPk::store(agg_packets(k), pc, tag_agg);
+                }
+                float Pa[V], Ca[V];          // map of the tiles between the predecessor at q and this one
 #pragma unroll
                 for (int v = 0; v < V; ++v) { Pa[v] = 1.0f; Ca[v] = 0.0f; }
-                int64_t q = t.k - p.ncols;
-                while (true) {
-                    uint32_t f = 0;
-                    uint32_t it = 0;
-                    for (; it < kMaxSpins; ++it) {
-                        f = ld_acquire(p.flags + q);
-                        if (__all_sync(0xffffffffu, (f >> 2) == epoch && (f & 3u) != 0)) break;
-                        if ((it & 15u) == 15u && __any_sync(0xffffffffu, ctl.aborted())) { ok = false; break; }
-                        __nanosleep(40);
-                    }
-                    if (ok && it == kMaxSpins) { if (lane == 0) ctl.give_up(FSS_STATUS_LOOKBACK_TIMEOUT); ok = false; }
-                    if (!ok) break;
-                    const float *qd = p.desc + q * (4 * Dc) + ch;
-                    float x0[V], x1[V];
-                    // a tile that has ever shown "aggregate" keeps valid aggregate data, so a mixed
-                    // observation is handled as aggregate
-                    if (__all_sync(0xffffffffu, (f & 3u) == kStateInclusive)) {
-                        ldg_vec<V>(qd + 2 * Dc, x0);
-                        ldg_vec<V>(qd + 3 * Dc, x1);
+                int64_t q = k - p.ncols;
+                uint32_t spins = 0;
+                bool found = false;
+                while (!found) {
+                    // read up to kWindow predecessors in one round trip
+                    float inc[kWindow][NI], ag[kWindow][2 * V];
+                    bool inc_ok[kWindow], ag_ok[kWindow];
 #pragma unroll
-                        for (int v = 0; v < V; ++v) { cin[v] = fmaf(Pa[v], x0[v], Ca[v]); pin[v] = Pa[v] * x1[v]; }
-                        break;
-                    }
-                    ldg_vec<V>(qd, x0);          // aggregate P
-                    ldg_vec<V>(qd + Dc, x1);     // aggregate C
-#pragma unroll
-                    for (int v = 0; v < V; ++v) { Ca[v] = fmaf(Pa[v], x1[v], Ca[v]); Pa[v] *= x0[v]; }
-                    q -= p.ncols;
-                    if (q < 0) {
-#pragma unroll
-                        for (int v = 0; v < V; ++v) {
-                            const float s0 = (p.state_in && ch_ok) ? p.state_in[t.b * p.D + dch + v] : 0.0f;
-                            cin[v] = fmaf(Pa[v], s0, Ca[v]);
-                            pin[v] = Pa[v];
+                    for (int j = 0; j < kWindow; ++j) {
+                        const int64_t qj = q - j * p.ncols;
+                        inc_ok[j] = false; ag_ok[j] = false;
+                        if (qj >= 0) {
+                            inc_ok[j] = IncPk::load(inc_packets(qj), inc[j], tag_inc);
+                            ag_ok[j] = AggPk::load(agg_packets(qj), ag[j], tag_agg);
                         }
-                        break;
+                    }
+                    int adv = 0;          // predecessors folded in this round
+                    bool stop = false;
+#pragma unroll
+                    for (int j = 0; j < kWindow; ++j) {
+                        const int64_t qj = q - j * p.ncols;     // warp-uniform
+                        if (found || stop) {
+                            // nothing more to do in this round
+                        } else if (qj < 0) {
+                            stop = true;
+                        } else if (__all_sync(0xffffffffu, inc_ok[j])) {
+#pragma unroll
+                            for (int v = 0; v < V; ++v) {
+                                cin[v] = fmaf(Pa[v], inc[j][v], Ca[v]);
+                                pin[v] = kProd ? Pa[v] * inc[j][kProd ? V + v : v] : 1.0f;
+                            }
+                            found = true;
+                        } else if (__all_sync(0xffffffffu, ag_ok[j])) {
+#pragma unroll
+                            for (int v = 0; v < V; ++v) {
+                                Ca[v] = fmaf(Pa[v], ag[j][V + v], Ca[v]);
+                                Pa[v] *= ag[j][v];
+                            }
+                            adv = j + 1;
+                            if (qj - p.ncols < 0) {      // folded everything down to row block 0
+#pragma unroll
+                                for (int v = 0; v < V; ++v) { cin[v] = fmaf(Pa[v], state0(v), Ca[v]); pin[v] = Pa[v]; }
+                                found = true;
+                            }
+                        } else {
+                            stop = true;                 // not published yet: poll again from here
+                        }
+                    }
+                    if (found) break;
+                    q -= (int64_t)adv * p.ncols;
+                    if (adv == 0) {
+                        ++spins;
+                        if ((spins & 15u) == 0u && __any_sync(0xffffffffu, ctl.aborted())) { ok = false; break; }
+                        if (spins >= kMaxSpins) {
+                            if (lane == 0) ctl.give_up(FSS_STATUS_LOOKBACK_TIMEOUT);
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(32);
                     }
                 }
                 if (!ok) break;
             }
 
-            // ---- publish the inclusive state, then hand the consumers their entering states
-            float cinc[V], pinc[V];
+            // ---- hand every consumer warp the state entering its rows (into its P slot)
+            float run[V];
 #pragma unroll
-            for (int v = 0; v < V; ++v) { cinc[v] = fmaf(Pt[v], cin[v], Ct[v]); pinc[v] = Pt[v] * pin[v]; }
-            if (t.s + 1 < p.S) {
-                stg_vec<V>(my_desc + 2 * Dc, cinc);
-                stg_vec<V>(my_desc + 3 * Dc, pinc);
-                __syncwarp();
-                if (lane == 0) st_release(p.flags + t.k, (epoch << 2) | kStateInclusive);
-            }
+            for (int v = 0; v < V; ++v) run[v] = cin[v];
+            VecF aP[kW], aC[kW];
 #pragma unroll
-            for (int w = 0; w < kW; ++w) {
+            for (int w = 0; w < kW; ++w) { aP[w] = agg_at(g, w, 0, lane); aC[w] = agg_at(g, w, 1, lane); }
 #pragma unroll
-                for (int v = 0; v < V; ++v) agg[agg_off(g, w, 0) + ch + v] = fmaf(Pex[w][v], cin[v], Cex[w][v]);
+            for (int j = 0; j < kW; ++j) {
+                const int w = kBackward ? kW - 1 - j : j;
+                VecF hand;
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    vec_set(hand, v, run[v]);
+                    run[v] = fmaf(vec_get(aP[w], v), run[v], vec_get(aC[w], v));
+                }
+                agg_at(g, w, 0, lane) = hand;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_carry(g));
 
-            if (ch_ok) {
-                if (p.block_prod) {
-                    const int64_t blk = kBackward ? (p.S - 1 - t.s) : t.s;
-                    float *bp = p.block_prod + (t.b * p.S + blk) * p.D + dch;
+            // ---- publish the inclusive descriptor: state after this tile, product through it
+            float out[NI];
 #pragma unroll
-                    for (int v = 0; v < V; ++v) bp[v] = pinc[v];
+            for (int v = 0; v < V; ++v) {
+                out[v] = run[v];
+                if (kProd) out[kProd ? V + v : v] = Pt[v] * pin[v];
+            }
+            if (s + 1 < (int32_t)p.S) IncPk::store(inc_packets(k), out, tag_inc);
+
+            if (ch_ok) {
+                if (kProd && p.block_prod) {
+                    const int64_t blk = kBackward ? (p.S - 1 - s) : s;
+                    float *bp = p.block_prod + ((int64_t)b * p.S + blk) * p.D + dch;
+#pragma unroll
+                    for (int v = 0; v < V; ++v) bp[v] = out[kProd ? V + v : v];
                 }
-                if (t.s + 1 == p.S) {
+                if (s + 1 == (int32_t)p.S) {
 #pragma unroll
                     for (int v = 0; v < V; ++v) {
-                        if (p.state_out) p.state_out[t.b * p.D + dch + v] = cinc[v];
-                        if (p.prod_out) p.prod_out[t.b * p.D + dch + v] = pinc[v];
+                        if (p.state_out) p.state_out[(int64_t)b * p.D + dch + v] = out[v];
+                        if (kProd && p.prod_out) p.prod_out[(int64_t)b * p.D + dch + v] = out[kProd ? V + v : v];
                     }
                 }
             }
@@ -463,20 +571,28 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // ============================================================ consumers
         const uint32_t lane_off = (uint32_t)(warp * kR) * kRowBytes + (uint32_t)lane * kLaneBytes;
         const int ch = lane * V;
+        using Raw = typename Lane<T>::Raw;
+        auto tile_ptr = [&](int st, int tensor) {
+            return reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + tensor * kTileBytes + lane_off);
+        };
+        constexpr int kRowStride = kRowBytes / (int)sizeof(Raw);
+
+        TileIter it1, it2;     // positions of the next pass-1 unit and the next pass-2 unit
+        it1.init(p, first);
+        it2.init(p, first);
 
         auto pass1 = [&](int64_t i) -> bool {
-            const Tile t = decode_tile<kBackward>(p, first + i * G);
-            const int st = (int)(i % kStages), g = (int)(i & 1);
+            const int st = (int)(i % kStages), g = (int)(i % kGens);
+            const bool head = (it1.template row0<kBackward>(p) == 0) && (warp == 0) && !p.continuation;
+            it1.advance(p);
             if (!ctl.wait(bar_full(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) return false;
-            const uint32_t a_t = smem_base + st * SM::kStageBytes + lane_off;
-            const uint32_t x_t = a_t + kTileBytes;
+            Raw *a_t = tile_ptr(st, 0);
+            const Raw *x_t = tile_ptr(st, 1);
             // row 0 of the whole sequence: alpha_0 is not part of the recurrence
-            if (t.row0 == 0 && warp == 0 && !p.continuation) {
-                float z[V];
+            if (head) a_t[0] = Lane<T>::zero();
+            Raw ra[kR], rx[kR];
 #pragma unroll
-                for (int v = 0; v < V; ++v) z[v] = 0.0f;
-                Lane<T>::store(a_t, z);
-            }
+            for (int r = 0; r < kR; ++r) { ra[r] = a_t[r * kRowStride]; rx[r] = x_t[r * kRowStride]; }
             float P[V], C[V];
 #pragma unroll
             for (int v = 0; v < V; ++v) { P[v] = 1.0f; C[v] = 0.0f; }
@@ -484,8 +600,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             for (int j = 0; j < kR; ++j) {
                 const int r = kBackward ? kR - 1 - j : j;
                 float a[V], x[V];
-                Lane<T>::load(a_t + r * kRowBytes, a);
-                Lane<T>::load(x_t + r * kRowBytes, x);
+                Lane<T>::unpack(ra[r], a);
+                Lane<T>::unpack(rx[r], x);
 #pragma unroll
                 for (int v = 0; v < V; ++v) {
                     if (!kBackward) C[v] = fmaf(a[v], C[v], x[v]);
@@ -493,52 +609,66 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                     P[v] *= a[v];
                 }
             }
+            VecF vp, vc;
 #pragma unroll
-            for (int v = 0; v < V; ++v) {
-                agg[agg_off(g, warp, 0) + ch + v] = P[v];
-                agg[agg_off(g, warp, 1) + ch + v] = C[v];
-            }
+            for (int v = 0; v < V; ++v) { vec_set(vp, v, P[v]); vec_set(vc, v, C[v]); }
+            agg_at(g, warp, 0, lane) = vp;
+            agg_at(g, warp, 1, lane) = vc;
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_agg(g));
             return true;
         };
 
         auto pass2 = [&](int64_t i) -> bool {
-            const Tile t = decode_tile<kBackward>(p, first + i * G);
-            const int st = (int)(i % kStages), g = (int)(i & 1);
-            if (!ctl.wait(bar_carry(g), (uint32_t)((i >> 1) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) return false;
-            const uint32_t a_t = smem_base + st * SM::kStageBytes + lane_off;
-            const uint32_t x_t = a_t + kTileBytes;
-            float stv[V];
+            const int st = (int)(i % kStages), g = (int)(i % kGens);
+            const bool head = (it2.template row0<kBackward>(p) == 0) && (warp == 0);
+            const int32_t b = it2.batch(p);
+            const int64_t dch = (int64_t)it2.cgroup(p) * Dc + ch;
+            it2.advance(p);
+            Raw *x_t = tile_ptr(st, 1);
+            const Raw *a_t = tile_ptr(st, 0);
+            // the tile's data has been resident since pass 1: fetch it while the carry is resolved
+            Raw ra[kR], rx[kR];
 #pragma unroll
-            for (int v = 0; v < V; ++v) stv[v] = agg[agg_off(g, warp, 0) + ch + v];
+            for (int r = 0; r < kR; ++r) { ra[r] = a_t[r * kRowStride]; rx[r] = x_t[r * kRowStride]; }
             if (!kBackward) {
+                if (!ctl.wait(bar_carry(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) return false;
+                const VecF cv = agg_at(g, warp, 0, lane);
+                float stv[V];
+#pragma unroll
+                for (int v = 0; v < V; ++v) stv[v] = vec_get(cv, v);
 #pragma unroll
                 for (int r = 0; r < kR; ++r) {
                     float a[V], x[V];
-                    Lane<T>::load(a_t + r * kRowBytes, a);
-                    Lane<T>::load(x_t + r * kRowBytes, x);
+                    Lane<T>::unpack(ra[r], a);
+                    Lane<T>::unpack(rx[r], x);
 #pragma unroll
                     for (int v = 0; v < V; ++v) stv[v] = fmaf(a[v], stv[v], x[v]);
-                    Lane<T>::store(x_t + r * kRowBytes, stv);
+                    x_t[r * kRowStride] = Lane<T>::pack(stv);
                 }
             } else {
-                const uint32_t h_t = x_t + kTileBytes;
-                const bool head = (t.row0 == 0) && (warp == 0);
+                Raw *h_t = tile_ptr(st, 2);
+                Raw rh[kR];
+#pragma unroll
+                for (int r = 0; r < kR; ++r) rh[r] = h_t[r * kRowStride];
                 if (head && p.continuation && p.h_prev) {    // h_{-1} of a continued sequence
                     float hp[V];
-                    const int64_t dch = t.cg * Dc + ch;
 #pragma unroll
-                    for (int v = 0; v < V; ++v) hp[v] = (dch < p.D) ? p.h_prev[t.b * p.D + dch + v] : 0.0f;
-                    Lane<T>::store(h_t, hp);
+                    for (int v = 0; v < V; ++v) hp[v] = (dch < p.D) ? p.h_prev[(int64_t)b * p.D + dch + v] : 0.0f;
+                    rh[0] = Lane<T>::pack(hp);
                 }
+                if (!ctl.wait(bar_carry(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) return false;
+                const VecF cv = agg_at(g, warp, 0, lane);
+                float stv[V];
+#pragma unroll
+                for (int v = 0; v < V; ++v) stv[v] = vec_get(cv, v);
 #pragma unroll
                 for (int j = 0; j < kR; ++j) {
                     const int r = kR - 1 - j;
                     float a[V], x[V], hp[V], da[V], dh[V];
-                    Lane<T>::load(a_t + r * kRowBytes, a);
-                    Lane<T>::load(x_t + r * kRowBytes, x);
-                    Lane<T>::load(h_t + r * kRowBytes, hp);
+                    Lane<T>::unpack(ra[r], a);
+                    Lane<T>::unpack(rx[r], x);
+                    Lane<T>::unpack(rh[r], hp);
 #pragma unroll
                     for (int v = 0; v < V; ++v) {
                         dh[v] = x[v] + stv[v];
@@ -549,8 +679,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
 #pragma unroll
                         for (int v = 0; v < V; ++v) da[v] = 0.0f;
                     }
-                    Lane<T>::store(x_t + r * kRowBytes, dh);
-                    Lane<T>::store(h_t + r * kRowBytes, da);
+                    x_t[r * kRowStride] = Lane<T>::pack(dh);
+                    h_t[r * kRowStride] = Lane<T>::pack(da);
                 }
             }
             fence_proxy_async();      // make the in-place results visible to the TMA store
@@ -559,14 +689,16 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             return true;
         };
 
-        bool alive = n_my > 0 && pass1(0);
+        // pass 1 runs kLead units ahead of pass 2
+        bool alive = true;
+        for (int64_t j = 0; alive && j < kLead && j < n_my; ++j) alive = pass1(j);
         for (int64_t i = 0; alive && i < n_my; ++i) {
-            if (i + 1 < n_my) alive = pass1(i + 1);
+            if (i + kLead < n_my) alive = pass1(i + kLead);
             if (alive) alive = pass2(i);
         }
     }
 
-    // ---- leave: the last CTA advances the epoch, which invalidates every flag of this launch
+    // ---- leave: the last CTA advances the epoch, which invalidates every packet of this launch
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
@@ -585,11 +717,16 @@ inline int64_t block_rows(int, int64_t, int64_t, int64_t) { return kTc; }
 
 template <typename T> inline int64_t channel_groups(int64_t D) { return ceil_div(D, Cfg<T>::Dc); }
 
-// float scratch (tile descriptors); the flag words live in the workspace's flag area
+// bytes of descriptor packets for a problem (worst case: with products)
+template <typename T> constexpr int packets_per_tile(bool prod) {
+    return (PacketGroup<2 * Cfg<T>::V>::kPackets +
+            (prod ? PacketGroup<2 * Cfg<T>::V>::kPackets : PacketGroup<Cfg<T>::V>::kPackets)) * 32;
+}
 inline size_t workspace_bytes(int64_t B, int64_t T, int64_t D, int dtype) {
     const int Dc = dtype == FSS_DTYPE_BF16 ? Cfg<bf16>::Dc : Cfg<float>::Dc;
+    const int per_tile = dtype == FSS_DTYPE_BF16 ? packets_per_tile<bf16>(true) : packets_per_tile<float>(true);
     const int64_t ntiles = B * ceil_div(D, Dc) * ceil_div(T, kTc);
-    return (size_t)ntiles * 4 * Dc * sizeof(float);
+    return (size_t)ntiles * per_tile * 16;
 }
 
 // What TMA needs: 16-byte aligned bases and strides, extents that fit its 32-bit coordinates.
@@ -628,9 +765,9 @@ inline EncodeTiledFn encode_fn() {
 // 3-D map (channels, rows, batch) with a (Dc, kTc, 1) box; out-of-range elements read as zero
 // and are dropped on store.
 template <typename T>
-inline bool make_map(CUtensorMap *map, const fss_view *v, int64_t B, int64_t Tn, int64_t D) {
+inline bool make_map(CUtensorMap *map, const fss_view *v, int64_t B, int64_t Tn, int64_t D, std::string *err) {
     EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
+    if (!fn) { *err = "cuTensorMapEncodeTiled entry point not found"; return false; }
     const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Tn, (cuuint64_t)B};
     const int64_t sb = B > 1 ? v->stride_b : v->stride_t * Tn;
     const cuuint64_t strides[2] = {(cuuint64_t)(v->stride_t * (int64_t)sizeof(T)),
@@ -638,20 +775,28 @@ inline bool make_map(CUtensorMap *map, const fss_view *v, int64_t B, int64_t Tn,
     const cuuint32_t box[3] = {(cuuint32_t)Cfg<T>::Dc, (cuuint32_t)kTc, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-    return fn(map, dt, 3, v->ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const CUresult r = fn(map, dt, 3, v->ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        *err = "cuTensorMapEncodeTiled returned " + std::to_string((int)r) + " for ptr " +
+               std::to_string((unsigned long long)(uintptr_t)v->ptr) + " dims " + std::to_string(D) + "x" +
+               std::to_string(Tn) + "x" + std::to_string(B) + " strides " + std::to_string(strides[0]) + "," +
+               std::to_string(strides[1]);
+        return false;
+    }
+    return true;
 }
 
 // CTAs that fit the device at once (one per SM with these shared-memory sizes), per device.
-template <typename T, bool kBackward> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
+template <typename T, bool kBackward, bool kProd> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
     static std::mutex mu;
     static int cached[64];
     static bool have[64];
     std::lock_guard<std::mutex> lock(mu);
     if (device < 0 || device >= 64) { *err = cudaErrorInvalidDevice; return 0; }
     if (!have[device]) {
-        auto kern = scan_kernel<T, kBackward>;
+        auto kern = scan_kernel<T, kBackward, kProd>;
         *err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (*err != cudaSuccess) return 0;
         int per_sm = 0, sms = 0;
@@ -666,7 +811,7 @@ template <typename T, bool kBackward> inline int resident_ctas(int device, int s
     return cached[device];
 }
 
-template <typename T, bool kBackward>
+template <typename T, bool kBackward, bool kProd>
 inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t Tn, int64_t D,
                   const fss_view *alpha, const fss_view *x, const fss_view *h, const fss_view *out0,
                   const fss_view *out1, Params p, std::string *err_text) {
@@ -676,11 +821,12 @@ inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t 
     constexpr int Dc = Cfg<T>::Dc;
 
     CUtensorMap m_alpha, m_x, m_h, m_o0, m_o1;
-    if (!make_map<T>(&m_alpha, alpha, B, Tn, D) || !make_map<T>(&m_x, x, B, Tn, D) ||
-        !make_map<T>(&m_o0, out0, B, Tn, D))
+    if (!make_map<T>(&m_alpha, alpha, B, Tn, D, err_text) || !make_map<T>(&m_x, x, B, Tn, D, err_text) ||
+        !make_map<T>(&m_o0, out0, B, Tn, D, err_text))
         return FSS_E_TENSORMAP;
     if (kBackward) {
-        if (!make_map<T>(&m_h, h, B, Tn, D) || !make_map<T>(&m_o1, out1, B, Tn, D)) return FSS_E_TENSORMAP;
+        if (!make_map<T>(&m_h, h, B, Tn, D, err_text) || !make_map<T>(&m_o1, out1, B, Tn, D, err_text))
+            return FSS_E_TENSORMAP;
     } else {
         m_h = m_alpha; m_o1 = m_o0;
     }
@@ -688,7 +834,7 @@ inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t 
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) { *err_text = cudaGetErrorString(e); return FSS_E_DEVICE; }
-    const int resident = resident_ctas<T, kBackward>(device, smem_bytes, &e);
+    const int resident = resident_ctas<T, kBackward, kProd>(device, smem_bytes, &e);
     if (e != cudaSuccess || resident < 1) { *err_text = cudaGetErrorString(e); return FSS_E_LAUNCH; }
 
     p.B = B; p.T = Tn; p.D = D;
@@ -696,16 +842,17 @@ inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t 
     p.ncols = B * p.ncg;
     p.S = ceil_div(Tn, kTc);
     p.ntiles = p.ncols * p.S;
-    if ((size_t)p.ntiles * 4 > ws.flag_bytes || (size_t)p.ntiles * 4 * Dc * sizeof(float) > ws.float_bytes)
-        return FSS_E_WORKSPACE;
+    if ((size_t)p.ntiles * packets_per_tile<T>(kProd) * 16 > ws.packet_bytes) return FSS_E_WORKSPACE;
     p.hdr = reinterpret_cast<Header *>(ws.hdr);
-    p.flags = reinterpret_cast<uint32_t *>(ws.flags);
-    p.desc = reinterpret_cast<float *>(ws.floats);
+    p.packets = reinterpret_cast<uint4 *>(ws.packets);
     p.status = ctx->status;
     p.continuation = (ctx->flags & FSS_FLAG_CONTINUATION) ? 1 : 0;
 
     const unsigned grid = (unsigned)(p.ntiles < resident ? p.ntiles : resident);
-    scan_kernel<T, kBackward><<<grid, kThreads, smem_bytes, (cudaStream_t)ctx->stream>>>(
+    p.grid = grid;
+    p.grid_q = (int32_t)(grid / p.ncols);
+    p.grid_r = (int32_t)(grid % p.ncols);
+    scan_kernel<T, kBackward, kProd><<<grid, kThreads, smem_bytes, (cudaStream_t)ctx->stream>>>(
         m_alpha, m_x, m_h, m_o0, m_o1, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { *err_text = std::string("look-back launch: ") + cudaGetErrorString(e); return FSS_E_LAUNCH; }
@@ -724,7 +871,9 @@ inline int forward(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t
         p.prod_out = st->prod;
         p.block_prod = st->block_prod;
     }
-    return launch<T, false>(ctx, ws, B, Tn, D, alpha, beta, nullptr, h, nullptr, p, err_text);
+    if (p.prod_out || p.block_prod)
+        return launch<T, false, true>(ctx, ws, B, Tn, D, alpha, beta, nullptr, h, nullptr, p, err_text);
+    return launch<T, false, false>(ctx, ws, B, Tn, D, alpha, beta, nullptr, h, nullptr, p, err_text);
 }
 
 template <typename T>
@@ -739,7 +888,9 @@ inline int backward(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_
         p.block_prod = st->block_prod;
         p.h_prev = cont ? st->h_prev : nullptr;
     }
-    return launch<T, true>(ctx, ws, B, Tn, D, alpha, grad, h, dalpha, dbeta, p, err_text);
+    if (p.block_prod)
+        return launch<T, true, true>(ctx, ws, B, Tn, D, alpha, grad, h, dalpha, dbeta, p, err_text);
+    return launch<T, true, false>(ctx, ws, B, Tn, D, alpha, grad, h, dalpha, dbeta, p, err_text);
 }
 
 }  // namespace lookback

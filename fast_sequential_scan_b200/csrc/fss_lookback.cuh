@@ -47,11 +47,12 @@ constexpr int kRowBytes = 256;                // bytes of one tile row
 constexpr int kLaneBytes = 8;
 constexpr int kTileBytes = kTc * kRowBytes;   // 16 KiB per tensor and stage
 constexpr int kProducerWarp = kW;
-constexpr int kLookbackWarp0 = kW + 1;        // first of the look-back warps
+constexpr int kSummaryWarp = kW + 1;
+constexpr int kLookbackWarp0 = kW + 2;        // first of the look-back warps
 constexpr int kLookbackWarps = 2;
-constexpr int kGens = 4;                      // generations of summary buffers (units in flight)
+constexpr int kGens = 3;                      // generations of summary buffers (units in flight)
 constexpr int kLead = 2;                      // pass 1 runs this many units ahead of pass 2
-constexpr int kThreads = (kW + 1 + kLookbackWarps) * 32;
+constexpr int kThreads = (kW + 2 + kLookbackWarps) * 32;
 constexpr int kStagesFwd = 6;                 // 6 x 32 KiB
 constexpr int kStagesBwd = 4;                 // 4 x 48 KiB
 constexpr uint32_t kMaxSpins = 1u << 21;      // per wait; ~a second before giving up
@@ -240,8 +241,10 @@ template <int kTensors, int kStages> struct Smem {
     static constexpr int kStageBytes = kTensors * kTileBytes;
     // summaries: [generation][warp][P|C][lane] as 8-byte (fp32 x2) or 16-byte (fp32 x4) entries
     static constexpr int kAggBytes = kGens * kW * 2 * 32 * 16;
-    static constexpr int kBarriers = 2 * kStages + 2 * kGens;
-    static constexpr int kBytes = 128 /* alignment slack */ + kStages * kStageBytes + kAggBytes + kBarriers * 8 + 16;
+    static constexpr int kSumBytes = kGens * 2 * 32 * 16;      // tile summaries [generation][P|C][lane]
+    static constexpr int kBarriers = 2 * kStages + 3 * kGens;
+    static constexpr int kBytes = 128 /* alignment slack */ + kStages * kStageBytes + kAggBytes + kSumBytes +
+                                  kBarriers * 8 + 16;
 };
 
 // Position of a CTA's current work unit; advances by one grid stride without 64-bit division.
@@ -287,14 +290,17 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     unsigned char *smem_raw = smem_dyn + ((128u - (smem_u32(smem_dyn) & 127u)) & 127u);
     const uint32_t smem_base = smem_u32(smem_raw);
     VecF *agg = reinterpret_cast<VecF *>(smem_raw + kStages * SM::kStageBytes);
-    const uint32_t bars = smem_base + kStages * SM::kStageBytes + SM::kAggBytes;
+    VecF *sums = reinterpret_cast<VecF *>(smem_raw + kStages * SM::kStageBytes + SM::kAggBytes);
+    const uint32_t bars = smem_base + kStages * SM::kStageBytes + SM::kAggBytes + SM::kSumBytes;
     volatile int *cta_abort = reinterpret_cast<volatile int *>(smem_raw + kStages * SM::kStageBytes +
-                                                               SM::kAggBytes + SM::kBarriers * 8);
+                                                               SM::kAggBytes + SM::kSumBytes + SM::kBarriers * 8);
     volatile uint32_t *epoch_s = reinterpret_cast<volatile uint32_t *>(const_cast<int *>(cta_abort) + 1);
     auto bar_full = [&](int s) { return bars + 8u * s; };
     auto bar_done = [&](int s) { return bars + 8u * (kStages + s); };
     auto bar_agg = [&](int g) { return bars + 8u * (2 * kStages + g); };
     auto bar_carry = [&](int g) { return bars + 8u * (2 * kStages + kGens + g); };
+    auto bar_sum = [&](int g) { return bars + 8u * (2 * kStages + 2 * kGens + g); };
+    auto sum_at = [&](int g, int which, int ln) -> VecF & { return sums[(g * 2 + which) * 32 + ln]; };
     // agg[(g, w, P|C)][lane]
     auto agg_at = [&](int g, int w, int which, int ln) -> VecF & { return agg[((g * kW + w) * 2 + which) * 32 + ln]; };
 
@@ -304,7 +310,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_done(s), kW); }
-        for (int g = 0; g < kGens; ++g) { mbar_init(bar_agg(g), kW); mbar_init(bar_carry(g), 1); }
+        for (int g = 0; g < kGens; ++g) { mbar_init(bar_agg(g), kW); mbar_init(bar_carry(g), 1); mbar_init(bar_sum(g), 1); }
         *cta_abort = 0;
         *epoch_s = ld_volatile(&p.hdr->epoch) + 1u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -362,6 +368,47 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             }
             tma_wait_all();
         }
+    } else if (warp == kSummaryWarp) {
+        // ============================================================ summary
+        // Folds the eight warp summaries of every unit into the tile summary as soon as pass 1
+        // has produced them, leaves it in shared memory for the look-back warps and publishes it
+        // at once: successors of this tile can then fold it without waiting for the tile's own
+        // carry resolution.  This warp never waits on anything outside its CTA.
+        using AggPk = PacketGroup<2 * V>;
+        constexpr int kTilePackets = (AggPk::kPackets + PacketGroup<(kProd ? 2 : 1) * V>::kPackets) * 32;
+        const uint32_t tag_agg = (epoch << 2) | kStateAggregate;
+        TileIter it;
+        it.init(p, first);
+        for (int64_t i = 0; i < n_my; ++i) {
+            const int g = (int)(i % kGens);
+            const int64_t k = it.k;
+            const bool last_block = it.s + 1 == (int32_t)p.S;
+            it.advance(p);
+            if (!ctl.wait(bar_agg(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
+            VecF aP[kW], aC[kW];
+#pragma unroll
+            for (int w = 0; w < kW; ++w) { aP[w] = agg_at(g, w, 0, lane); aC[w] = agg_at(g, w, 1, lane); }
+            float pc[2 * V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) { pc[v] = 1.0f; pc[V + v] = 0.0f; }
+#pragma unroll
+            for (int j = 0; j < kW; ++j) {
+                const int w = kBackward ? kW - 1 - j : j;
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    pc[V + v] = fmaf(vec_get(aP[w], v), pc[V + v], vec_get(aC[w], v));
+                    pc[v] *= vec_get(aP[w], v);
+                }
+            }
+            VecF sp, sc;
+#pragma unroll
+            for (int v = 0; v < V; ++v) { vec_set(sp, v, pc[v]); vec_set(sc, v, pc[V + v]); }
+            sum_at(g, 0, lane) = sp;
+            sum_at(g, 1, lane) = sc;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sum(g));
+            if (!last_block) AggPk::store(p.packets + k * kTilePackets + lane, pc, tag_agg);
+        }
     } else if (warp >= kLookbackWarp0) {
         // ============================================================ look-back
         // kLookbackWarps warps share the work units round-robin, so several carry resolutions
@@ -407,25 +454,14 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             pre_ok = false;
             if (i + kLookbackWarps < n_my && it.s > 0) pre_ok = IncPk::load(inc_packets(it.k - p.ncols), pre, tag_inc);
 
-            if (!ctl.wait(bar_agg(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
+            if (!ctl.wait(bar_sum(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
 
-            // fold the warp summaries in scan order into the tile summary
-            float Pt[V], Ct[V];
-#pragma unroll
-            for (int v = 0; v < V; ++v) { Pt[v] = 1.0f; Ct[v] = 0.0f; }
+            // product of alpha over the tile (its summary's P), folded by the summary warp
+            float Pt[V];
             {
-                VecF aP[kW], aC[kW];
+                const VecF sp = sum_at(g, 0, lane);
 #pragma unroll
-                for (int w = 0; w < kW; ++w) { aP[w] = agg_at(g, w, 0, lane); aC[w] = agg_at(g, w, 1, lane); }
-#pragma unroll
-                for (int j = 0; j < kW; ++j) {
-                    const int w = kBackward ? kW - 1 - j : j;
-#pragma unroll
-                    for (int v = 0; v < V; ++v) {
-                        Ct[v] = fmaf(vec_get(aP[w], v), Ct[v], vec_get(aC[w], v));
-                        Pt[v] *= vec_get(aP[w], v);
-                    }
-                }
+                for (int v = 0; v < V; ++v) Pt[v] = vec_get(sp, v);
             }
 
             // ---- the state entering this tile (cin) and the product of alpha before it (pin)
@@ -446,14 +482,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
 #pragma unroll
                 for (int v = 0; v < V; ++v) { cin[v] = cur[v]; pin[v] = kProd ? cur[kProd ? V + v : v] : 1.0f; }
             } else {
-                // publish the summary first: successors can fold it without waiting for this
-                // tile's own look-back
-                {
-                    float pc[2 * V];
-#pragma unroll
-                    for (int v = 0; v < V; ++v) { pc[v] = Pt[v]; pc[V + v] = Ct[v]; }
-                    AggPk::store(agg_packets(k), pc, tag_agg);
-                }
                 float Pa[V], Ca[V];          // map of the tiles between the predecessor at q and this one
 #pragma unroll
                 for (int v = 0; v < V; ++v) { Pa[v] = 1.0f; Ca[v] = 0.0f; }

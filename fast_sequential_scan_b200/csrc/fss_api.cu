@@ -364,3 +364,13 @@ FSS_API int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_
         return fixup_backward_launch<float, 4>(ctx, B, T, D, alpha, h, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_rows);
     return fixup_backward_launch<float, 1>(ctx, B, T, D, alpha, h, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_rows);
 }
+
+#ifdef FSS_TRACE
+// development builds only: install / remove the timeline buffer ([ctas][units][8] uint64)
+FSS_API int fss_debug_set_trace(void *buffer, int units) {
+    unsigned long long *ptr = static_cast<unsigned long long *>(buffer);
+    if (cudaMemcpyToSymbol(fss::lookback::g_trace, &ptr, sizeof(ptr)) != cudaSuccess) return FSS_E_LAUNCH;
+    if (cudaMemcpyToSymbol(fss::lookback::g_trace_units, &units, sizeof(units)) != cudaSuccess) return FSS_E_LAUNCH;
+    return FSS_OK;
+}
+#endif

@@ -6,25 +6,27 @@
 // next ...; the backward numbers row blocks from the end), CTA c of G takes tiles c, c+G, c+2G...
 // so a tile only ever depends on tiles with smaller numbers, which are always resident or done.
 //
-// A CTA runs three roles, coupled only by shared-memory mbarriers:
+// A CTA runs four roles, coupled only by shared-memory mbarriers:
 //   producer warp (1 thread)  TMA-loads the tiles of upcoming work units into a ring of stages
-//                             (cp.async.bulk.tensor, complete_tx on full[stage]); when a unit is
-//                             finished it TMA-stores the results that were written in place and
-//                             refills the stage.
+//                             (cp.async.bulk.tensor, complete_tx on full[stage]) and refills a
+//                             stage as soon as its unit is finished.
 //   8 consumer warps          each owns 8 rows of the tile, each lane 8 bytes of channels.
 //                             pass 1: scan own rows from a zero state -> (P, C) to shared memory;
-//                             pass 2: re-scan from the true entering state, results in place.
-//                             Software-pipelined: pass 1 of unit i+1 runs before pass 2 of unit i,
-//                             so the carry resolution below is off the critical path.
-//   look-back warp            folds the 8 warp summaries into the tile summary, resolves the
-//                             state entering the tile by decoupled look-back over the global
-//                             descriptors of its predecessors, hands every consumer warp its
-//                             entering state and publishes the tile's own descriptors.
-//                             A descriptor is a set of 16-byte packets {3 floats, tag}; each packet
-//                             is written and read with ONE 128-bit relaxed gpu-scope access, so a
-//                             packet whose tag carries this launch's epoch is complete by itself:
-//                             no flag word, no fence, one L2 round trip per look-back step, and
-//                             several predecessors can be read at once.
+//                             pass 2: re-scan from the true entering state and store the results
+//                             straight from registers (a warp writes 256 contiguous bytes per row).
+//                             Software-pipelined: pass 1 runs kLead units ahead of pass 2, so the
+//                             carry resolution below is off the critical path.
+//   summary warp              folds the 8 warp summaries of a unit into the tile summary and
+//                             publishes it at once, so that successors never wait for this tile's
+//                             own carry resolution.
+//   2 look-back warps         take units alternately: resolve the state entering the tile by
+//                             decoupled look-back over the global descriptors of its predecessors,
+//                             hand every consumer warp its entering state, publish the tile's
+//                             inclusive descriptor.
+//                             A descriptor is a set of 8-byte cells {fp32 value, tag}, each moved
+//                             with relaxed gpu-scope 64-bit accesses: a cell whose tag carries this
+//                             launch's epoch is complete by itself -- no flag word, no fence, one L2
+//                             round trip per look-back step, several predecessors read at once.
 // Every wait is bounded; a wait that runs out records a status, raises the abort flag that all
 // other waits poll, and the CTA drains its copies and leaves.
 #pragma once
@@ -49,7 +51,10 @@ constexpr int kTileBytes = kTc * kRowBytes;   // 16 KiB per tensor and stage
 constexpr int kProducerWarp = kW;
 constexpr int kSummaryWarp = kW + 1;
 constexpr int kLookbackWarp0 = kW + 2;        // first of the look-back warps
-constexpr int kLookbackWarps = 2;
+#ifndef FSS_LB_WARPS
+#define FSS_LB_WARPS 2
+#endif
+constexpr int kLookbackWarps = FSS_LB_WARPS;
 constexpr int kGens = 3;                      // generations of summary buffers (units in flight)
 constexpr int kLead = 2;                      // pass 1 runs this many units ahead of pass 2
 constexpr int kThreads = (kW + 2 + kLookbackWarps) * 32;
@@ -89,7 +94,27 @@ struct Params {
     int continuation;
     int64_t grid;            // CTAs of the launch, and grid = grid_q * ncols + grid_r
     int32_t grid_q, grid_r;
+
 };
+
+// ------------------------------------------------------------------ optional timeline trace
+// Compiled in only with -DFSS_TRACE (development builds): every role stamps the global
+// nanosecond timer per work unit into a caller-provided buffer [cta][unit][event].
+#ifdef FSS_TRACE
+__device__ unsigned long long *g_trace = nullptr;
+__device__ int g_trace_units = 0;
+enum { kEvFull = 0, kEvP1 = 1, kEvSum = 2, kEvLbStart = 3, kEvLbDone = 4, kEvP2 = 5, kEvLbTop = 6, kEvRefill = 7,
+       kEvLbIssued = 8, kEvLbFound = 9, kEvCarrySeen = 10, kEvLbA = 11, kEvLbB = 12, kEvLbC = 13, kEvLbE = 14, kEvents = 16 };
+__device__ __forceinline__ void trace(int64_t unit, int ev) {
+    if (g_trace && unit < g_trace_units) {
+        const unsigned long long t = (unsigned long long)clock64();   // SM clock: comparable inside a CTA
+        g_trace[((int64_t)blockIdx.x * g_trace_units + unit) * kEvents + ev] = t;
+    }
+}
+#define FSS_TRACE_EV(unit, ev) do { if ((threadIdx.x & 31) == 0) trace(unit, ev); } while (0)
+#else
+#define FSS_TRACE_EV(unit, ev) do { } while (0)
+#endif
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -132,50 +157,53 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t sr
 __device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
 __device__ __forceinline__ uint32_t ld_volatile(const uint32_t *p) {
     return *reinterpret_cast<const volatile uint32_t *>(p);
 }
 
-// 16-byte descriptor packets: three floats and a tag, moved as one 128-bit access
-__device__ __forceinline__ void st_packet(uint4 *p, float x, float y, float z, uint32_t tag) {
-    const unsigned long long lo = (unsigned long long)__float_as_uint(x) | ((unsigned long long)__float_as_uint(y) << 32);
-    const unsigned long long hi = (unsigned long long)__float_as_uint(z) | ((unsigned long long)tag << 32);
-    asm volatile("{\n\t.reg .b128 t;\n\tmov.b128 t, {%1, %2};\n\tst.relaxed.gpu.global.b128 [%0], t;\n\t}"
-                 ::"l"(p), "l"(lo), "l"(hi) : "memory");
+// Descriptor cells.  A cell is 8 bytes: one fp32 value and a 32-bit tag.  An aligned 64-bit access
+// is single-copy atomic, so a cell whose tag carries this launch's epoch holds the value that was
+// written with it -- no separate flag, no fence.  Cells travel two at a time in 16-byte vector
+// accesses (each element keeps its own tag, so nothing relies on 128-bit atomicity).  The accesses
+// use the .cg cache operator: they are served by L2, the point of coherence between SMs, and --
+// unlike gpu-scope "strong" accesses, which were measured to issue one after the other -- they
+// pipeline, so a whole look-back window costs one round trip.
+__device__ __forceinline__ unsigned long long make_cell(float x, uint32_t tag) {
+    return (unsigned long long)__float_as_uint(x) | ((unsigned long long)tag << 32);
 }
-__device__ __forceinline__ void ld_packet(const uint4 *p, float &x, float &y, float &z, uint32_t &tag) {
-    unsigned long long lo, hi;
-    asm volatile("{\n\t.reg .b128 t;\n\tld.relaxed.gpu.global.b128 t, [%2];\n\tmov.b128 {%0, %1}, t;\n\t}"
-                 : "=l"(lo), "=l"(hi) : "l"(p) : "memory");
-    x = __uint_as_float((uint32_t)lo); y = __uint_as_float((uint32_t)(lo >> 32));
-    z = __uint_as_float((uint32_t)hi); tag = (uint32_t)(hi >> 32);
-}
-// N floats as ceil(N/3) packets, packet j of a tile's group at p[j*32]
+// N floats as N/2 cell pairs; pair j of a tile's group sits at p[j*32] (one uint4 per lane)
 template <int N> struct PacketGroup {
-    static constexpr int kPackets = (N + 2) / 3;
+    static_assert(N % 2 == 0, "cells are moved in pairs");
+    static constexpr int kPackets = N / 2;
     static __device__ __forceinline__ void store(uint4 *p, const float (&v)[N], uint32_t tag) {
 #pragma unroll
-        for (int j = 0; j < kPackets; ++j) {
-            const float x = v[3 * j];
-            const float y = (3 * j + 1 < N) ? v[3 * j + 1] : 0.0f;
-            const float z = (3 * j + 2 < N) ? v[3 * j + 2] : 0.0f;
-            st_packet(p + j * 32, x, y, z, tag);
-        }
+        for (int j = 0; j < kPackets; ++j)
+            asm volatile("st.global.cg.v2.b64 [%0], {%1, %2};"
+                         ::"l"(p + j * 32), "l"(make_cell(v[2 * j], tag)), "l"(make_cell(v[2 * j + 1], tag)) : "memory");
     }
-    // returns true when every packet of the group carries `tag`
-    static __device__ __forceinline__ bool load(const uint4 *p, float (&v)[N], uint32_t tag) {
+    // Issue the loads only: nothing here depends on the returned data, so the caller can keep
+    // working (or wait on a barrier) while they are in flight, and decode() later.
+    struct Raw { unsigned long long c[N]; };
+    static __device__ __forceinline__ void load_raw(const uint4 *p, Raw &r) {
+#pragma unroll
+        for (int j = 0; j < kPackets; ++j)
+            asm volatile("ld.global.cg.v2.b64 {%0, %1}, [%2];"
+                         : "=l"(r.c[2 * j]), "=l"(r.c[2 * j + 1]) : "l"(p + j * 32) : "memory");
+    }
+    // true when every cell of the group carries `tag`
+    static __device__ __forceinline__ bool decode(const Raw &r, float (&v)[N], uint32_t tag) {
         bool ok = true;
 #pragma unroll
-        for (int j = 0; j < kPackets; ++j) {
-            float x, y, z; uint32_t t;
-            ld_packet(p + j * 32, x, y, z, t);
-            v[3 * j] = x;
-            if (3 * j + 1 < N) v[3 * j + 1] = y;
-            if (3 * j + 2 < N) v[3 * j + 2] = z;
-            ok &= (t == tag);
+        for (int j = 0; j < N; ++j) {
+            v[j] = __uint_as_float((uint32_t)r.c[j]);
+            ok &= ((uint32_t)(r.c[j] >> 32) == tag);
         }
         return ok;
+    }
+    static __device__ __forceinline__ bool load(const uint4 *p, float (&v)[N], uint32_t tag) {
+        Raw r;
+        load_raw(p, r);
+        return decode(r, v, tag);
     }
 };
 
@@ -270,9 +298,10 @@ struct TileIter {
 };
 
 // ------------------------------------------------------------------ the kernel
-// Forward: tensors (alpha, beta) are loaded, h is stored from beta's stage slot.
+// Forward: tiles of (alpha, beta) are loaded, h is stored from beta's stage slot.
 // Backward: (alpha, grad, h shifted one row down) are loaded; dbeta is stored from grad's slot,
-// dalpha from h's slot.
+// dalpha from h's slot.  Results are written in place in shared memory and leave through TMA
+// stores issued by the producer, so the consumer warps never stall on the global write path.
 template <typename T, bool kBackward, bool kProd>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant__ CUtensorMap map_x,
@@ -357,6 +386,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                     issue(issued);
                     ++issued;
                 }
+                FSS_TRACE_EV(i, kEvRefill);
             }
             // leave nothing in flight: loads that were issued but never consumed, and all stores
             if (i < n_my) {
@@ -408,6 +438,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_sum(g));
             if (!last_block) AggPk::store(p.packets + k * kTilePackets + lane, pc, tag_agg);
+            FSS_TRACE_EV(i, kEvSum);
         }
     } else if (warp >= kLookbackWarp0) {
         // ============================================================ look-back
@@ -430,11 +461,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
 
         // the predecessor's inclusive descriptor is fetched one of this warp's units ahead of its
         // use and, if it was not there yet, once more when the unit starts
-        float pre[NI];
-        bool pre_ok = false;
-        {
-            if (lb < n_my && it.s > 0) pre_ok = IncPk::load(inc_packets(it.k - p.ncols), pre, tag_inc);
-        }
+        typename IncPk::Raw pre;
+        bool have_pre = false;
+#ifndef FSS_NO_PRE
+        if (lb < n_my && it.s > 0) { IncPk::load_raw(inc_packets(it.k - p.ncols), pre); have_pre = true; }
+#endif
 
         for (int64_t i = lb; i < n_my; i += kLookbackWarps) {
             const int g = (int)(i % kGens);
@@ -444,17 +475,31 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             const bool ch_ok = dch < p.D;
             for (int j = 0; j < kLookbackWarps; ++j) it.advance(p);  // -> this warp's next unit
 
+            FSS_TRACE_EV(i, kEvLbTop);
             float cur[NI];
-#pragma unroll
-            for (int v = 0; v < NI; ++v) cur[v] = pre[v];
-            bool hit = __all_sync(0xffffffffu, pre_ok);
-            float late[NI];
-            bool late_ok = false;
-            if (s > 0 && !hit) late_ok = IncPk::load(inc_packets(k - p.ncols), late, tag_inc);
-            pre_ok = false;
-            if (i + kLookbackWarps < n_my && it.s > 0) pre_ok = IncPk::load(inc_packets(it.k - p.ncols), pre, tag_inc);
+            bool hit = false;
+            if (have_pre) hit = __all_sync(0xffffffffu, IncPk::decode(pre, cur, tag_inc));
+            FSS_TRACE_EV(i, kEvLbA);
+            // second chance for this unit and first look for this warp's next one: both are only
+            // issued here and decoded after the summary barrier, so their latency is hidden
+            typename IncPk::Raw late;
+#ifndef FSS_NO_LATE
+            const bool have_late = s > 0 && !hit;
+#else
+            const bool have_late = false;
+#endif
+            if (have_late) IncPk::load_raw(inc_packets(k - p.ncols), late);
+            FSS_TRACE_EV(i, kEvLbB);
+#ifndef FSS_NO_PRE
+            have_pre = i + kLookbackWarps < n_my && it.s > 0;
+            if (have_pre) IncPk::load_raw(inc_packets(it.k - p.ncols), pre);
+#else
+            have_pre = false;
+#endif
 
+            FSS_TRACE_EV(i, kEvLbIssued);
             if (!ctl.wait(bar_sum(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
+            FSS_TRACE_EV(i, kEvLbStart);
 
             // product of alpha over the tile (its summary's P), folded by the summary warp
             float Pt[V];
@@ -470,10 +515,13 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             auto state0 = [&](int v) {
                 return (p.state_in && ch_ok) ? p.state_in[(int64_t)b * p.D + dch + v] : 0.0f;
             };
-            if (s > 0 && !hit && __all_sync(0xffffffffu, late_ok)) {
-                hit = true;
+            if (have_late) {
+                float lv[NI];
+                if (__all_sync(0xffffffffu, IncPk::decode(late, lv, tag_inc))) {
+                    hit = true;
 #pragma unroll
-                for (int v = 0; v < NI; ++v) cur[v] = late[v];
+                    for (int v = 0; v < NI; ++v) cur[v] = lv[v];
+                }
             }
             if (s == 0) {
 #pragma unroll
@@ -549,6 +597,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 if (!ok) break;
             }
 
+            FSS_TRACE_EV(i, kEvLbFound);
             // ---- hand every consumer warp the state entering its rows (into its P slot)
             float run[V];
 #pragma unroll
@@ -569,6 +618,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_carry(g));
+            FSS_TRACE_EV(i, kEvLbDone);
 
             // ---- publish the inclusive descriptor: state after this tile, product through it
             float out[NI];
@@ -577,7 +627,9 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 out[v] = run[v];
                 if (kProd) out[kProd ? V + v : v] = Pt[v] * pin[v];
             }
+            FSS_TRACE_EV(i, kEvLbE);
             if (s + 1 < (int32_t)p.S) IncPk::store(inc_packets(k), out, tag_inc);
+            FSS_TRACE_EV(i, kEvLbC);
 
             if (ch_ok) {
                 if (kProd && p.block_prod) {
@@ -614,6 +666,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             const bool head = (it1.template row0<kBackward>(p) == 0) && (warp == 0) && !p.continuation;
             it1.advance(p);
             if (!ctl.wait(bar_full(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) return false;
+            if (warp == 0) FSS_TRACE_EV(i, kEvFull);
             Raw *a_t = tile_ptr(st, 0);
             const Raw *x_t = tile_ptr(st, 1);
             // row 0 of the whole sequence: alpha_0 is not part of the recurrence
@@ -644,23 +697,27 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             agg_at(g, warp, 1, lane) = vc;
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_agg(g));
+            if (warp == 0) FSS_TRACE_EV(i, kEvP1);
             return true;
         };
 
         auto pass2 = [&](int64_t i) -> bool {
             const int st = (int)(i % kStages), g = (int)(i % kGens);
-            const bool head = (it2.template row0<kBackward>(p) == 0) && (warp == 0);
+            const int32_t row0 = it2.template row0<kBackward>(p);
+            const bool head = (row0 == 0) && (warp == 0);
             const int32_t b = it2.batch(p);
             const int64_t dch = (int64_t)it2.cgroup(p) * Dc + ch;
             it2.advance(p);
-            Raw *x_t = tile_ptr(st, 1);
             const Raw *a_t = tile_ptr(st, 0);
+            Raw *x_t = tile_ptr(st, 1);
             // the tile's data has been resident since pass 1: fetch it while the carry is resolved
             Raw ra[kR], rx[kR];
 #pragma unroll
             for (int r = 0; r < kR; ++r) { ra[r] = a_t[r * kRowStride]; rx[r] = x_t[r * kRowStride]; }
+            const bool col_ok = dch < p.D;
             if (!kBackward) {
                 if (!ctl.wait(bar_carry(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) return false;
+                if (warp == 0) FSS_TRACE_EV(i, kEvCarrySeen);
                 const VecF cv = agg_at(g, warp, 0, lane);
                 float stv[V];
 #pragma unroll
@@ -682,10 +739,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 if (head && p.continuation && p.h_prev) {    // h_{-1} of a continued sequence
                     float hp[V];
 #pragma unroll
-                    for (int v = 0; v < V; ++v) hp[v] = (dch < p.D) ? p.h_prev[(int64_t)b * p.D + dch + v] : 0.0f;
+                    for (int v = 0; v < V; ++v) hp[v] = col_ok ? p.h_prev[(int64_t)b * p.D + dch + v] : 0.0f;
                     rh[0] = Lane<T>::pack(hp);
                 }
                 if (!ctl.wait(bar_carry(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) return false;
+                if (warp == 0) FSS_TRACE_EV(i, kEvCarrySeen);
                 const VecF cv = agg_at(g, warp, 0, lane);
                 float stv[V];
 #pragma unroll
@@ -714,6 +772,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             fence_proxy_async();      // make the in-place results visible to the TMA store
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_done(st));
+            if (warp == 0) FSS_TRACE_EV(i, kEvP2);
             return true;
         };
 

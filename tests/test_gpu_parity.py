@@ -251,3 +251,28 @@ def test_non_default_stream_and_saved_output_untouched():
     assert torch.equal(h.detach(), keep)
     h_ref, _, _ = oracle.reference_values(a, b, None)
     assert_parity(h, h_ref, BF16_TOL, "h on side stream")
+
+
+@pytest.mark.parametrize("shape", [(4, 4096, 2048), (2, 8192, 1024), (1, 16384, 512)])
+def test_lookback_descriptors_survive_reuse_with_different_data(shape):
+    """Consecutive launches on one workspace with DIFFERENT inputs of one shape: a stale tile
+    descriptor of the previous launch must never pass for a current one.  Few columns and many
+    row blocks, so that most tiles resolve their carry from descriptors of tiles that are
+    running at the same time."""
+    _, native, _lib = _mods()
+    import fast_sequential_scan_b200 as pkg
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    sets = []
+    for _ in range(3):
+        a = (0.5 + 0.499 * torch.rand(shape, generator=gen, device="cuda")).bfloat16()
+        b = (torch.randn(shape, generator=gen, device="cuda") * 3).bfloat16()
+        ref = torch.empty_like(a)
+        native.forward_into(a, b, ref, algo=_lib.ALGO_CHUNKED)
+        sets.append((a, b, ref))
+    h = torch.empty_like(sets[0][0])
+    for it in range(24):
+        a, b, ref = sets[it % 3]
+        native.forward_into(a, b, h, algo=_lib.ALGO_LOOKBACK)
+        r = oracle.mixed_error_ratio(h, ref, BF16_TOL)
+        assert r <= 1.0, f"launch {it}: ratio {r}"
+    pkg.check_status()

@@ -269,7 +269,7 @@ template <int kTensors, int kStages> struct Smem {
     static constexpr int kStageBytes = kTensors * kTileBytes;
     // summaries: [generation][warp][P|C][lane] as 8-byte (fp32 x2) or 16-byte (fp32 x4) entries
     static constexpr int kAggBytes = kGens * kW * 2 * 32 * 16;
-    static constexpr int kSumBytes = kGens * 2 * 32 * 16;      // tile summaries [generation][P|C][lane]
+    static constexpr int kSumBytes = kGens * 3 * 32 * 16;      // [generation][tile P | tile C | entering state][lane]
     static constexpr int kBarriers = 2 * kStages + 3 * kGens;
     static constexpr int kBytes = 128 /* alignment slack */ + kStages * kStageBytes + kAggBytes + kSumBytes +
                                   kBarriers * 8 + 16;
@@ -329,7 +329,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     auto bar_agg = [&](int g) { return bars + 8u * (2 * kStages + g); };
     auto bar_carry = [&](int g) { return bars + 8u * (2 * kStages + kGens + g); };
     auto bar_sum = [&](int g) { return bars + 8u * (2 * kStages + 2 * kGens + g); };
-    auto sum_at = [&](int g, int which, int ln) -> VecF & { return sums[(g * 2 + which) * 32 + ln]; };
+    auto sum_at = [&](int g, int which, int ln) -> VecF & { return sums[(g * 3 + which) * 32 + ln]; };
     // agg[(g, w, P|C)][lane]
     auto agg_at = [&](int g, int w, int which, int ln) -> VecF & { return agg[((g * kW + w) * 2 + which) * 32 + ln]; };
 
@@ -421,14 +421,20 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             float pc[2 * V];
 #pragma unroll
             for (int v = 0; v < V; ++v) { pc[v] = 1.0f; pc[V + v] = 0.0f; }
+            // every warp's slot receives the map of the warps BEFORE it (its exclusive prefix)
 #pragma unroll
             for (int j = 0; j < kW; ++j) {
                 const int w = kBackward ? kW - 1 - j : j;
+                VecF ep, ec;
 #pragma unroll
                 for (int v = 0; v < V; ++v) {
+                    vec_set(ep, v, pc[v]);
+                    vec_set(ec, v, pc[V + v]);
                     pc[V + v] = fmaf(vec_get(aP[w], v), pc[V + v], vec_get(aC[w], v));
                     pc[v] *= vec_get(aP[w], v);
                 }
+                agg_at(g, w, 0, lane) = ep;
+                agg_at(g, w, 1, lane) = ec;
             }
             VecF sp, sc;
 #pragma unroll
@@ -501,12 +507,12 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             if (!ctl.wait(bar_sum(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
             FSS_TRACE_EV(i, kEvLbStart);
 
-            // product of alpha over the tile (its summary's P), folded by the summary warp
-            float Pt[V];
+            // the tile's summary, folded by the summary warp
+            float Pt[V], Ct[V];
             {
-                const VecF sp = sum_at(g, 0, lane);
+                const VecF sp = sum_at(g, 0, lane), sc = sum_at(g, 1, lane);
 #pragma unroll
-                for (int v = 0; v < V; ++v) Pt[v] = vec_get(sp, v);
+                for (int v = 0; v < V; ++v) { Pt[v] = vec_get(sp, v); Ct[v] = vec_get(sc, v); }
             }
 
             // ---- the state entering this tile (cin) and the product of alpha before it (pin)
@@ -598,23 +604,13 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             }
 
             FSS_TRACE_EV(i, kEvLbFound);
-            // ---- hand every consumer warp the state entering its rows (into its P slot)
-            float run[V];
+            // ---- hand the entering state to the consumers: each warp applies the exclusive prefix
+            // the summary warp left in its slot
+            {
+                VecF vin;
 #pragma unroll
-            for (int v = 0; v < V; ++v) run[v] = cin[v];
-            VecF aP[kW], aC[kW];
-#pragma unroll
-            for (int w = 0; w < kW; ++w) { aP[w] = agg_at(g, w, 0, lane); aC[w] = agg_at(g, w, 1, lane); }
-#pragma unroll
-            for (int j = 0; j < kW; ++j) {
-                const int w = kBackward ? kW - 1 - j : j;
-                VecF hand;
-#pragma unroll
-                for (int v = 0; v < V; ++v) {
-                    vec_set(hand, v, run[v]);
-                    run[v] = fmaf(vec_get(aP[w], v), run[v], vec_get(aC[w], v));
-                }
-                agg_at(g, w, 0, lane) = hand;
+                for (int v = 0; v < V; ++v) vec_set(vin, v, cin[v]);
+                sum_at(g, 2, lane) = vin;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_carry(g));
@@ -624,7 +620,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             float out[NI];
 #pragma unroll
             for (int v = 0; v < V; ++v) {
-                out[v] = run[v];
+                out[v] = fmaf(Pt[v], cin[v], Ct[v]);
                 if (kProd) out[kProd ? V + v : v] = Pt[v] * pin[v];
             }
             FSS_TRACE_EV(i, kEvLbE);
@@ -718,10 +714,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             if (!kBackward) {
                 if (!ctl.wait(bar_carry(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) return false;
                 if (warp == 0) FSS_TRACE_EV(i, kEvCarrySeen);
-                const VecF cv = agg_at(g, warp, 0, lane);
+                // state entering this warp's rows = (map of the warps before it)(state entering the tile)
+                const VecF ep = agg_at(g, warp, 0, lane), ec = agg_at(g, warp, 1, lane), vin = sum_at(g, 2, lane);
                 float stv[V];
 #pragma unroll
-                for (int v = 0; v < V; ++v) stv[v] = vec_get(cv, v);
+                for (int v = 0; v < V; ++v) stv[v] = fmaf(vec_get(ep, v), vec_get(vin, v), vec_get(ec, v));
 #pragma unroll
                 for (int r = 0; r < kR; ++r) {
                     float a[V], x[V];
@@ -744,10 +741,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 }
                 if (!ctl.wait(bar_carry(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) return false;
                 if (warp == 0) FSS_TRACE_EV(i, kEvCarrySeen);
-                const VecF cv = agg_at(g, warp, 0, lane);
+                // state entering this warp's rows = (map of the warps before it)(state entering the tile)
+                const VecF ep = agg_at(g, warp, 0, lane), ec = agg_at(g, warp, 1, lane), vin = sum_at(g, 2, lane);
                 float stv[V];
 #pragma unroll
-                for (int v = 0; v < V; ++v) stv[v] = vec_get(cv, v);
+                for (int v = 0; v < V; ++v) stv[v] = fmaf(vec_get(ep, v), vec_get(vin, v), vec_get(ec, v));
 #pragma unroll
                 for (int j = 0; j < kR; ++j) {
                     const int r = kR - 1 - j;

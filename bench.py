@@ -38,6 +38,7 @@ def parse_args():
     p.add_argument("--impl", default="b200", choices=["b200", "reference"])
     p.add_argument("--workload", default="c2")
     p.add_argument("--algo", default="auto", choices=["auto", "chunked", "lookback"])
+    p.add_argument("--shape", default=None, help="override batch,seq,d_model of the workload (same gates and dtype)")
     p.add_argument("--mode", default="shard", choices=["shard", "seqpar"])
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-graphs", action="store_true", help="launch every step from Python instead of replaying CUDA graphs")
@@ -215,6 +216,10 @@ def main():
         return
 
     w = CONFIGS[args.workload]
+    if args.shape:
+        import dataclasses
+        bb, tt, dd = (int(x) for x in args.shape.split(","))
+        w = dataclasses.replace(w, name=f"{w.name}[{bb}x{tt}x{dd}]", batch=bb, seq=tt, d_model=dd)
     algo = _lib.ALGO_BY_NAME[args.algo]
     dt = w.torch_dtype
     esize = 2 if w.dtype == "bf16" else 4

@@ -42,22 +42,23 @@
 namespace fss {
 namespace lookback {
 
-constexpr int kW = 8;                         // consumer warps
-constexpr int kR = 8;                         // rows per consumer warp and tile
+constexpr int kW = 4;                         // warps per pass (pass-1 group and pass-2 group)
+constexpr int kR = 16;                        // rows per warp and tile
+constexpr int kRh = 8;                        // rows handled per register batch
 constexpr int kTc = kW * kR;                  // rows per tile
 constexpr int kRowBytes = 256;                // bytes of one tile row
 constexpr int kLaneBytes = 8;
 constexpr int kTileBytes = kTc * kRowBytes;   // 16 KiB per tensor and stage
-constexpr int kProducerWarp = kW;
-constexpr int kSummaryWarp = kW + 1;
-constexpr int kLookbackWarp0 = kW + 2;        // first of the look-back warps
+constexpr int kPass2Warp0 = kW;               // warps [0,kW) run pass 1, [kW,2kW) run pass 2
+constexpr int kProducerWarp = 2 * kW;
+constexpr int kSummaryWarp = 2 * kW + 1;
+constexpr int kLookbackWarp0 = 2 * kW + 2;    // first of the look-back warps
 #ifndef FSS_LB_WARPS
 #define FSS_LB_WARPS 2
 #endif
 constexpr int kLookbackWarps = FSS_LB_WARPS;
-constexpr int kGens = 3;                      // generations of summary buffers (units in flight)
-constexpr int kLead = 2;                      // pass 1 runs this many units ahead of pass 2
-constexpr int kThreads = (kW + 2 + kLookbackWarps) * 32;
+constexpr int kGens = 4;                      // generations of summary buffers: pass 1 may run this far ahead of pass 2
+constexpr int kThreads = (2 * kW + 2 + kLookbackWarps) * 32;
 constexpr int kStagesFwd = 6;                 // 6 x 32 KiB
 constexpr int kStagesBwd = 4;                 // 4 x 48 KiB
 constexpr uint32_t kMaxSpins = 1u << 21;      // per wait; ~a second before giving up
@@ -643,47 +644,50 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 }
             }
         }
-    } else {
-        // ============================================================ consumers
-        const uint32_t lane_off = (uint32_t)(warp * kR) * kRowBytes + (uint32_t)lane * kLaneBytes;
-        const int ch = lane * V;
+    } else if (warp < kPass2Warp0) {
+        // ============================================================ pass 1
+        // Scans this warp's rows of every unit from a zero state as soon as the tile has landed
+        // and leaves (P, C); never waits for a carry, only for the summary buffers to be free.
         using Raw = typename Lane<T>::Raw;
-        auto tile_ptr = [&](int st, int tensor) {
-            return reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + tensor * kTileBytes + lane_off);
-        };
         constexpr int kRowStride = kRowBytes / (int)sizeof(Raw);
-
-        TileIter it1, it2;     // positions of the next pass-1 unit and the next pass-2 unit
-        it1.init(p, first);
-        it2.init(p, first);
-
-        auto pass1 = [&](int64_t i) -> bool {
+        const uint32_t lane_off = (uint32_t)(warp * kR) * kRowBytes + (uint32_t)lane * kLaneBytes;
+        TileIter it;
+        it.init(p, first);
+        for (int64_t i = 0; i < n_my; ++i) {
             const int st = (int)(i % kStages), g = (int)(i % kGens);
-            const bool head = (it1.template row0<kBackward>(p) == 0) && (warp == 0) && !p.continuation;
-            it1.advance(p);
-            if (!ctl.wait(bar_full(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) return false;
+            const bool head = (it.template row0<kBackward>(p) == 0) && (warp == 0) && !p.continuation;
+            it.advance(p);
+            if (i >= kGens) {      // the summary buffers of this generation are free once pass 2 of unit i-kGens is done
+                const int64_t o = i - kGens;
+                if (!ctl.wait(bar_done((int)(o % kStages)), (uint32_t)((o / kStages) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
+            }
+            if (!ctl.wait(bar_full(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
             if (warp == 0) FSS_TRACE_EV(i, kEvFull);
-            Raw *a_t = tile_ptr(st, 0);
-            const Raw *x_t = tile_ptr(st, 1);
+            Raw *a_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + lane_off);
+            const Raw *x_t = reinterpret_cast<const Raw *>(smem_raw + st * SM::kStageBytes + kTileBytes + lane_off);
             // row 0 of the whole sequence: alpha_0 is not part of the recurrence
             if (head) a_t[0] = Lane<T>::zero();
-            Raw ra[kR], rx[kR];
-#pragma unroll
-            for (int r = 0; r < kR; ++r) { ra[r] = a_t[r * kRowStride]; rx[r] = x_t[r * kRowStride]; }
             float P[V], C[V];
 #pragma unroll
             for (int v = 0; v < V; ++v) { P[v] = 1.0f; C[v] = 0.0f; }
 #pragma unroll
-            for (int j = 0; j < kR; ++j) {
-                const int r = kBackward ? kR - 1 - j : j;
-                float a[V], x[V];
-                Lane<T>::unpack(ra[r], a);
-                Lane<T>::unpack(rx[r], x);
+            for (int hb = 0; hb < kR / kRh; ++hb) {
+                const int base = kBackward ? kR - kRh * (hb + 1) : kRh * hb;     // rows of this batch
+                Raw ra[kRh], rx[kRh];
 #pragma unroll
-                for (int v = 0; v < V; ++v) {
-                    if (!kBackward) C[v] = fmaf(a[v], C[v], x[v]);
-                    else C[v] = a[v] * (x[v] + C[v]);
-                    P[v] *= a[v];
+                for (int r = 0; r < kRh; ++r) { ra[r] = a_t[(base + r) * kRowStride]; rx[r] = x_t[(base + r) * kRowStride]; }
+#pragma unroll
+                for (int j = 0; j < kRh; ++j) {
+                    const int r = kBackward ? kRh - 1 - j : j;
+                    float a[V], x[V];
+                    Lane<T>::unpack(ra[r], a);
+                    Lane<T>::unpack(rx[r], x);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        if (!kBackward) C[v] = fmaf(a[v], C[v], x[v]);
+                        else C[v] = a[v] * (x[v] + C[v]);
+                        P[v] *= a[v];
+                    }
                 }
             }
             VecF vp, vc;
@@ -694,92 +698,88 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_agg(g));
             if (warp == 0) FSS_TRACE_EV(i, kEvP1);
-            return true;
-        };
-
-        auto pass2 = [&](int64_t i) -> bool {
+        }
+    } else {
+        // ============================================================ pass 2
+        // Re-scans this warp's rows from the true entering state and writes the results in place.
+        using Raw = typename Lane<T>::Raw;
+        constexpr int kRowStride = kRowBytes / (int)sizeof(Raw);
+        const int w2 = warp - kPass2Warp0;
+        const uint32_t lane_off = (uint32_t)(w2 * kR) * kRowBytes + (uint32_t)lane * kLaneBytes;
+        const int ch = lane * V;
+        TileIter it;
+        it.init(p, first);
+        for (int64_t i = 0; i < n_my; ++i) {
             const int st = (int)(i % kStages), g = (int)(i % kGens);
-            const int32_t row0 = it2.template row0<kBackward>(p);
-            const bool head = (row0 == 0) && (warp == 0);
-            const int32_t b = it2.batch(p);
-            const int64_t dch = (int64_t)it2.cgroup(p) * Dc + ch;
-            it2.advance(p);
-            const Raw *a_t = tile_ptr(st, 0);
-            Raw *x_t = tile_ptr(st, 1);
-            // the tile's data has been resident since pass 1: fetch it while the carry is resolved
-            Raw ra[kR], rx[kR];
-#pragma unroll
-            for (int r = 0; r < kR; ++r) { ra[r] = a_t[r * kRowStride]; rx[r] = x_t[r * kRowStride]; }
-            const bool col_ok = dch < p.D;
-            if (!kBackward) {
-                if (!ctl.wait(bar_carry(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) return false;
-                if (warp == 0) FSS_TRACE_EV(i, kEvCarrySeen);
-                // state entering this warp's rows = (map of the warps before it)(state entering the tile)
-                const VecF ep = agg_at(g, warp, 0, lane), ec = agg_at(g, warp, 1, lane), vin = sum_at(g, 2, lane);
-                float stv[V];
+            const bool head = (it.template row0<kBackward>(p) == 0) && (w2 == 0);
+            const int32_t b = it.batch(p);
+            const int64_t dch = (int64_t)it.cgroup(p) * Dc + ch;
+            it.advance(p);
+            const Raw *a_t = reinterpret_cast<const Raw *>(smem_raw + st * SM::kStageBytes + lane_off);
+            Raw *x_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + kTileBytes + lane_off);
+            Raw *h_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + 2 * kTileBytes + lane_off);
+            // the carry barrier is reached through pass 1 of this unit, so the tile is resident
+            if (!ctl.wait(bar_carry(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
+            if (w2 == 0) FSS_TRACE_EV(i, kEvCarrySeen);
+            // state entering this warp's rows = (map of the warps before it)(state entering the tile)
+            float stv[V];
+            {
+                const VecF ep = agg_at(g, w2, 0, lane), ec = agg_at(g, w2, 1, lane), vin = sum_at(g, 2, lane);
 #pragma unroll
                 for (int v = 0; v < V; ++v) stv[v] = fmaf(vec_get(ep, v), vec_get(vin, v), vec_get(ec, v));
+            }
 #pragma unroll
-                for (int r = 0; r < kR; ++r) {
-                    float a[V], x[V];
-                    Lane<T>::unpack(ra[r], a);
-                    Lane<T>::unpack(rx[r], x);
+            for (int hb = 0; hb < kR / kRh; ++hb) {
+                const int base = kBackward ? kR - kRh * (hb + 1) : kRh * hb;
+                Raw ra[kRh], rx[kRh];
 #pragma unroll
-                    for (int v = 0; v < V; ++v) stv[v] = fmaf(a[v], stv[v], x[v]);
-                    x_t[r * kRowStride] = Lane<T>::pack(stv);
-                }
-            } else {
-                Raw *h_t = tile_ptr(st, 2);
-                Raw rh[kR];
+                for (int r = 0; r < kRh; ++r) { ra[r] = a_t[(base + r) * kRowStride]; rx[r] = x_t[(base + r) * kRowStride]; }
+                if (!kBackward) {
 #pragma unroll
-                for (int r = 0; r < kR; ++r) rh[r] = h_t[r * kRowStride];
-                if (head && p.continuation && p.h_prev) {    // h_{-1} of a continued sequence
-                    float hp[V];
+                    for (int r = 0; r < kRh; ++r) {
+                        float a[V], x[V];
+                        Lane<T>::unpack(ra[r], a);
+                        Lane<T>::unpack(rx[r], x);
 #pragma unroll
-                    for (int v = 0; v < V; ++v) hp[v] = col_ok ? p.h_prev[(int64_t)b * p.D + dch + v] : 0.0f;
-                    rh[0] = Lane<T>::pack(hp);
-                }
-                if (!ctl.wait(bar_carry(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) return false;
-                if (warp == 0) FSS_TRACE_EV(i, kEvCarrySeen);
-                // state entering this warp's rows = (map of the warps before it)(state entering the tile)
-                const VecF ep = agg_at(g, warp, 0, lane), ec = agg_at(g, warp, 1, lane), vin = sum_at(g, 2, lane);
-                float stv[V];
-#pragma unroll
-                for (int v = 0; v < V; ++v) stv[v] = fmaf(vec_get(ep, v), vec_get(vin, v), vec_get(ec, v));
-#pragma unroll
-                for (int j = 0; j < kR; ++j) {
-                    const int r = kR - 1 - j;
-                    float a[V], x[V], hp[V], da[V], dh[V];
-                    Lane<T>::unpack(ra[r], a);
-                    Lane<T>::unpack(rx[r], x);
-                    Lane<T>::unpack(rh[r], hp);
-#pragma unroll
-                    for (int v = 0; v < V; ++v) {
-                        dh[v] = x[v] + stv[v];
-                        da[v] = dh[v] * hp[v];
-                        stv[v] = a[v] * dh[v];
+                        for (int v = 0; v < V; ++v) stv[v] = fmaf(a[v], stv[v], x[v]);
+                        x_t[(base + r) * kRowStride] = Lane<T>::pack(stv);
                     }
-                    if (r == 0 && head && !p.continuation) {
+                } else {
+                    Raw rh[kRh];
 #pragma unroll
-                        for (int v = 0; v < V; ++v) da[v] = 0.0f;
+                    for (int r = 0; r < kRh; ++r) rh[r] = h_t[(base + r) * kRowStride];
+                    if (base == 0 && head && p.continuation && p.h_prev) {    // h_{-1} of a continued sequence
+                        float hp[V];
+#pragma unroll
+                        for (int v = 0; v < V; ++v) hp[v] = (dch < p.D) ? p.h_prev[(int64_t)b * p.D + dch + v] : 0.0f;
+                        rh[0] = Lane<T>::pack(hp);
                     }
-                    x_t[r * kRowStride] = Lane<T>::pack(dh);
-                    h_t[r * kRowStride] = Lane<T>::pack(da);
+#pragma unroll
+                    for (int j = 0; j < kRh; ++j) {
+                        const int r = kRh - 1 - j;
+                        float a[V], x[V], hp[V], da[V], dh[V];
+                        Lane<T>::unpack(ra[r], a);
+                        Lane<T>::unpack(rx[r], x);
+                        Lane<T>::unpack(rh[r], hp);
+#pragma unroll
+                        for (int v = 0; v < V; ++v) {
+                            dh[v] = x[v] + stv[v];
+                            da[v] = dh[v] * hp[v];
+                            stv[v] = a[v] * dh[v];
+                        }
+                        if (base + r == 0 && head && !p.continuation) {
+#pragma unroll
+                            for (int v = 0; v < V; ++v) da[v] = 0.0f;
+                        }
+                        x_t[(base + r) * kRowStride] = Lane<T>::pack(dh);
+                        h_t[(base + r) * kRowStride] = Lane<T>::pack(da);
+                    }
                 }
             }
             fence_proxy_async();      // make the in-place results visible to the TMA store
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_done(st));
-            if (warp == 0) FSS_TRACE_EV(i, kEvP2);
-            return true;
-        };
-
-        // pass 1 runs kLead units ahead of pass 2
-        bool alive = true;
-        for (int64_t j = 0; alive && j < kLead && j < n_my; ++j) alive = pass1(j);
-        for (int64_t i = 0; alive && i < n_my; ++i) {
-            if (i + kLead < n_my) alive = pass1(i + kLead);
-            if (alive) alive = pass2(i);
+            if (w2 == 0) FSS_TRACE_EV(i, kEvP2);
         }
     }
 

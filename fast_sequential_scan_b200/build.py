@@ -2,8 +2,8 @@
 
 No libtorch, no pybind: the only inputs are ``csrc/*.cu[h]`` and ``include/fss_b200.h``; the
 result sits beside this file so that it travels with the source tree.  Run as
-``python -m fast_sequential_scan_b200.build`` (add ``--force`` to rebuild, ``--verbose`` for
-ptxas resource usage).
+``python fast_sequential_scan_b200/build.py`` (add ``--force`` to rebuild, ``--verbose`` for ptxas
+resource usage); run it as a script, not with ``-m``: importing the package needs the library.
 """
 from __future__ import annotations
 
@@ -50,7 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     cmd = [_nvcc(), *NVCC_FLAGS]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB), str(CSRC / "fss_api.cu")]
+    cmd += ["-o", str(LIB)] + [str(f) for f in sorted(CSRC.glob("*.cu"))]
     env = dict(os.environ)
     res = subprocess.run(cmd, env=env, capture_output=True, text=True)
     if verbose or res.returncode:

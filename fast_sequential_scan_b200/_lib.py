@@ -66,6 +66,7 @@ SIGNATURES = {
                                          c_void_p, c_void_p, c_int64]),
     "fss_seqpar_fixup_backward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64] + [_P(View)] * 4
                                   + [c_void_p, c_void_p, c_void_p, c_int64]),
+    "fss_scan_forward_noalloc": (c_int, [c_int, c_int, c_void_p, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View)]),
 }
 
 _lib = None
@@ -87,7 +88,7 @@ def lib() -> ctypes.CDLL:
         path = Path(os.environ.get("FSS_B200_LIB", LIB_PATH))
         if not path.is_file():
             raise ImportError(
-                f"{path} is missing: build it with `python -m fast_sequential_scan_b200.build` "
+                f"{path} is missing: build it with `python fast_sequential_scan_b200/build.py` "
                 "(needs nvcc); this package has no CPU or PyTorch fallback")
         L = ctypes.CDLL(str(path))
         for name, (res, args) in SIGNATURES.items():

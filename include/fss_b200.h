@@ -174,6 +174,27 @@ int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_t B, int
                               const fss_view *grad_beta, const float *u_in, const float *h_prev,
                               const float *block_prod, int64_t block_rows);
 
+/* ---- a forward scan that allocates nothing ------------------------------------------------ */
+/* Has no counterpart in the reference.  It exists for callers that cannot obtain scratch memory
+ * when they need a scan -- a plugin inside a host that owns all device memory, a loop that must
+ * not run into cudaMalloc's device-wide synchronisation, a process whose memory budget is frozen.
+ * The chunk summaries of this forward scan (chunked algorithm, h_0 = b_0 rule, no boundary state)
+ * go to a fixed array of FSS_NOALLOC_SCRATCH_BYTES that is part of the library image; every GPU
+ * that loads the library holds that array until the process exits.  The caller passes only the
+ * tensors.  Limits and rules:
+ *   - the problem must satisfy  8 * B * D * ceil(T / L) <= FSS_NOALLOC_SCRATCH_BYTES  with L the
+ *     chunk length (16..256 rows, chosen like fss_block_rows(..., FSS_ALGO_CHUNKED));
+ *     larger problems return FSS_E_TOO_LARGE and launch nothing;
+ *   - all calls share the one array: calls whose kernels can overlap on the GPU race and must be
+ *     serialised by the caller; nothing in the array needs clearing between calls;
+ *   - the first call that targets a device looks up the array's device address; make that first
+ *     call before any stream capture starts.
+ * No cudaMalloc, cudaFree or other allocating routine is called.  device: CUDA ordinal, or -1 for
+ * the calling thread's current device. */
+#define FSS_NOALLOC_SCRATCH_BYTES (8u << 20)
+int fss_scan_forward_noalloc(int dtype, int device, void *stream, int64_t B, int64_t T, int64_t D,
+                             const fss_view *alpha, const fss_view *beta, const fss_view *h);
+
 #ifdef __cplusplus
 }
 #endif

@@ -190,6 +190,63 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------ sequence-parallel mode
+def run_seqpar(args, world, rank, dev):
+    """BASELINE config 5 style: every rank holds 65,536 rows of a (65,536 * N)-row sequence; a step
+    is the sequence-parallel forward (local scan, all-gather of carries, fix-up) plus backward."""
+    import torch
+    import torch.distributed as dist
+    import fast_sequential_scan_b200 as pkg
+    from fast_sequential_scan_b200 import distributed as fd
+    from fast_sequential_scan_b200.workloads import CONFIGS, make_inputs
+    w = CONFIGS["c5_rank"]
+    a, b, g = make_inputs(w, dev, seed=rank)
+    ops = fd.NativeOps()
+    group = None
+    if world == 1:      # no process group needed: a 1-rank gather is the identity
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29517", rank=0, world_size=1)
+
+    def step():
+        h, saved = fd.seqpar_forward(a, b, group, ops)
+        fd.seqpar_backward(a, h, g, saved, group, ops)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    pkg.check_status()
+    peak, kind = peaks()
+    total = w.elems * world
+    gbs = w.elems * 16 / (ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": total / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"c5: sequence-parallel fwd+bwd scan, B1 T{w.seq * world} D{w.d_model}, "
+                                   f"{w.seq} rows per GPU, a~U(0.9,0.9999)",
+                       "parallelism": f"sequence split x{world}: local scan, all-gather of (prod, carry), fix-up",
+                       "l2": "per-rank working set 1.6 GB >> L2"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                         "traffic": None, "peak_kind": f"of {kind}", "per": "GPU, fwd+bwd 16 B/elem, fix-up traffic not counted"},
+            "gpu_launches": None}), flush=True)
+    dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------ GPU arm
 def main():
     args = parse_args()
@@ -211,8 +268,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     if args.mode == "seqpar":
-        from fast_sequential_scan_b200 import bench_seqpar
-        bench_seqpar.run(args, world, rank, dev)
+        run_seqpar(args, world, rank, dev)
         return
 
     w = CONFIGS[args.workload]

@@ -36,11 +36,13 @@ class ScanCtx(Structure):
 
 
 class ForwardState(Structure):
-    _fields_ = [("h_in", c_void_p), ("h_last", c_void_p), ("prod", c_void_p), ("block_prod", c_void_p)]
+    _fields_ = [("h_in", c_void_p), ("h_last", c_void_p), ("prod", c_void_p), ("block_prod", c_void_p),
+                ("block_state", c_void_p)]
 
 
 class BackwardState(Structure):
-    _fields_ = [("u_in", c_void_p), ("h_prev", c_void_p), ("u_out", c_void_p), ("block_prod", c_void_p)]
+    _fields_ = [("u_in", c_void_p), ("h_prev", c_void_p), ("u_out", c_void_p), ("block_prod", c_void_p),
+                ("block_state", c_void_p)]
 
 
 _P = POINTER
@@ -62,10 +64,10 @@ SIGNATURES = {
                              + [_P(BackwardState)]),
     "fss_block_rows": (c_int64, [c_int, c_int64, c_int64, c_int64, c_int]),
     "fss_seqpar_compose": (c_int, [_P(ScanCtx), c_int, c_int, c_int, c_int64, c_void_p, c_void_p]),
-    "fss_seqpar_fixup_forward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View),
-                                         c_void_p, c_void_p, c_int64]),
-    "fss_seqpar_fixup_backward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64] + [_P(View)] * 4
-                                  + [c_void_p, c_void_p, c_void_p, c_int64]),
+    "fss_seqpar_fixup_forward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View),
+                                         c_void_p, c_void_p, c_void_p, c_int64]),
+    "fss_seqpar_fixup_backward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64] + [_P(View)] * 5
+                                  + [c_void_p, c_void_p, c_void_p, c_void_p, c_int64]),
     "fss_scan_forward_noalloc": (c_int, [c_int, c_int, c_void_p, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View)]),
 }
 

@@ -101,7 +101,7 @@ static int chunked_forward(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64
     const int64_t cols = B * D;
     chunk_compose<false><<<(unsigned)ceil_div(cols, 128), 128, 0, stream>>>(
         g, wsP, wsC, (st && cont) ? st->h_in : nullptr, st ? st->h_last : nullptr,
-        st ? st->prod : nullptr, st ? st->block_prod : nullptr);
+        st ? st->prod : nullptr, st ? st->block_prod : nullptr, st ? st->block_state : nullptr);
     chunk_scan_forward<T, V><<<blocks, kThreads, 0, stream>>>(g, a, b, out, wsC, cont);
     return launch_check("chunked forward launch");
 }
@@ -125,7 +125,7 @@ static int chunked_backward(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int6
     const int64_t cols = B * D;
     chunk_compose<true><<<(unsigned)ceil_div(cols, 128), 128, 0, stream>>>(
         g, wsP, wsC, st ? st->u_in : nullptr, st ? st->u_out : nullptr, nullptr,
-        st ? st->block_prod : nullptr);
+        st ? st->block_prod : nullptr, st ? st->block_state : nullptr);
     chunk_scan_backward<T, V><<<blocks, kThreads, 0, stream>>>(
         g, a, hh, gr, make_view<T>(dalpha), make_view<T>(dbeta), wsC,
         (st && cont) ? st->h_prev : nullptr, cont);
@@ -301,68 +301,71 @@ static seqpar::Geometry fixup_geometry(int64_t B, int64_t T, int64_t D, int64_t 
 
 template <typename T, int V>
 static int fixup_forward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *alpha,
-                                const fss_view *h, const float *carry_in, const float *bp, int64_t R) {
+                                const fss_view *beta, const fss_view *h, const float *carry_in, const float *bp,
+                                const float *bs, int64_t R) {
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
     seqpar::fixup_forward<T, V><<<(unsigned)(g.vblocks * g.NB * B), seqpar::kThreads, 0, (cudaStream_t)ctx->stream>>>(
-        g, make_view<const T>(alpha), make_view<T>(h), carry_in, bp);
+        g, make_view<const T>(alpha), make_view<const T>(beta), make_view<T>(h), carry_in, bp, bs);
     return launch_check("seqpar forward fix-up launch");
 }
 
 template <typename T, int V>
 static int fixup_backward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *alpha,
-                                 const fss_view *h, const fss_view *da, const fss_view *db, const float *u_in,
-                                 const float *h_prev, const float *bp, int64_t R) {
+                                 const fss_view *h, const fss_view *grad, const fss_view *da, const fss_view *db,
+                                 const float *u_in, const float *h_prev, const float *bp, const float *bs, int64_t R) {
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
     seqpar::fixup_backward<T, V><<<(unsigned)(g.vblocks * g.NB * B), seqpar::kThreads, 0, (cudaStream_t)ctx->stream>>>(
-        g, make_view<const T>(alpha), make_view<const T>(h), make_view<T>(da), make_view<T>(db), u_in, h_prev, bp);
+        g, make_view<const T>(alpha), make_view<const T>(h), make_view<const T>(grad), make_view<T>(da),
+        make_view<T>(db), u_in, h_prev, bp, bs, (ctx->flags & FSS_FLAG_CONTINUATION) != 0);
     return launch_check("seqpar backward fix-up launch");
 }
 }  // namespace fss
 
 FSS_API int fss_seqpar_fixup_forward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
-                                     const fss_view *alpha, const fss_view *h, const float *carry_in,
-                                     const float *block_prod, int64_t block_rows) {
+                                     const fss_view *alpha, const fss_view *beta, const fss_view *h,
+                                     const float *carry_in, const float *block_prod, const float *block_state,
+                                     int64_t block_rows) {
     int rc;
     if ((rc = check_ctx(ctx))) return rc;
     if ((rc = check_shape(dtype, B, T, D))) return rc;
     if (B == 0 || T == 0 || D == 0) return FSS_OK;
-    if ((rc = check_view(alpha, B, T, D)) || (rc = check_view(h, B, T, D))) return rc;
-    if (!carry_in || !block_prod) return FSS_E_NULL;
+    for (const fss_view *v : {alpha, beta, h})
+        if ((rc = check_view(v, B, T, D))) return rc;
+    if (!carry_in || !block_prod || !block_state) return FSS_E_NULL;
     if (block_rows < 1) return FSS_E_SHAPE;
     DeviceGuard guard(ctx->device);
     if (guard.error) return guard.error;
     if (dtype == FSS_DTYPE_BF16) {
-        if (chunked::vector_ok<bf16>(D, {alpha, h}))
-            return fixup_forward_launch<bf16, 8>(ctx, B, T, D, alpha, h, carry_in, block_prod, block_rows);
-        return fixup_forward_launch<bf16, 1>(ctx, B, T, D, alpha, h, carry_in, block_prod, block_rows);
+        if (chunked::vector_ok<bf16>(D, {alpha, beta, h}))
+            return fixup_forward_launch<bf16, 8>(ctx, B, T, D, alpha, beta, h, carry_in, block_prod, block_state, block_rows);
+        return fixup_forward_launch<bf16, 1>(ctx, B, T, D, alpha, beta, h, carry_in, block_prod, block_state, block_rows);
     }
-    if (chunked::vector_ok<float>(D, {alpha, h}))
-        return fixup_forward_launch<float, 4>(ctx, B, T, D, alpha, h, carry_in, block_prod, block_rows);
-    return fixup_forward_launch<float, 1>(ctx, B, T, D, alpha, h, carry_in, block_prod, block_rows);
+    if (chunked::vector_ok<float>(D, {alpha, beta, h}))
+        return fixup_forward_launch<float, 4>(ctx, B, T, D, alpha, beta, h, carry_in, block_prod, block_state, block_rows);
+    return fixup_forward_launch<float, 1>(ctx, B, T, D, alpha, beta, h, carry_in, block_prod, block_state, block_rows);
 }
 
 FSS_API int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
-                                      const fss_view *alpha, const fss_view *h, const fss_view *grad_alpha,
-                                      const fss_view *grad_beta, const float *u_in, const float *h_prev,
-                                      const float *block_prod, int64_t block_rows) {
+                                      const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
+                                      const fss_view *grad_alpha, const fss_view *grad_beta, const float *u_in,
+                                      const float *h_prev, const float *block_prod, const float *block_state,
+                                      int64_t block_rows) {
     int rc;
     if ((rc = check_ctx(ctx))) return rc;
     if ((rc = check_shape(dtype, B, T, D))) return rc;
     if (B == 0 || T == 0 || D == 0) return FSS_OK;
-    for (const fss_view *v : {alpha, h, grad_alpha, grad_beta})
+    for (const fss_view *v : {alpha, h, grad_out, grad_alpha, grad_beta})
         if ((rc = check_view(v, B, T, D))) return rc;
-    if (!u_in || !block_prod) return FSS_E_NULL;
+    if (!u_in || !block_prod || !block_state) return FSS_E_NULL;
     if (block_rows < 1) return FSS_E_SHAPE;
     DeviceGuard guard(ctx->device);
     if (guard.error) return guard.error;
-    if (dtype == FSS_DTYPE_BF16) {
-        if (chunked::vector_ok<bf16>(D, {alpha, h, grad_alpha, grad_beta}))
-            return fixup_backward_launch<bf16, 8>(ctx, B, T, D, alpha, h, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_rows);
-        return fixup_backward_launch<bf16, 1>(ctx, B, T, D, alpha, h, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_rows);
-    }
-    if (chunked::vector_ok<float>(D, {alpha, h, grad_alpha, grad_beta}))
-        return fixup_backward_launch<float, 4>(ctx, B, T, D, alpha, h, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_rows);
-    return fixup_backward_launch<float, 1>(ctx, B, T, D, alpha, h, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_rows);
+#define FSS_FIXB(TT, VV) fixup_backward_launch<TT, VV>(ctx, B, T, D, alpha, h, grad_out, grad_alpha, grad_beta, \
+                                                       u_in, h_prev, block_prod, block_state, block_rows)
+    if (dtype == FSS_DTYPE_BF16)
+        return chunked::vector_ok<bf16>(D, {alpha, h, grad_out, grad_alpha, grad_beta}) ? FSS_FIXB(bf16, 8) : FSS_FIXB(bf16, 1);
+    return chunked::vector_ok<float>(D, {alpha, h, grad_out, grad_alpha, grad_beta}) ? FSS_FIXB(float, 4) : FSS_FIXB(float, 1);
+#undef FSS_FIXB
 }
 
 #ifdef FSS_TRACE

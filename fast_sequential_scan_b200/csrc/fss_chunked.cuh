@@ -89,7 +89,8 @@ chunk_summary(Geometry g, View<const T> alpha, View<const T> other /* beta | gra
 template <bool kBackward>
 __global__ void chunk_compose(Geometry g, float *__restrict__ wsP, float *__restrict__ wsC,
                               const float *__restrict__ state_in, float *__restrict__ state_out,
-                              float *__restrict__ prod_out, float *__restrict__ block_prod) {
+                              float *__restrict__ prod_out, float *__restrict__ block_prod,
+                              float *__restrict__ block_state) {
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= g.B * g.D) return;
     const int64_t b = idx / g.D, d = idx % g.D;
@@ -105,6 +106,7 @@ __global__ void chunk_compose(Geometry g, float *__restrict__ wsP, float *__rest
         run *= p;
         wsP[o] = run;
         if (block_prod) block_prod[o] = run;
+        if (block_state) block_state[o] = carry;
     }
     if (state_out) state_out[idx] = carry;
     if (prod_out) prod_out[idx] = run;

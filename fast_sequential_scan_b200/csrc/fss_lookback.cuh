@@ -91,6 +91,7 @@ struct Params {
     float *state_out;        // forward h_last / backward u_out
     float *prod_out;         // forward prod
     float *block_prod;       // [B, S, D]
+    float *block_state;      // [B, S, D]
     const float *h_prev;     // backward only
     int continuation;
     int64_t grid;            // CTAs of the launch, and grid = grid_q * ncols + grid_r
@@ -221,6 +222,7 @@ template <> struct Lane<bf16> {
     using Raw = uint2;
     using VecF = float4;
     static __device__ __forceinline__ Raw zero() { return make_uint2(0u, 0u); }
+    static __device__ __forceinline__ Raw one() { return make_uint2(0x3f803f80u, 0x3f803f80u); }
     static __device__ __forceinline__ void unpack(const Raw &r, float (&x)[4]) {
         x[0] = __uint_as_float(r.x << 16); x[1] = __uint_as_float(r.x & 0xffff0000u);
         x[2] = __uint_as_float(r.y << 16); x[3] = __uint_as_float(r.y & 0xffff0000u);
@@ -236,6 +238,7 @@ template <> struct Lane<float> {
     using Raw = float2;
     using VecF = float2;
     static __device__ __forceinline__ Raw zero() { return make_float2(0.0f, 0.0f); }
+    static __device__ __forceinline__ Raw one() { return make_float2(1.0f, 1.0f); }
     static __device__ __forceinline__ void unpack(const Raw &r, float (&x)[2]) { x[0] = r.x; x[1] = r.y; }
     static __device__ __forceinline__ Raw pack(const float (&x)[2]) { return make_float2(x[0], x[1]); }
 };
@@ -634,6 +637,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                     float *bp = p.block_prod + ((int64_t)b * p.S + blk) * p.D + dch;
 #pragma unroll
                     for (int v = 0; v < V; ++v) bp[v] = out[kProd ? V + v : v];
+                    if (p.block_state) {
+                        float *bs = p.block_state + ((int64_t)b * p.S + blk) * p.D + dch;
+#pragma unroll
+                        for (int v = 0; v < V; ++v) bs[v] = out[v];
+                    }
                 }
                 if (s + 1 == (int32_t)p.S) {
 #pragma unroll
@@ -655,7 +663,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         it.init(p, first);
         for (int64_t i = 0; i < n_my; ++i) {
             const int st = (int)(i % kStages), g = (int)(i % kGens);
-            const bool head = (it.template row0<kBackward>(p) == 0) && (warp == 0) && !p.continuation;
+            const int32_t row0 = it.template row0<kBackward>(p);
+            const bool head = (row0 == 0) && (warp == 0) && !p.continuation;
+            // rows of this warp that exist in the sequence (fewer than kR only in the last row block)
+            const int64_t left = p.T - row0 - (int64_t)warp * kR;
+            const int nvalid = left >= kR ? kR : (left > 0 ? (int)left : 0);
             it.advance(p);
             if (i >= kGens) {      // the summary buffers of this generation are free once pass 2 of unit i-kGens is done
                 const int64_t o = i - kGens;
@@ -667,6 +679,12 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             const Raw *x_t = reinterpret_cast<const Raw *>(smem_raw + st * SM::kStageBytes + kTileBytes + lane_off);
             // row 0 of the whole sequence: alpha_0 is not part of the recurrence
             if (head) a_t[0] = Lane<T>::zero();
+            // rows past the end of the sequence arrive zero-filled; alpha = 1 (beta, grad = 0) makes
+            // them the identity for both passes, so the state after the tile is the state after
+            // the last real row
+            if (nvalid < kR) {
+                for (int r = nvalid; r < kR; ++r) a_t[r * kRowStride] = Lane<T>::one();
+            }
             float P[V], C[V];
 #pragma unroll
             for (int v = 0; v < V; ++v) { P[v] = 1.0f; C[v] = 0.0f; }
@@ -955,6 +973,7 @@ inline int forward(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t
         p.state_out = st->h_last;
         p.prod_out = st->prod;
         p.block_prod = st->block_prod;
+        p.block_state = st->block_state;
     }
     if (p.prod_out || p.block_prod)
         return launch<T, false, true>(ctx, ws, B, Tn, D, alpha, beta, nullptr, h, nullptr, p, err_text);
@@ -971,6 +990,7 @@ inline int backward(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_
         p.state_in = st->u_in;
         p.state_out = st->u_out;
         p.block_prod = st->block_prod;
+        p.block_state = st->block_state;
         p.h_prev = cont ? st->h_prev : nullptr;
     }
     if (p.block_prod)

@@ -70,7 +70,7 @@ int run(cudaStream_t stream, float *scratch, int64_t B, int64_t Tn, int64_t D, c
     auto b = make_view<const T>(beta);
     chunk_summary<T, V, false><<<blocks, kThreads, 0, stream>>>(g, a, b, wsP, wsC, false);
     chunk_compose<false><<<(unsigned)ceil_div(B * D, 128), 128, 0, stream>>>(g, wsP, wsC, nullptr, nullptr,
-                                                                           nullptr, nullptr);
+                                                                           nullptr, nullptr, nullptr);
     chunk_scan_forward<T, V><<<blocks, kThreads, 0, stream>>>(g, a, b, make_view<T>(h), wsC, false);
     return cudaGetLastError() == cudaSuccess ? FSS_OK : FSS_E_LAUNCH;
 }

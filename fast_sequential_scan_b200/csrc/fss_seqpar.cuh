@@ -46,77 +46,80 @@ __device__ __forceinline__ void decode_block(const Geometry &g, int64_t &vb, int
     b = id / g.NB;
 }
 
-// h_t += (a_0 ... a_t) * carry_in
+// Re-scan of the blocks that the entering state still reaches (forward).
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
-fixup_forward(Geometry g, View<const T> alpha, View<T> h, const float *__restrict__ carry_in,
-              const float *__restrict__ block_prod) {
+fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, const float *__restrict__ carry_in,
+              const float *__restrict__ block_prod, const float *__restrict__ block_state) {
     int64_t vb, j, b;
     decode_block(g, vb, j, b);
     const int64_t v = vb * kThreads + threadIdx.x;
     if (v >= g.nvec) return;
     const int64_t d0 = v * V;
-    float w[V];
+    float st[V];
     bool live = false;
 #pragma unroll
     for (int i = 0; i < V; ++i) {
-        const float q = (j == 0) ? 1.0f : block_prod[(b * g.NB + j - 1) * g.D + d0 + i];
-        w[i] = q * carry_in[b * g.D + d0 + i];
-        live |= (w[i] != 0.0f);
+        const int64_t o = (b * g.NB + j - 1) * g.D + d0 + i;
+        const float w = (j == 0 ? 1.0f : block_prod[o]) * carry_in[b * g.D + d0 + i];
+        st[i] = (j == 0 ? 0.0f : block_state[o]) + w;
+        live |= (w != 0.0f);
     }
-    if (!live) return;   // every later term is exactly zero: nothing to add
+    if (!live) return;   // the zero-state result of this block is already exact
     const int64_t r0 = j * g.R, r1 = min(g.T, r0 + g.R);
 #pragma unroll 4
     for (int64_t t = r0; t < r1; ++t) {
         float a[V], x[V];
         Frag<T, V>::load(alpha.row(b, t) + d0, a);
-        FragRW<T, V>::load(h.row(b, t) + d0, x);
+        Frag<T, V>::load(beta.row(b, t) + d0, x);
 #pragma unroll
-        for (int i = 0; i < V; ++i) { w[i] *= a[i]; x[i] += w[i]; }
-        Frag<T, V>::store(h.row(b, t) + d0, x);
+        for (int i = 0; i < V; ++i) st[i] = fmaf(a[i], st[i], x[i]);
+        Frag<T, V>::store(h.row(b, t) + d0, st);
     }
 }
 
-// dbeta_t += R_t*u_in ; dalpha_t += R_t*u_in*h_{t-1} ;  R_t = a_{t+1} ... a_{T-1}
+// Re-scan of the blocks that the arriving u still reaches (backward).
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)
-fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<T> dalpha, View<T> dbeta,
-               const float *__restrict__ u_in, const float *__restrict__ h_prev,
-               const float *__restrict__ block_prod) {
+fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> grad, View<T> dalpha,
+               View<T> dbeta, const float *__restrict__ u_in, const float *__restrict__ h_prev,
+               const float *__restrict__ block_prod, const float *__restrict__ block_state, bool continuation) {
     int64_t vb, j, b;
     decode_block(g, vb, j, b);
     const int64_t v = vb * kThreads + threadIdx.x;
     if (v >= g.nvec) return;
     const int64_t d0 = v * V;
-    float w[V];
+    float u[V];
     bool live = false;
 #pragma unroll
     for (int i = 0; i < V; ++i) {
-        const float q = (j == g.NB - 1) ? 1.0f : block_prod[(b * g.NB + j + 1) * g.D + d0 + i];
-        w[i] = q * u_in[b * g.D + d0 + i];
-        live |= (w[i] != 0.0f);
+        const int64_t o = (b * g.NB + j + 1) * g.D + d0 + i;
+        const bool lastb = j == g.NB - 1;
+        const float w = (lastb ? 1.0f : block_prod[o]) * u_in[b * g.D + d0 + i];
+        u[i] = (lastb ? 0.0f : block_state[o]) + w;
+        live |= (w != 0.0f);
     }
     if (!live) return;
     const int64_t r0 = j * g.R, r1 = min(g.T, r0 + g.R);
 #pragma unroll 4
     for (int64_t t = r1 - 1; t >= r0; --t) {
-        float a[V], hp[V], da[V], db[V];
+        float a[V], gr[V], hp[V], da[V], dh[V];
         Frag<T, V>::load(alpha.row(b, t) + d0, a);
+        Frag<T, V>::load(grad.row(b, t) + d0, gr);
         if (t > 0) {
             Frag<T, V>::load(h.row(b, t - 1) + d0, hp);
         } else {
 #pragma unroll
-            for (int i = 0; i < V; ++i) hp[i] = h_prev ? h_prev[b * g.D + d0 + i] : 0.0f;
+            for (int i = 0; i < V; ++i) hp[i] = (continuation && h_prev) ? h_prev[b * g.D + d0 + i] : 0.0f;
         }
-        FragRW<T, V>::load(dalpha.row(b, t) + d0, da);
-        FragRW<T, V>::load(dbeta.row(b, t) + d0, db);
+        const bool head = (t == 0) && !continuation;
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            db[i] += w[i];
-            da[i] = fmaf(w[i], hp[i], da[i]);
-            w[i] *= a[i];
+            dh[i] = gr[i] + u[i];
+            da[i] = head ? 0.0f : dh[i] * hp[i];
+            u[i] = (head ? 0.0f : a[i]) * dh[i];
         }
-        Frag<T, V>::store(dbeta.row(b, t) + d0, db);
+        Frag<T, V>::store(dbeta.row(b, t) + d0, dh);
         Frag<T, V>::store(dalpha.row(b, t) + d0, da);
     }
 }

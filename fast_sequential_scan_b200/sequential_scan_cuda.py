@@ -79,8 +79,16 @@ def _vec(t: Optional[torch.Tensor], B: int, D: int, name: str) -> Optional[int]:
     return t.data_ptr()
 
 
+def _blocks(t: Optional[torch.Tensor], name: str) -> Optional[int]:
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+        raise RuntimeError(f"{name}: expected a contiguous fp32 CUDA tensor [B, nblocks, D]")
+    return t.data_ptr()
+
+
 def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_last=None,
-                 prod=None, block_prod=None) -> None:
+                 prod=None, block_prod=None, block_state=None) -> None:
     """h <- scan(alpha, beta) into a caller-owned tensor, with the optional boundary state."""
     dtype = alpha.dtype
     if dtype not in _DTYPES:
@@ -99,14 +107,10 @@ def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_
         ws = workspace.get(alpha.device, L.fss_workspace_bytes(B, T, D, _DTYPES[dtype]))
         ctx = _ctx(alpha.device, ws, algo, _lib.FLAG_CONTINUATION if continuation else 0)
         state = None
-        if any(x is not None for x in (h_in, h_last, prod, block_prod)):
-            bp = None
-            if block_prod is not None:
-                if block_prod.dtype != torch.float32 or not block_prod.is_contiguous():
-                    raise RuntimeError("block_prod: expected contiguous fp32")
-                bp = block_prod.data_ptr()
+        if any(x is not None for x in (h_in, h_last, prod, block_prod, block_state)):
             state = _lib.ForwardState(_vec(h_in, B, D, "h_in"), _vec(h_last, B, D, "h_last"),
-                                      _vec(prod, B, D, "prod"), bp)
+                                      _vec(prod, B, D, "prod"), _blocks(block_prod, "block_prod"),
+                                      _blocks(block_state, "block_state"))
         va, vb, vh = _view(a), _view(b), _view(h)
         rc = L.fss_scan_forward_ex(ctypes.byref(ctx), _DTYPES[dtype], B, T, D, ctypes.byref(va),
                                    ctypes.byref(vb), ctypes.byref(vh),
@@ -115,7 +119,7 @@ def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_
 
 
 def backward_into(alpha, h, grad_out, grad_alpha, grad_beta, *, algo=None, continuation=False,
-                  u_in=None, h_prev=None, u_out=None, block_prod=None) -> None:
+                  u_in=None, h_prev=None, u_out=None, block_prod=None, block_state=None) -> None:
     dtype = alpha.dtype
     if dtype not in _DTYPES:
         raise RuntimeError(f"alpha_saved: unsupported dtype {dtype} (bf16 or fp32)")
@@ -136,14 +140,10 @@ def backward_into(alpha, h, grad_out, grad_alpha, grad_beta, *, algo=None, conti
         ws = workspace.get(alpha.device, L.fss_workspace_bytes(B, T, D, _DTYPES[dtype]))
         ctx = _ctx(alpha.device, ws, algo, _lib.FLAG_CONTINUATION if continuation else 0)
         state = None
-        if any(x is not None for x in (u_in, h_prev, u_out, block_prod)):
-            bp = None
-            if block_prod is not None:
-                if block_prod.dtype != torch.float32 or not block_prod.is_contiguous():
-                    raise RuntimeError("block_prod: expected contiguous fp32")
-                bp = block_prod.data_ptr()
+        if any(x is not None for x in (u_in, h_prev, u_out, block_prod, block_state)):
             state = _lib.BackwardState(_vec(u_in, B, D, "u_in"), _vec(h_prev, B, D, "h_prev"),
-                                       _vec(u_out, B, D, "u_out"), bp)
+                                       _vec(u_out, B, D, "u_out"), _blocks(block_prod, "block_prod"),
+                                       _blocks(block_state, "block_state"))
         views = [_view(t) for t in (a, hh, g, grad_alpha, grad_beta)]
         rc = L.fss_scan_backward_ex(ctypes.byref(ctx), _DTYPES[dtype], B, T, D,
                                     *[ctypes.byref(v) for v in views],
@@ -185,3 +185,68 @@ def scan_forward_half(alpha: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
 def scan_backward_half(alpha_saved, h_saved, grad_out) -> List[torch.Tensor]:
     """bf16 backward (reference: csrc/sequential_scan_kernel.cu:189-268)."""
     return _backward(alpha_saved, h_saved, grad_out, torch.bfloat16)
+
+
+# ---------------------------------------------------------------------------------------------
+# Sequence-parallel pieces (no counterpart in the reference, which never splits the sequence)
+
+def block_rows(dtype: torch.dtype, B: int, T: int, D: int, algo: Optional[int] = None) -> int:
+    """Rows per block of the ``block_prod`` outputs for this problem."""
+    a = default_algo() if algo is None else algo
+    return int(_lib.lib().fss_block_rows(_DTYPES[dtype], B, T, D, a))
+
+
+def _plain_ctx(device: torch.device, algo: Optional[int] = None):
+    ws = workspace.get(device, 1 << 16)
+    return _ctx(device, ws, algo)
+
+
+def seqpar_compose(pc: torch.Tensor, rank: int, backward: bool) -> torch.Tensor:
+    """Fold the gathered ``[world, 2, n]`` (product, state) vectors into what enters ``rank``."""
+    if pc.dtype != torch.float32 or not pc.is_cuda or not pc.is_contiguous() or pc.dim() != 3 or pc.shape[1] != 2:
+        raise RuntimeError("pc: expected a contiguous fp32 CUDA tensor [world, 2, n]")
+    world, _, n = pc.shape
+    out = torch.empty(n, dtype=torch.float32, device=pc.device)
+    with torch.cuda.device(pc.device):
+        ctx = _plain_ctx(pc.device)
+        rc = _lib.lib().fss_seqpar_compose(ctypes.byref(ctx), int(backward), world, rank, n,
+                                           pc.data_ptr(), out.data_ptr())
+    _lib.check(rc, "fss_seqpar_compose")
+    return out
+
+
+def seqpar_fixup_forward(alpha, beta, h, carry_in, block_prod, block_state, rows_per_block: int) -> None:
+    """In place: re-scan the blocks of a zero-state forward scan that ``carry_in`` still reaches."""
+    dtype = alpha.dtype
+    _check_tensor("alpha", alpha, None, dtype)
+    _check_tensor("beta", beta, alpha, dtype)
+    _check_tensor("h", h, alpha, dtype)
+    B, T, D = alpha.shape
+    a, b = _rowwise(alpha), _rowwise(beta)
+    va, vb, vh = _view(a), _view(b), _view(h)
+    with torch.cuda.device(alpha.device):
+        ws = workspace.get(alpha.device, 1 << 16)
+        ctx = _ctx(alpha.device, ws, None, _lib.FLAG_CONTINUATION)
+        rc = _lib.lib().fss_seqpar_fixup_forward(ctypes.byref(ctx), _DTYPES[dtype], B, T, D, ctypes.byref(va),
+                                                 ctypes.byref(vb), ctypes.byref(vh), _vec(carry_in, B, D, "carry_in"),
+                                                 _blocks(block_prod, "block_prod"), _blocks(block_state, "block_state"),
+                                                 rows_per_block)
+    _lib.check(rc, "fss_seqpar_fixup_forward")
+
+
+def seqpar_fixup_backward(alpha, h, grad_out, grad_alpha, grad_beta, u_in, h_prev, block_prod, block_state,
+                          rows_per_block: int, continuation: bool) -> None:
+    """In place: re-scan the blocks of a zero-state backward scan that ``u_in`` still reaches."""
+    dtype = alpha.dtype
+    B, T, D = alpha.shape
+    a, hh, g = _rowwise(alpha), _rowwise(h), _rowwise(grad_out)
+    views = [_view(t) for t in (a, hh, g, grad_alpha, grad_beta)]
+    with torch.cuda.device(alpha.device):
+        ws = workspace.get(alpha.device, 1 << 16)
+        ctx = _ctx(alpha.device, ws, None, _lib.FLAG_CONTINUATION if continuation else 0)
+        rc = _lib.lib().fss_seqpar_fixup_backward(ctypes.byref(ctx), _DTYPES[dtype], B, T, D,
+                                                  *[ctypes.byref(v) for v in views], _vec(u_in, B, D, "u_in"),
+                                                  _vec(h_prev, B, D, "h_prev") if h_prev is not None else None,
+                                                  _blocks(block_prod, "block_prod"),
+                                                  _blocks(block_state, "block_state"), rows_per_block)
+    _lib.check(rc, "fss_seqpar_fixup_backward")

@@ -96,6 +96,8 @@ typedef struct fss_forward_state {
     float *prod;       /* out: product of alpha over all rows (0 without FSS_FLAG_CONTINUATION) */
     float *block_prod; /* out, [B, nblocks, D]: product of alpha over rows 0..(j+1)*R-1 for every
                           block j of R = fss_block_rows() rows; feeds fss_seqpar_fixup_forward  */
+    float *block_state; /* out, [B, nblocks, D]: unrounded state after row (j+1)*R-1 (needs
+                          block_prod as well)                                                   */
 } fss_forward_state;
 
 typedef struct fss_backward_state {
@@ -104,6 +106,7 @@ typedef struct fss_backward_state {
     float *u_out;        /* out: a_0*dh_0, what these rows hand to the rows before them         */
     float *block_prod;   /* out, [B, nblocks, D]: product of alpha over rows j*R..T-1 for every
                             block j of R = fss_block_rows() rows; feeds fss_seqpar_fixup_backward */
+    float *block_state;  /* out, [B, nblocks, D]: u = a*dh handed on by row j*R (needs block_prod) */
 } fss_backward_state;
 
 /* ---- library information ------------------------------------------------------------- */
@@ -160,19 +163,24 @@ int64_t fss_block_rows(int dtype, int64_t B, int64_t T, int64_t D, int algo);
  *             ranks rank+1..world-1.  One small launch on ctx->stream. */
 int fss_seqpar_compose(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n,
                        const float *pc, float *carry_in);
-/* Add the effect of carry_in to a zero-state forward scan:  h_t += (a_0*...*a_t) * carry_in.
- * block_prod / block_rows are what the zero-state scan wrote; a block whose entering product has
- * underflowed to exactly zero is skipped, which changes no bit of the result. */
+/* Correct a zero-state forward scan for the state carry_in that really enters row 0: every block
+ * whose entering product times carry_in is not exactly zero is re-scanned from its true entering
+ * state  block_state[j-1] + block_prod[j-1]*carry_in  (one rounding per stored value, like the
+ * undivided scan); all other blocks already hold the exact result and are skipped.  block_prod,
+ * block_state, block_rows are what the zero-state scan wrote.  Needs FSS_FLAG_CONTINUATION. */
 int fss_seqpar_fixup_forward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
-                             const fss_view *alpha, const fss_view *h, const float *carry_in,
-                             const float *block_prod, int64_t block_rows);
-/* Add the effect of u_in (entering after the last row) to a zero-state backward scan:
- *   dbeta_t += R_t*u_in ; dalpha_t += R_t*u_in*h_{t-1},  R_t = a_{t+1}*...*a_{T-1}.
- * h_prev is h_{-1} (NULL = 0). */
+                             const fss_view *alpha, const fss_view *beta, const fss_view *h,
+                             const float *carry_in, const float *block_prod, const float *block_state,
+                             int64_t block_rows);
+/* The same for the backward scan and the u_in that really arrives after the last row: blocks
+ * whose leaving product times u_in is non-zero are re-scanned from
+ * block_state[j+1] + block_prod[j+1]*u_in.  h_prev is h_{-1} (NULL = 0; used with
+ * FSS_FLAG_CONTINUATION, without it row 0 keeps dalpha_0 = 0). */
 int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
-                              const fss_view *alpha, const fss_view *h, const fss_view *grad_alpha,
-                              const fss_view *grad_beta, const float *u_in, const float *h_prev,
-                              const float *block_prod, int64_t block_rows);
+                              const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
+                              const fss_view *grad_alpha, const fss_view *grad_beta, const float *u_in,
+                              const float *h_prev, const float *block_prod, const float *block_state,
+                              int64_t block_rows);
 
 /* ---- a forward scan that allocates nothing ------------------------------------------------ */
 /* Has no counterpart in the reference.  It exists for callers that cannot obtain scratch memory

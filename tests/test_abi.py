@@ -30,7 +30,7 @@ def test_struct_layouts_match_the_header():
     from fast_sequential_scan_b200 import _lib
     assert ctypes.sizeof(_lib.View) == 24
     assert ctypes.sizeof(_lib.ScanCtx) == 48
-    assert ctypes.sizeof(_lib.ForwardState) == 32 and ctypes.sizeof(_lib.BackwardState) == 32
+    assert ctypes.sizeof(_lib.ForwardState) == 40 and ctypes.sizeof(_lib.BackwardState) == 40
 
 
 def test_error_strings_and_argument_checks_need_no_device():

@@ -276,3 +276,73 @@ def test_lookback_descriptors_survive_reuse_with_different_data(shape):
         r = oracle.mixed_error_ratio(h, ref, BF16_TOL)
         assert r <= 1.0, f"launch {it}: ratio {r}"
     pkg.check_status()
+
+
+@pytest.mark.parametrize("algo", ["chunked", "auto"])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_sequence_parallel_pieces_on_one_gpu(dtype, algo):
+    """The sequence-parallel protocol with its ranks played one after the other on one device:
+    zero-state local scans with products, the gathered (product, state) table, carry folding and
+    the fix-up kernels, forward and backward, against the undivided scan."""
+    from fast_sequential_scan_b200.distributed import NativeOps
+    dt = torch.bfloat16 if dtype == "bf16" else torch.float32
+    tol = BF16_TOL if dtype == "bf16" else F32_TOL
+    world, B, Tl, D = 4, 2, 3000, 256                 # 3000 rows per rank: partial last block
+    gen = torch.Generator(device="cuda").manual_seed(31)
+    shape = (B, world * Tl, D)
+    # bf16: the long-memory gates of configuration 5; fp32: shorter memory, so that fp32 round-off of
+    # fused vs unfused multiply-add over 12,000 rows stays inside the 1e-5 bound
+    lo, span = (0.9, 0.0999) if dtype == "bf16" else (0.5, 0.49)
+    a = (lo + span * torch.rand(shape, generator=gen, device="cuda")).to(dt)
+    b = torch.randn(shape, generator=gen, device="cuda").to(dt)
+    g = torch.randn(shape, generator=gen, device="cuda").to(dt)
+    ops = NativeOps(_algo_id(algo))
+    rows = [slice(r * Tl, (r + 1) * Tl) for r in range(world)]
+    # forward
+    loc = [ops.local_forward(a[:, rows[r]], b[:, rows[r]], continuation=r > 0) for r in range(world)]
+    pc = torch.stack([torch.stack([l[2].reshape(-1), l[1].reshape(-1)]) for l in loc]).contiguous()
+    hs, carries = [], []
+    for r in range(world):
+        h, _, _, blocks = loc[r]
+        carry = None
+        if r > 0:
+            carry = ops.compose(pc, r, backward=False).reshape(B, D)
+            ops.fixup_forward(a[:, rows[r]], b[:, rows[r]], h, carry, blocks)
+        hs.append(h); carries.append(carry)
+    h_all = torch.cat(hs, dim=1)
+    h_ref, _, _ = oracle.reference_values(a, b, None)
+    assert_parity(h_all, h_ref, tol, "sequence-parallel h")
+    # backward (uses the stored h of every rank, like the undivided backward uses the saved h)
+    bl = [ops.local_backward(a[:, rows[r]], hs[r], g[:, rows[r]], continuation=r > 0, h_prev=carries[r])
+          for r in range(world)]
+    pcb = torch.stack([torch.stack([loc[r][2].reshape(-1), bl[r][2].reshape(-1)]) for r in range(world)]).contiguous()
+    das, dbs = [], []
+    for r in range(world):
+        da, db, _, blocks = bl[r]
+        if r < world - 1:
+            u_in = ops.compose(pcb, r, backward=True).reshape(B, D)
+            ops.fixup_backward(a[:, rows[r]], hs[r], g[:, rows[r]], da, db, u_in, carries[r], blocks, r > 0)
+        das.append(da); dbs.append(db)
+    da_ref, db_ref = oracle.scan_backward_f32(a.float().cpu().numpy(), h_all.float().cpu().numpy(),
+                                              g.float().cpu().numpy())
+    assert_parity(torch.cat(dbs, dim=1), torch.from_numpy(db_ref), tol, "dbeta")
+    assert_parity(torch.cat(das, dim=1), torch.from_numpy(da_ref), tol, "dalpha")
+    import fast_sequential_scan_b200 as pkg
+    pkg.check_status()
+
+
+def test_boundary_state_vectors_continue_a_scan():
+    """h_in / h_last / u_in / u_out: scanning two halves with the state handed over equals one scan."""
+    _, native, _lib = _mods()
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    B, T, D = 2, 1000, 128
+    a = torch.rand(B, T, D, generator=gen, device="cuda") * 0.5 + 0.5
+    b = torch.randn(B, T, D, generator=gen, device="cuda")
+    for algo in ("chunked", "auto"):
+        full = torch.empty_like(a)
+        native.forward_into(a, b, full, algo=_algo_id(algo))
+        h1, h2 = torch.empty_like(a[:, :400]), torch.empty_like(a[:, 400:])
+        last = torch.empty(B, D, device="cuda")
+        native.forward_into(a[:, :400], b[:, :400], h1, algo=_algo_id(algo), h_last=last)
+        native.forward_into(a[:, 400:], b[:, 400:], h2, algo=_algo_id(algo), continuation=True, h_in=last)
+        assert torch.allclose(torch.cat([h1, h2], 1), full, rtol=1e-5, atol=1e-5), algo

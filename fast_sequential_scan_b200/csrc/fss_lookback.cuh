@@ -94,6 +94,7 @@ struct Params {
     float *block_state;      // [B, S, D]
     const float *h_prev;     // backward only
     int continuation;
+    int32_t tile_rows;       // rows per tile: 64 * split
     int64_t grid;            // CTAs of the launch, and grid = grid_q * ncols + grid_r
     int32_t grid_q, grid_r;
 
@@ -173,15 +174,15 @@ __device__ __forceinline__ uint32_t ld_volatile(const uint32_t *p) {
 __device__ __forceinline__ unsigned long long make_cell(float x, uint32_t tag) {
     return (unsigned long long)__float_as_uint(x) | ((unsigned long long)tag << 32);
 }
-// N floats as N/2 cell pairs; pair j of a tile's group sits at p[j*32] (one uint4 per lane)
-template <int N> struct PacketGroup {
+// N floats as N/2 cell pairs; pair j of a tile's group sits at p[j*kStride] (one uint4 per channel lane)
+template <int N, int kStride = 32> struct PacketGroup {
     static_assert(N % 2 == 0, "cells are moved in pairs");
     static constexpr int kPackets = N / 2;
     static __device__ __forceinline__ void store(uint4 *p, const float (&v)[N], uint32_t tag) {
 #pragma unroll
         for (int j = 0; j < kPackets; ++j)
             asm volatile("st.global.cg.v2.b64 [%0], {%1, %2};"
-                         ::"l"(p + j * 32), "l"(make_cell(v[2 * j], tag)), "l"(make_cell(v[2 * j + 1], tag)) : "memory");
+                         ::"l"(p + j * kStride), "l"(make_cell(v[2 * j], tag)), "l"(make_cell(v[2 * j + 1], tag)) : "memory");
     }
     // Issue the loads only: nothing here depends on the returned data, so the caller can keep
     // working (or wait on a barrier) while they are in flight, and decode() later.
@@ -190,7 +191,7 @@ template <int N> struct PacketGroup {
 #pragma unroll
         for (int j = 0; j < kPackets; ++j)
             asm volatile("ld.global.cg.v2.b64 {%0, %1}, [%2];"
-                         : "=l"(r.c[2 * j]), "=l"(r.c[2 * j + 1]) : "l"(p + j * 32) : "memory");
+                         : "=l"(r.c[2 * j]), "=l"(r.c[2 * j + 1]) : "l"(p + j * kStride) : "memory");
     }
     // true when every cell of the group carries `tag`
     static __device__ __forceinline__ bool decode(const Raw &r, float (&v)[N], uint32_t tag) {
@@ -297,7 +298,7 @@ struct TileIter {
     __device__ __forceinline__ int32_t batch(const Params &p) const { return col / (int32_t)p.ncg; }
     __device__ __forceinline__ int32_t cgroup(const Params &p) const { return col % (int32_t)p.ncg; }
     template <bool kBackward> __device__ __forceinline__ int32_t row0(const Params &p) const {
-        return (kBackward ? ((int32_t)p.S - 1 - s) : s) * kTc;
+        return (kBackward ? ((int32_t)p.S - 1 - s) : s) * p.tile_rows;
     }
 };
 
@@ -306,7 +307,7 @@ struct TileIter {
 // Backward: (alpha, grad, h shifted one row down) are loaded; dbeta is stored from grad's slot,
 // dalpha from h's slot.  Results are written in place in shared memory and leave through TMA
 // stores issued by the producer, so the consumer warps never stall on the global write path.
-template <typename T, bool kBackward, bool kProd>
+template <typename T, bool kBackward, bool kProd, int kSp>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant__ CUtensorMap map_x,
             const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_out0,
@@ -315,7 +316,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     constexpr int kStages = kBackward ? kStagesBwd : kStagesFwd;
     using SM = Smem<kTensors, kStages>;
     constexpr int V = Cfg<T>::V;
-    constexpr int Dc = Cfg<T>::Dc;
+    // Tile shape: kSp = 1: 64 rows x 256 bytes; 2: 128 x 128; 4: 256 x 64 (same 16 KiB).  A warp then
+    // covers kSp row groups of kR rows at once: lane = (row group q, channel lane cl).
+    constexpr int LPG = 32 / kSp;                 // lanes per row group
+    constexpr int Dc = Cfg<T>::Dc / kSp;          // channels per tile
+    constexpr int kRowB = kRowBytes / kSp;        // bytes of a tile row
     using VecF = typename Lane<T>::VecF;          // V floats as one shared-memory word group
 
     // TMA tiles want 128-byte aligned shared addresses: align the dynamic window by hand
@@ -338,6 +343,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     auto agg_at = [&](int g, int w, int which, int ln) -> VecF & { return agg[((g * kW + w) * 2 + which) * 32 + ln]; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q = lane / LPG, cl = lane % LPG;
     const int64_t first = blockIdx.x;
     const int64_t n_my = first < p.ntiles ? (p.ntiles - first + p.grid - 1) / p.grid : 0;
 
@@ -408,8 +414,9 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // has produced them, leaves it in shared memory for the look-back warps and publishes it
         // at once: successors of this tile can then fold it without waiting for the tile's own
         // carry resolution.  This warp never waits on anything outside its CTA.
-        using AggPk = PacketGroup<2 * V>;
-        constexpr int kTilePackets = (AggPk::kPackets + PacketGroup<(kProd ? 2 : 1) * V>::kPackets) * 32;
+        using AggPk = PacketGroup<2 * V, LPG>;
+        constexpr int kTilePackets = (AggPk::kPackets + PacketGroup<(kProd ? 2 : 1) * V>::kPackets) * LPG;
+        constexpr int kGroups = kW * kSp;          // row groups of a tile, in row order
         const uint32_t tag_agg = (epoch << 2) | kStateAggregate;
         TileIter it;
         it.init(p, first);
@@ -419,26 +426,29 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             const bool last_block = it.s + 1 == (int32_t)p.S;
             it.advance(p);
             if (!ctl.wait(bar_agg(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
-            VecF aP[kW], aC[kW];
-#pragma unroll
-            for (int w = 0; w < kW; ++w) { aP[w] = agg_at(g, w, 0, lane); aC[w] = agg_at(g, w, 1, lane); }
             float pc[2 * V];
 #pragma unroll
             for (int v = 0; v < V; ++v) { pc[v] = 1.0f; pc[V + v] = 0.0f; }
-            // every warp's slot receives the map of the warps BEFORE it (its exclusive prefix)
+            // every row group's slot receives the map of the groups BEFORE it (its exclusive prefix);
+            // all lanes with the same channel lane fold the same values, each writes its own slots
 #pragma unroll
-            for (int j = 0; j < kW; ++j) {
-                const int w = kBackward ? kW - 1 - j : j;
-                VecF ep, ec;
+            for (int j = 0; j < kGroups; ++j) {
+                const int gamma = kBackward ? kGroups - 1 - j : j;
+                const int w = gamma / kSp, src = (gamma % kSp) * LPG + cl;
+                const VecF ap = agg_at(g, w, 0, src), ac = agg_at(g, w, 1, src);
+                if (kSp > 1) __syncwarp();          // every lane has read the slot before its owner rewrites it
+                if (gamma % kSp == q) {
+                    VecF ep, ec;
+#pragma unroll
+                    for (int v = 0; v < V; ++v) { vec_set(ep, v, pc[v]); vec_set(ec, v, pc[V + v]); }
+                    agg_at(g, w, 0, lane) = ep;
+                    agg_at(g, w, 1, lane) = ec;
+                }
 #pragma unroll
                 for (int v = 0; v < V; ++v) {
-                    vec_set(ep, v, pc[v]);
-                    vec_set(ec, v, pc[V + v]);
-                    pc[V + v] = fmaf(vec_get(aP[w], v), pc[V + v], vec_get(aC[w], v));
-                    pc[v] *= vec_get(aP[w], v);
+                    pc[V + v] = fmaf(vec_get(ap, v), pc[V + v], vec_get(ac, v));
+                    pc[v] *= vec_get(ap, v);
                 }
-                agg_at(g, w, 0, lane) = ep;
-                agg_at(g, w, 1, lane) = ec;
             }
             VecF sp, sc;
 #pragma unroll
@@ -447,7 +457,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             sum_at(g, 1, lane) = sc;
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_sum(g));
-            if (!last_block) AggPk::store(p.packets + k * kTilePackets + lane, pc, tag_agg);
+            if (!last_block && q == 0) AggPk::store(p.packets + k * kTilePackets + cl, pc, tag_agg);
             FSS_TRACE_EV(i, kEvSum);
         }
     } else if (warp >= kLookbackWarp0) {
@@ -455,15 +465,15 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // kLookbackWarps warps share the work units round-robin, so several carry resolutions
         // (each a few L2 round trips) are in flight per CTA.
         constexpr int NI = kProd ? 2 * V : V;          // floats of an inclusive descriptor
-        using AggPk = PacketGroup<2 * V>;              // (P, C) of the tile scanned from zero
-        using IncPk = PacketGroup<NI>;                 // state after the tile (and product up to it)
-        constexpr int kTilePackets = (AggPk::kPackets + IncPk::kPackets) * 32;
+        using AggPk = PacketGroup<2 * V, LPG>;         // (P, C) of the tile scanned from zero
+        using IncPk = PacketGroup<NI, LPG>;                 // state after the tile (and product up to it)
+        constexpr int kTilePackets = (AggPk::kPackets + IncPk::kPackets) * LPG;
         const uint32_t tag_agg = (epoch << 2) | kStateAggregate;
         const uint32_t tag_inc = (epoch << 2) | kStateInclusive;
         const int lb = warp - kLookbackWarp0;
-        const int ch = lane * V;    // first channel of this lane inside the tile
-        auto agg_packets = [&](int64_t k) { return p.packets + k * kTilePackets + lane; };
-        auto inc_packets = [&](int64_t k) { return p.packets + k * kTilePackets + AggPk::kPackets * 32 + lane; };
+        const int ch = cl * V;      // first channel of this lane inside the tile
+        auto agg_packets = [&](int64_t k) { return p.packets + k * kTilePackets + cl; };
+        auto inc_packets = [&](int64_t k) { return p.packets + k * kTilePackets + AggPk::kPackets * LPG + cl; };
 
         TileIter it;
         it.init(p, first);
@@ -628,10 +638,10 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 if (kProd) out[kProd ? V + v : v] = Pt[v] * pin[v];
             }
             FSS_TRACE_EV(i, kEvLbE);
-            if (s + 1 < (int32_t)p.S) IncPk::store(inc_packets(k), out, tag_inc);
+            if (s + 1 < (int32_t)p.S && q == 0) IncPk::store(inc_packets(k), out, tag_inc);
             FSS_TRACE_EV(i, kEvLbC);
 
-            if (ch_ok) {
+            if (ch_ok && q == 0) {
                 if (kProd && p.block_prod) {
                     const int64_t blk = kBackward ? (p.S - 1 - s) : s;
                     float *bp = p.block_prod + ((int64_t)b * p.S + blk) * p.D + dch;
@@ -657,16 +667,17 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // Scans this warp's rows of every unit from a zero state as soon as the tile has landed
         // and leaves (P, C); never waits for a carry, only for the summary buffers to be free.
         using Raw = typename Lane<T>::Raw;
-        constexpr int kRowStride = kRowBytes / (int)sizeof(Raw);
-        const uint32_t lane_off = (uint32_t)(warp * kR) * kRowBytes + (uint32_t)lane * kLaneBytes;
+        constexpr int kRowStride = kRowB / (int)sizeof(Raw);
+        const int grp = warp * kSp + q;            // this lane's row group inside the tile
+        const uint32_t lane_off = (uint32_t)(grp * kR) * kRowB + (uint32_t)cl * kLaneBytes;
         TileIter it;
         it.init(p, first);
         for (int64_t i = 0; i < n_my; ++i) {
             const int st = (int)(i % kStages), g = (int)(i % kGens);
             const int32_t row0 = it.template row0<kBackward>(p);
-            const bool head = (row0 == 0) && (warp == 0) && !p.continuation;
-            // rows of this warp that exist in the sequence (fewer than kR only in the last row block)
-            const int64_t left = p.T - row0 - (int64_t)warp * kR;
+            const bool head = (row0 == 0) && (grp == 0) && !p.continuation;
+            // rows of this group that exist in the sequence (fewer than kR only in the last row block)
+            const int64_t left = p.T - row0 - (int64_t)grp * kR;
             const int nvalid = left >= kR ? kR : (left > 0 ? (int)left : 0);
             it.advance(p);
             if (i >= kGens) {      // the summary buffers of this generation are free once pass 2 of unit i-kGens is done
@@ -721,15 +732,16 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // ============================================================ pass 2
         // Re-scans this warp's rows from the true entering state and writes the results in place.
         using Raw = typename Lane<T>::Raw;
-        constexpr int kRowStride = kRowBytes / (int)sizeof(Raw);
+        constexpr int kRowStride = kRowB / (int)sizeof(Raw);
         const int w2 = warp - kPass2Warp0;
-        const uint32_t lane_off = (uint32_t)(w2 * kR) * kRowBytes + (uint32_t)lane * kLaneBytes;
-        const int ch = lane * V;
+        const int grp = w2 * kSp + q;
+        const uint32_t lane_off = (uint32_t)(grp * kR) * kRowB + (uint32_t)cl * kLaneBytes;
+        const int ch = cl * V;
         TileIter it;
         it.init(p, first);
         for (int64_t i = 0; i < n_my; ++i) {
             const int st = (int)(i % kStages), g = (int)(i % kGens);
-            const bool head = (it.template row0<kBackward>(p) == 0) && (w2 == 0);
+            const bool head = (it.template row0<kBackward>(p) == 0) && (grp == 0);
             const int32_t b = it.batch(p);
             const int64_t dch = (int64_t)it.cgroup(p) * Dc + ch;
             it.advance(p);
@@ -816,7 +828,18 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
 }
 
 // ------------------------------------------------------------------ host side
-inline int64_t block_rows(int, int64_t, int64_t, int64_t) { return kTc; }
+// Tile shape for a problem: split s gives tiles of 64*s rows x 256/s bytes.  Narrow, tall tiles
+// multiply the number of columns; with fewer columns than about two per SM several row blocks of
+// one column are in flight at once and the carry chain between them limits the speed.
+inline int choose_split(int dtype, int64_t B, int64_t T, int64_t D) {
+    if (const char *e = getenv("FSS_B200_SPLIT")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4) return v; }
+    const int64_t row_bytes = D * (dtype == FSS_DTYPE_BF16 ? 2 : 4);
+    const int64_t cols = B * ceil_div(row_bytes, kRowBytes);
+    int s = 1;
+    while (s < 4 && cols * s < 2 * 148 && row_bytes >= kRowBytes / s && T >= 2 * kTc * s * 2) s *= 2;
+    return s;
+}
+inline int64_t block_rows(int dtype, int64_t B, int64_t T, int64_t D) { return (int64_t)kTc * choose_split(dtype, B, T, D); }
 
 template <typename T> inline int64_t channel_groups(int64_t D) { return ceil_div(D, Cfg<T>::Dc); }
 
@@ -828,8 +851,13 @@ template <typename T> constexpr int packets_per_tile(bool prod) {
 inline size_t workspace_bytes(int64_t B, int64_t T, int64_t D, int dtype) {
     const int Dc = dtype == FSS_DTYPE_BF16 ? Cfg<bf16>::Dc : Cfg<float>::Dc;
     const int per_tile = dtype == FSS_DTYPE_BF16 ? packets_per_tile<bf16>(true) : packets_per_tile<float>(true);
-    const int64_t ntiles = B * ceil_div(D, Dc) * ceil_div(T, kTc);
-    return (size_t)ntiles * per_tile * 16;
+    size_t worst = 0;
+    for (int s = 1; s <= 4; s *= 2) {       // any tile shape the launcher may pick
+        const int64_t ntiles = B * ceil_div(D, Dc / s) * ceil_div(T, (int64_t)kTc * s);
+        const size_t need = (size_t)ntiles * (per_tile / s) * 16;
+        if (need > worst) worst = need;
+    }
+    return worst;
 }
 
 // What TMA needs: 16-byte aligned bases and strides, extents that fit its 32-bit coordinates.
@@ -868,14 +896,14 @@ inline EncodeTiledFn encode_fn() {
 // 3-D map (channels, rows, batch) with a (Dc, kTc, 1) box; out-of-range elements read as zero
 // and are dropped on store.
 template <typename T>
-inline bool make_map(CUtensorMap *map, const fss_view *v, int64_t B, int64_t Tn, int64_t D, std::string *err) {
+inline bool make_map(CUtensorMap *map, const fss_view *v, int64_t B, int64_t Tn, int64_t D, int split, std::string *err) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) { *err = "cuTensorMapEncodeTiled entry point not found"; return false; }
     const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Tn, (cuuint64_t)B};
     const int64_t sb = B > 1 ? v->stride_b : v->stride_t * Tn;
     const cuuint64_t strides[2] = {(cuuint64_t)(v->stride_t * (int64_t)sizeof(T)),
                                    (cuuint64_t)(sb * (int64_t)sizeof(T))};
-    const cuuint32_t box[3] = {(cuuint32_t)Cfg<T>::Dc, (cuuint32_t)kTc, 1};
+    const cuuint32_t box[3] = {(cuuint32_t)(Cfg<T>::Dc / split), (cuuint32_t)(kTc * split), 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     const CUresult r = fn(map, dt, 3, v->ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -892,14 +920,14 @@ inline bool make_map(CUtensorMap *map, const fss_view *v, int64_t B, int64_t Tn,
 }
 
 // CTAs that fit the device at once (one per SM with these shared-memory sizes), per device.
-template <typename T, bool kBackward, bool kProd> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
+template <typename T, bool kBackward, bool kProd, int kSp> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
     static std::mutex mu;
     static int cached[64];
     static bool have[64];
     std::lock_guard<std::mutex> lock(mu);
     if (device < 0 || device >= 64) { *err = cudaErrorInvalidDevice; return 0; }
     if (!have[device]) {
-        auto kern = scan_kernel<T, kBackward, kProd>;
+        auto kern = scan_kernel<T, kBackward, kProd, kSp>;
         *err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (*err != cudaSuccess) return 0;
         int per_sm = 0, sms = 0;
@@ -914,21 +942,21 @@ template <typename T, bool kBackward, bool kProd> inline int resident_ctas(int d
     return cached[device];
 }
 
-template <typename T, bool kBackward, bool kProd>
-inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t Tn, int64_t D,
+template <typename T, bool kBackward, bool kProd, int kSp>
+inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t Tn, int64_t D,
                   const fss_view *alpha, const fss_view *x, const fss_view *h, const fss_view *out0,
                   const fss_view *out1, Params p, std::string *err_text) {
     constexpr int kTensors = kBackward ? 3 : 2;
     constexpr int kStages = kBackward ? kStagesBwd : kStagesFwd;
     constexpr int smem_bytes = Smem<kTensors, kStages>::kBytes;
-    constexpr int Dc = Cfg<T>::Dc;
+    constexpr int Dc = Cfg<T>::Dc / kSp;
 
     CUtensorMap m_alpha, m_x, m_h, m_o0, m_o1;
-    if (!make_map<T>(&m_alpha, alpha, B, Tn, D, err_text) || !make_map<T>(&m_x, x, B, Tn, D, err_text) ||
-        !make_map<T>(&m_o0, out0, B, Tn, D, err_text))
+    if (!make_map<T>(&m_alpha, alpha, B, Tn, D, kSp, err_text) || !make_map<T>(&m_x, x, B, Tn, D, kSp, err_text) ||
+        !make_map<T>(&m_o0, out0, B, Tn, D, kSp, err_text))
         return FSS_E_TENSORMAP;
     if (kBackward) {
-        if (!make_map<T>(&m_h, h, B, Tn, D, err_text) || !make_map<T>(&m_o1, out1, B, Tn, D, err_text))
+        if (!make_map<T>(&m_h, h, B, Tn, D, kSp, err_text) || !make_map<T>(&m_o1, out1, B, Tn, D, kSp, err_text))
             return FSS_E_TENSORMAP;
     } else {
         m_h = m_alpha; m_o1 = m_o0;
@@ -937,15 +965,16 @@ inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t 
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) { *err_text = cudaGetErrorString(e); return FSS_E_DEVICE; }
-    const int resident = resident_ctas<T, kBackward, kProd>(device, smem_bytes, &e);
+    const int resident = resident_ctas<T, kBackward, kProd, kSp>(device, smem_bytes, &e);
     if (e != cudaSuccess || resident < 1) { *err_text = cudaGetErrorString(e); return FSS_E_LAUNCH; }
 
     p.B = B; p.T = Tn; p.D = D;
     p.ncg = ceil_div(D, Dc);
     p.ncols = B * p.ncg;
-    p.S = ceil_div(Tn, kTc);
+    p.S = ceil_div(Tn, (int64_t)kTc * kSp);
+    p.tile_rows = kTc * kSp;
     p.ntiles = p.ncols * p.S;
-    if ((size_t)p.ntiles * packets_per_tile<T>(kProd) * 16 > ws.packet_bytes) return FSS_E_WORKSPACE;
+    if ((size_t)p.ntiles * (packets_per_tile<T>(kProd) / kSp) * 16 > ws.packet_bytes) return FSS_E_WORKSPACE;
     p.hdr = reinterpret_cast<Header *>(ws.hdr);
     p.packets = reinterpret_cast<uint4 *>(ws.packets);
     p.status = ctx->status;
@@ -955,11 +984,23 @@ inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t 
     p.grid = grid;
     p.grid_q = (int32_t)(grid / p.ncols);
     p.grid_r = (int32_t)(grid % p.ncols);
-    scan_kernel<T, kBackward, kProd><<<grid, kThreads, smem_bytes, (cudaStream_t)ctx->stream>>>(
+    scan_kernel<T, kBackward, kProd, kSp><<<grid, kThreads, smem_bytes, (cudaStream_t)ctx->stream>>>(
         m_alpha, m_x, m_h, m_o0, m_o1, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { *err_text = std::string("look-back launch: ") + cudaGetErrorString(e); return FSS_E_LAUNCH; }
     return FSS_OK;
+}
+
+template <typename T, bool kBackward, bool kProd>
+inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t Tn, int64_t D,
+                  const fss_view *alpha, const fss_view *x, const fss_view *h, const fss_view *out0,
+                  const fss_view *out1, Params p, std::string *err_text) {
+    const int dtype = sizeof(T) == 2 ? FSS_DTYPE_BF16 : FSS_DTYPE_F32;
+    switch (choose_split(dtype, B, Tn, D)) {
+    case 4: return launch_split<T, kBackward, kProd, 4>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, err_text);
+    case 2: return launch_split<T, kBackward, kProd, 2>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, err_text);
+    default: return launch_split<T, kBackward, kProd, 1>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, err_text);
+    }
 }
 
 template <typename T>

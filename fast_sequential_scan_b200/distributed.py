@@ -40,29 +40,42 @@ class NativeOps:
     def __init__(self, algo: Optional[int] = None):
         self.algo = algo
 
+    def _algo_for(self, *tensors):
+        """The kernel family that will really run: block sizes of the two families differ, so a
+        layout the single-pass kernels cannot take is sent to the chunked ones explicitly."""
+        from . import _lib, sequential_scan_cuda as native
+        if self.algo is not None:
+            return self.algo
+        algo = native.default_algo()
+        if algo == _lib.ALGO_AUTO and not native.tma_eligible(*tensors):
+            return _lib.ALGO_CHUNKED
+        return algo
+
     def local_forward(self, alpha, beta, continuation: bool):
         from . import sequential_scan_cuda as native
         B, T, D = alpha.shape
-        R = native.block_rows(alpha.dtype, B, T, D, self.algo)
+        algo = self._algo_for(alpha, beta)
+        R = native.block_rows(alpha.dtype, B, T, D, algo)
         nb = -(-T // R)
         f32 = dict(dtype=torch.float32, device=alpha.device)
         h = torch.empty_like(alpha)
         h_last, prod = torch.empty(B, D, **f32), torch.empty(B, D, **f32)
         blocks = (torch.empty(B, nb, D, **f32), torch.empty(B, nb, D, **f32), R)     # products, states, rows
-        native.forward_into(alpha, beta, h, algo=self.algo, continuation=continuation, h_last=h_last, prod=prod,
+        native.forward_into(alpha, beta, h, algo=algo, continuation=continuation, h_last=h_last, prod=prod,
                             block_prod=blocks[0], block_state=blocks[1])
         return h, h_last, prod, blocks
 
     def local_backward(self, alpha, h, grad, continuation: bool, h_prev):
         from . import sequential_scan_cuda as native
         B, T, D = alpha.shape
-        R = native.block_rows(alpha.dtype, B, T, D, self.algo)
+        algo = self._algo_for(alpha, h, grad)
+        R = native.block_rows(alpha.dtype, B, T, D, algo)
         nb = -(-T // R)
         f32 = dict(dtype=torch.float32, device=alpha.device)
         da, db = torch.empty_like(alpha), torch.empty_like(alpha)
         u_out = torch.empty(B, D, **f32)
         blocks = (torch.empty(B, nb, D, **f32), torch.empty(B, nb, D, **f32), R)
-        native.backward_into(alpha, h, grad, da, db, algo=self.algo, continuation=continuation, h_prev=h_prev,
+        native.backward_into(alpha, h, grad, da, db, algo=algo, continuation=continuation, h_prev=h_prev,
                              u_out=u_out, block_prod=blocks[0], block_state=blocks[1])
         return da, db, u_out, blocks
 

@@ -190,6 +190,19 @@ def scan_backward_half(alpha_saved, h_saved, grad_out) -> List[torch.Tensor]:
 # ---------------------------------------------------------------------------------------------
 # Sequence-parallel pieces (no counterpart in the reference, which never splits the sequence)
 
+def tma_eligible(*tensors: torch.Tensor) -> bool:
+    """True when the single-pass kernels can take these [B, T, D] tensors (16-byte aligned bases,
+    row and batch strides that are multiples of 16 bytes); otherwise ``auto`` uses the chunked kernels."""
+    for t in tensors:
+        per16 = 16 // t.element_size()
+        B, T, D = t.shape
+        if D % per16 or t.data_ptr() % 16 or (D > 1 and t.stride(2) != 1):
+            return False
+        if (T > 1 and t.stride(1) % per16) or (B > 1 and t.stride(0) % per16):
+            return False
+    return True
+
+
 def block_rows(dtype: torch.dtype, B: int, T: int, D: int, algo: Optional[int] = None) -> int:
     """Rows per block of the ``block_prod`` outputs for this problem."""
     a = default_algo() if algo is None else algo

@@ -115,7 +115,17 @@ __device__ __forceinline__ void trace(int64_t unit, int ev) {
     }
 }
 #define FSS_TRACE_EV(unit, ev) do { if ((threadIdx.x & 31) == 0) trace(unit, ev); } while (0)
+// kernel life: slot 15 of units 0..4 = SM clock at entry / after set-up / at exit, global ns at entry / exit
+__device__ __forceinline__ void trace_life(int which, bool global_ns) {
+    if (g_trace && threadIdx.x == 0 && which < g_trace_units) {
+        unsigned long long t;
+        if (global_ns) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); else t = (unsigned long long)clock64();
+        g_trace[((int64_t)blockIdx.x * g_trace_units + which) * kEvents + 15] = t;
+    }
+}
+#define FSS_TRACE_LIFE(which, ns) trace_life(which, ns)
 #else
+#define FSS_TRACE_LIFE(which, ns) do { } while (0)
 #define FSS_TRACE_EV(unit, ev) do { } while (0)
 #endif
 
@@ -344,6 +354,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q = lane / LPG, cl = lane % LPG;
+    FSS_TRACE_LIFE(0, false);
+    FSS_TRACE_LIFE(3, true);
     const int64_t first = blockIdx.x;
     const int64_t n_my = first < p.ntiles ? (p.ntiles - first + p.grid - 1) / p.grid : 0;
 
@@ -356,6 +368,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         fence_proxy_async();
     }
     __syncthreads();
+    FSS_TRACE_LIFE(1, false);
     const uint32_t epoch = *epoch_s;
     const Ctl ctl{p.hdr, p.status, cta_abort};
 
@@ -499,27 +512,29 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             float cur[NI];
             bool hit = false;
             if (have_pre) hit = __all_sync(0xffffffffu, IncPk::decode(pre, cur, tag_inc));
-            FSS_TRACE_EV(i, kEvLbA);
-            // second chance for this unit and first look for this warp's next one: both are only
-            // issued here and decoded after the summary barrier, so their latency is hidden
-            typename IncPk::Raw late;
-#ifndef FSS_NO_LATE
-            const bool have_late = s > 0 && !hit;
-#else
-            const bool have_late = false;
-#endif
-            if (have_late) IncPk::load_raw(inc_packets(k - p.ncols), late);
-            FSS_TRACE_EV(i, kEvLbB);
-#ifndef FSS_NO_PRE
+            // first look for this warp's next unit (decoded when that unit starts)
             have_pre = i + kLookbackWarps < n_my && it.s > 0;
             if (have_pre) IncPk::load_raw(inc_packets(it.k - p.ncols), pre);
-#else
-            have_pre = false;
-#endif
-
-            FSS_TRACE_EV(i, kEvLbIssued);
+            // While pass 1 and the summary warp are still working on this unit, keep asking for the
+            // predecessor's inclusive state: this warp has nothing else to do, and in the common case
+            // the answer is there before the summary is, so the carry costs no extra round trip.
+            if (s > 0) {
+                while (!hit) {      // every exit below is decided by a warp vote
+                    const bool summary_in = mbar_try_wait(bar_sum(g), (uint32_t)((i / kGens) & 1));
+                    if (__all_sync(0xffffffffu, summary_in)) break;
+                    typename IncPk::Raw again;
+                    IncPk::load_raw(inc_packets(k - p.ncols), again);
+                    hit = __all_sync(0xffffffffu, IncPk::decode(again, cur, tag_inc));
+                    if (!hit && __any_sync(0xffffffffu, ctl.aborted())) break;
+                }
+            }
             if (!ctl.wait(bar_sum(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
             FSS_TRACE_EV(i, kEvLbStart);
+            if (s > 0 && !hit) {       // one more look now that the summary is in
+                typename IncPk::Raw again;
+                IncPk::load_raw(inc_packets(k - p.ncols), again);
+                hit = __all_sync(0xffffffffu, IncPk::decode(again, cur, tag_inc));
+            }
 
             // the tile's summary, folded by the summary warp
             float Pt[V], Ct[V];
@@ -535,14 +550,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             auto state0 = [&](int v) {
                 return (p.state_in && ch_ok) ? p.state_in[(int64_t)b * p.D + dch + v] : 0.0f;
             };
-            if (have_late) {
-                float lv[NI];
-                if (__all_sync(0xffffffffu, IncPk::decode(late, lv, tag_inc))) {
-                    hit = true;
-#pragma unroll
-                    for (int v = 0; v < NI; ++v) cur[v] = lv[v];
-                }
-            }
             if (s == 0) {
 #pragma unroll
                 for (int v = 0; v < V; ++v) { cin[v] = state0(v); pin[v] = 1.0f; }
@@ -813,8 +820,10 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         }
     }
 
-    // ---- leave: the last CTA advances the epoch, which invalidates every packet of this launch
+    // ---- leave: the last CTA advances the epoch, which invalidates every descriptor of this launch
     __syncthreads();
+    FSS_TRACE_LIFE(2, false);
+    FSS_TRACE_LIFE(4, true);
     if (threadIdx.x == 0) {
         __threadfence();
         const uint32_t prev = atomicAdd(&p.hdr->done, 1u);

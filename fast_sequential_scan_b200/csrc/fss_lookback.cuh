@@ -151,6 +151,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// non-blocking probe of a phase (try_wait may park the warp until the phase completes)
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -478,6 +488,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // kLookbackWarps warps share the work units round-robin, so several carry resolutions
         // (each a few L2 round trips) are in flight per CTA.
         constexpr int NI = kProd ? 2 * V : V;          // floats of an inclusive descriptor
+        constexpr int kWin = (kProd && V == 4) ? 2 : kWindow;   // fewer at once where registers are short
         using AggPk = PacketGroup<2 * V, LPG>;         // (P, C) of the tile scanned from zero
         using IncPk = PacketGroup<NI, LPG>;                 // state after the tile (and product up to it)
         constexpr int kTilePackets = (AggPk::kPackets + IncPk::kPackets) * LPG;
@@ -507,8 +518,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             const int64_t dch = (int64_t)it.cgroup(p) * Dc + ch;     // channel in the tensor
             const bool ch_ok = dch < p.D;
             for (int j = 0; j < kLookbackWarps; ++j) it.advance(p);  // -> this warp's next unit
-
-            FSS_TRACE_EV(i, kEvLbTop);
             float cur[NI];
             bool hit = false;
             if (have_pre) hit = __all_sync(0xffffffffu, IncPk::decode(pre, cur, tag_inc));
@@ -519,13 +528,14 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             // predecessor's inclusive state: this warp has nothing else to do, and in the common case
             // the answer is there before the summary is, so the carry costs no extra round trip.
             if (s > 0) {
+                uint32_t polls = 0;
                 while (!hit) {      // every exit below is decided by a warp vote
-                    const bool summary_in = mbar_try_wait(bar_sum(g), (uint32_t)((i / kGens) & 1));
+                    const bool summary_in = mbar_test_wait(bar_sum(g), (uint32_t)((i / kGens) & 1));
                     if (__all_sync(0xffffffffu, summary_in)) break;
                     typename IncPk::Raw again;
                     IncPk::load_raw(inc_packets(k - p.ncols), again);
                     hit = __all_sync(0xffffffffu, IncPk::decode(again, cur, tag_inc));
-                    if (!hit && __any_sync(0xffffffffu, ctl.aborted())) break;
+                    if (!hit && (++polls & 31u) == 0u && __any_sync(0xffffffffu, ctl.aborted())) break;
                 }
             }
             if (!ctl.wait(bar_sum(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
@@ -564,11 +574,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 uint32_t spins = 0;
                 bool found = false;
                 while (!found) {
-                    // read up to kWindow predecessors in one round trip
-                    float inc[kWindow][NI], ag[kWindow][2 * V];
-                    bool inc_ok[kWindow], ag_ok[kWindow];
+                    // read up to kWin predecessors in one round trip
+                    float inc[kWin][NI], ag[kWin][2 * V];
+                    bool inc_ok[kWin], ag_ok[kWin];
 #pragma unroll
-                    for (int j = 0; j < kWindow; ++j) {
+                    for (int j = 0; j < kWin; ++j) {
                         const int64_t qj = q - j * p.ncols;
                         inc_ok[j] = false; ag_ok[j] = false;
                         if (qj >= 0) {
@@ -579,7 +589,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                     int adv = 0;          // predecessors folded in this round
                     bool stop = false;
 #pragma unroll
-                    for (int j = 0; j < kWindow; ++j) {
+                    for (int j = 0; j < kWin; ++j) {
                         const int64_t qj = q - j * p.ncols;     // warp-uniform
                         if (found || stop) {
                             // nothing more to do in this round
@@ -623,8 +633,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 }
                 if (!ok) break;
             }
-
-            FSS_TRACE_EV(i, kEvLbFound);
             // ---- hand the entering state to the consumers: each warp applies the exclusive prefix
             // the summary warp left in its slot
             {
@@ -644,9 +652,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 out[v] = fmaf(Pt[v], cin[v], Ct[v]);
                 if (kProd) out[kProd ? V + v : v] = Pt[v] * pin[v];
             }
-            FSS_TRACE_EV(i, kEvLbE);
             if (s + 1 < (int32_t)p.S && q == 0) IncPk::store(inc_packets(k), out, tag_inc);
-            FSS_TRACE_EV(i, kEvLbC);
 
             if (ch_ok && q == 0) {
                 if (kProd && p.block_prod) {

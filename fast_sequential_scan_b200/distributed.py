@@ -93,10 +93,20 @@ class NativeOps:
                                      continuation)
 
 
+def _rank(group) -> int:
+    return dist.get_rank(group) if dist.is_available() and dist.is_initialized() else 0
+
+
+def _world(group) -> int:
+    return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+
+
 def _gather(vec_a: torch.Tensor, vec_b: torch.Tensor, group) -> torch.Tensor:
     """All-gather of this rank's two [B, D] fp32 vectors -> [world, 2, B*D]."""
-    world = dist.get_world_size(group)
     mine = torch.stack([vec_a.reshape(-1), vec_b.reshape(-1)]).contiguous()
+    world = _world(group)
+    if world == 1:
+        return mine.view(1, 2, mine.shape[1])
     out = torch.empty((world * 2, mine.shape[1]), dtype=mine.dtype, device=mine.device)   # ranks concatenated
     dist.all_gather_into_tensor(out, mine, group=group)
     return out.view(world, 2, mine.shape[1])
@@ -106,7 +116,7 @@ def seqpar_forward(alpha, beta, group=None, ops=None):
     """Forward of the sequence-parallel scan on this rank's rows.  Returns ``(h, saved)`` where
     ``saved`` carries what the backward needs (state entering the rows, local product)."""
     ops = ops or NativeOps()
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    rank, world = _rank(group), _world(group)
     B, T, D = alpha.shape
     h, h_last, prod, blocks = ops.local_forward(alpha, beta, continuation=rank > 0)
     pc = _gather(prod, h_last, group)
@@ -120,7 +130,7 @@ def seqpar_forward(alpha, beta, group=None, ops=None):
 def seqpar_backward(alpha, h, grad, saved, group=None, ops=None):
     """Backward on this rank's rows: ``(dalpha, dbeta)`` for the local slices."""
     ops = ops or NativeOps()
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    rank, world = _rank(group), _world(group)
     B, T, D = alpha.shape
     h_prev = saved["carry_in"]
     da, db, u_out, blocks = ops.local_backward(alpha, h, grad, continuation=rank > 0, h_prev=h_prev)

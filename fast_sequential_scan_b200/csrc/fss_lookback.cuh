@@ -64,7 +64,10 @@ constexpr int kStagesBwd = 4;                 // 4 x 48 KiB
 constexpr uint32_t kMaxSpins = 1u << 21;      // per wait; ~a second before giving up
 
 constexpr uint32_t kStateAggregate = 1, kStateInclusive = 2;
-constexpr int kWindow = 4;                    // predecessors inspected per look-back round trip
+#ifndef FSS_WINDOW
+#define FSS_WINDOW 2
+#endif
+constexpr int kWindow = FSS_WINDOW;           // predecessors inspected per look-back round trip
 
 template <typename T> struct Cfg {
     static constexpr int V = kLaneBytes / (int)sizeof(T);   // channels per lane
@@ -369,10 +372,15 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     const int64_t first = blockIdx.x;
     const int64_t n_my = first < p.ntiles ? (p.ntiles - first + p.grid - 1) / p.grid : 0;
 
+    // Programmatic dependent launch: let the next launch on the stream start its own set-up as SMs
+    // become free, and do everything that touches no global memory before waiting for the previous
+    // launch to finish (both instructions do nothing for an ordinary launch).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_done(s), kW); }
         for (int g = 0; g < kGens; ++g) { mbar_init(bar_agg(g), kW); mbar_init(bar_carry(g), 1); mbar_init(bar_sum(g), 1); }
         *cta_abort = 0;
+        asm volatile("griddepcontrol.wait;" ::: "memory");      // the previous launch and its writes are complete
         *epoch_s = ld_volatile(&p.hdr->epoch) + 1u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
@@ -488,7 +496,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // kLookbackWarps warps share the work units round-robin, so several carry resolutions
         // (each a few L2 round trips) are in flight per CTA.
         constexpr int NI = kProd ? 2 * V : V;          // floats of an inclusive descriptor
-        constexpr int kWin = (kProd && V == 4) ? 2 : kWindow;   // fewer at once where registers are short
+        constexpr int kWin = kWindow;
         using AggPk = PacketGroup<2 * V, LPG>;         // (P, C) of the tile scanned from zero
         using IncPk = PacketGroup<NI, LPG>;                 // state after the tile (and product up to it)
         constexpr int kTilePackets = (AggPk::kPackets + IncPk::kPackets) * LPG;
@@ -999,9 +1007,21 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     p.grid = grid;
     p.grid_q = (int32_t)(grid / p.ncols);
     p.grid_r = (int32_t)(grid % p.ncols);
-    scan_kernel<T, kBackward, kProd, kSp><<<grid, kThreads, smem_bytes, (cudaStream_t)ctx->stream>>>(
-        m_alpha, m_x, m_h, m_o0, m_o1, p);
-    e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = (cudaStream_t)ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    // Opt-in (FSS_B200_PDL=1): measured on B200 it shortens back-to-back launches of tiny problems
+    // by ~10 % but slows some long backward launches, so it is off unless asked for.
+    static const bool use_pdl = [] { const char *e = getenv("FSS_B200_PDL"); return e && e[0] == '1'; }();
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, scan_kernel<T, kBackward, kProd, kSp>, m_alpha, m_x, m_h, m_o0, m_o1, p);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { *err_text = std::string("look-back launch: ") + cudaGetErrorString(e); return FSS_E_LAUNCH; }
     return FSS_OK;
 }

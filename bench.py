@@ -25,6 +25,10 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
+# DRAM bytes (read + write) per launch of the backward kernel from the committed ncu capture
+# (profiles/lookback_c2_ncu_full.md); only known for the workload that was captured
+NCU_TRAFFIC = {("c2", "lookback"): 130.1e6}
+
 METRIC = "scan fwd+bwd elems/s"
 UNIT = "elems/s"
 L2_BYTES = 126 * 1024 * 1024
@@ -388,7 +392,9 @@ def main():
     ach_step = (bwd_bytes + fwd_bytes) / (ms_step * 1e-3) / 1e9
     kernel_bwd = "fss::lookback::scan_backward_kernel" if took_lookback else "fss::chunked::chunk_scan_backward (+summary, compose)"
     roofline = {"bound": "hbm", "kernel": kernel_bwd, "achieved": ach_bwd, "peak": peak, "unit": "GB/s",
-                "frac": ach_bwd / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                "frac": ach_bwd / peak,
+                "traffic": NCU_TRAFFIC.get((args.workload if not args.shape else "", "lookback" if took_lookback else "chunked")),
+                "algorithmic_bytes": bwd_bytes, "peak_kind": f"of {peak_kind}",
                 "ms_per_launch": ms_bwd,
                 "forward": {"achieved": ach_fwd, "frac": ach_fwd / peak, "ms_per_launch": ms_fwd},
                 "step": {"achieved": ach_step, "frac": ach_step / peak}}

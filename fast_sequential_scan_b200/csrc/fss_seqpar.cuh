@@ -32,11 +32,16 @@ __global__ void compose(int backward, int world, int rank, int64_t n,
     carry_in[i] = carry;
 }
 
+// Fix-up geometry: one CTA per (block of R rows, group of 32 channel vectors, batch row); its
+// kWarps warps split the block's rows, lane = channel vector.
+constexpr int kWarps = 8;
+constexpr int kFixThreads = kWarps * 32;
+
 struct Geometry {
     int64_t B, T, D;
     int64_t R;        // rows per block (the block_prod granularity)
     int64_t NB;       // blocks per column
-    int64_t nvec, vblocks;
+    int64_t nvec, vblocks;   // channel vectors per row, CTAs along the channel axis (32 vectors each)
 };
 
 __device__ __forceinline__ void decode_block(const Geometry &g, int64_t &vb, int64_t &j, int64_t &b) {
@@ -46,29 +51,61 @@ __device__ __forceinline__ void decode_block(const Geometry &g, int64_t &vb, int
     b = id / g.NB;
 }
 
-// Re-scan of the blocks that the entering state still reaches (forward).
+// Re-scan of the blocks that the entering state still reaches (forward).  A block is live when
+// (product of alpha before it) * carry_in is non-zero for some channel; a dead block already holds
+// the exact result.  Inside a live block the warps first summarise their rows (P, C), then each
+// re-scans its rows from  (map of the warps before it)(true state entering the block).
 template <typename T, int V>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kFixThreads)
 fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, const float *__restrict__ carry_in,
               const float *__restrict__ block_prod, const float *__restrict__ block_state) {
+    __shared__ float sP[kWarps][32][V], sC[kWarps][32][V];
     int64_t vb, j, b;
     decode_block(g, vb, j, b);
-    const int64_t v = vb * kThreads + threadIdx.x;
-    if (v >= g.nvec) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t v = vb * 32 + lane;
+    const bool has = v < g.nvec;
     const int64_t d0 = v * V;
     float st[V];
     bool live = false;
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-        const int64_t o = (b * g.NB + j - 1) * g.D + d0 + i;
-        const float w = (j == 0 ? 1.0f : block_prod[o]) * carry_in[b * g.D + d0 + i];
-        st[i] = (j == 0 ? 0.0f : block_state[o]) + w;
-        live |= (w != 0.0f);
+    for (int i = 0; i < V; ++i) st[i] = 0.0f;
+    if (has) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int64_t o = (b * g.NB + j - 1) * g.D + d0 + i;
+            const float w = (j == 0 ? 1.0f : block_prod[o]) * carry_in[b * g.D + d0 + i];
+            st[i] = (j == 0 ? 0.0f : block_state[o]) + w;
+            live |= (w != 0.0f);
+        }
     }
-    if (!live) return;   // the zero-state result of this block is already exact
+    if (!__syncthreads_or(live)) return;   // the zero-state result of this block is already exact
     const int64_t r0 = j * g.R, r1 = min(g.T, r0 + g.R);
+    const int64_t per = (g.R + kWarps - 1) / kWarps;
+    const int64_t w0 = min(r1, r0 + warp * per), w1 = min(r1, w0 + per);
+    float P[V], C[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) { P[i] = 1.0f; C[i] = 0.0f; }
+    if (has) {
 #pragma unroll 4
-    for (int64_t t = r0; t < r1; ++t) {
+        for (int64_t t = w0; t < w1; ++t) {
+            float a[V], x[V];
+            Frag<T, V>::load(alpha.row(b, t) + d0, a);
+            Frag<T, V>::load(beta.row(b, t) + d0, x);
+#pragma unroll
+            for (int i = 0; i < V; ++i) { C[i] = fmaf(a[i], C[i], x[i]); P[i] *= a[i]; }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) { sP[warp][lane][i] = P[i]; sC[warp][lane][i] = C[i]; }
+    __syncthreads();
+    if (!has) return;
+    for (int w = 0; w < warp; ++w) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) st[i] = fmaf(sP[w][lane][i], st[i], sC[w][lane][i]);
+    }
+#pragma unroll 4
+    for (int64_t t = w0; t < w1; ++t) {
         float a[V], x[V];
         Frag<T, V>::load(alpha.row(b, t) + d0, a);
         Frag<T, V>::load(beta.row(b, t) + d0, x);
@@ -78,31 +115,67 @@ fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, co
     }
 }
 
-// Re-scan of the blocks that the arriving u still reaches (backward).
+// Re-scan of the blocks that the arriving u still reaches (backward); same structure, rows taken
+// from the end of the block.
 template <typename T, int V>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kFixThreads)
 fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> grad, View<T> dalpha,
                View<T> dbeta, const float *__restrict__ u_in, const float *__restrict__ h_prev,
                const float *__restrict__ block_prod, const float *__restrict__ block_state, bool continuation) {
+    __shared__ float sP[kWarps][32][V], sC[kWarps][32][V];
     int64_t vb, j, b;
     decode_block(g, vb, j, b);
-    const int64_t v = vb * kThreads + threadIdx.x;
-    if (v >= g.nvec) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t v = vb * 32 + lane;
+    const bool has = v < g.nvec;
     const int64_t d0 = v * V;
     float u[V];
     bool live = false;
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-        const int64_t o = (b * g.NB + j + 1) * g.D + d0 + i;
+    for (int i = 0; i < V; ++i) u[i] = 0.0f;
+    if (has) {
         const bool lastb = j == g.NB - 1;
-        const float w = (lastb ? 1.0f : block_prod[o]) * u_in[b * g.D + d0 + i];
-        u[i] = (lastb ? 0.0f : block_state[o]) + w;
-        live |= (w != 0.0f);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int64_t o = (b * g.NB + j + 1) * g.D + d0 + i;
+            const float w = (lastb ? 1.0f : block_prod[o]) * u_in[b * g.D + d0 + i];
+            u[i] = (lastb ? 0.0f : block_state[o]) + w;
+            live |= (w != 0.0f);
+        }
     }
-    if (!live) return;
+    if (!__syncthreads_or(live)) return;
     const int64_t r0 = j * g.R, r1 = min(g.T, r0 + g.R);
+    const int64_t per = (g.R + kWarps - 1) / kWarps;
+    // warp 0 takes the last rows of the block, warp 1 the rows before them, ...
+    const int64_t w1 = max(r0, r1 - warp * per), w0 = max(r0, w1 - per);
+    float P[V], C[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) { P[i] = 1.0f; C[i] = 0.0f; }
+    if (has) {
 #pragma unroll 4
-    for (int64_t t = r1 - 1; t >= r0; --t) {
+        for (int64_t t = w1 - 1; t >= w0; --t) {
+            float a[V], x[V];
+            Frag<T, V>::load(alpha.row(b, t) + d0, a);
+            Frag<T, V>::load(grad.row(b, t) + d0, x);
+            const bool head = (t == 0) && !continuation;
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const float av = head ? 0.0f : a[i];
+                C[i] = av * (x[i] + C[i]);
+                P[i] *= av;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) { sP[warp][lane][i] = P[i]; sC[warp][lane][i] = C[i]; }
+    __syncthreads();
+    if (!has) return;
+    for (int w = 0; w < warp; ++w) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) u[i] = fmaf(sP[w][lane][i], u[i], sC[w][lane][i]);
+    }
+#pragma unroll 4
+    for (int64_t t = w1 - 1; t >= w0; --t) {
         float a[V], gr[V], hp[V], da[V], dh[V];
         Frag<T, V>::load(alpha.row(b, t) + d0, a);
         Frag<T, V>::load(grad.row(b, t) + d0, gr);

@@ -355,7 +355,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     const uint32_t bars = smem_base + kStages * SM::kStageBytes + SM::kAggBytes + SM::kSumBytes;
     volatile int *cta_abort = reinterpret_cast<volatile int *>(smem_raw + kStages * SM::kStageBytes +
                                                                SM::kAggBytes + SM::kSumBytes + SM::kBarriers * 8);
-    volatile uint32_t *epoch_s = reinterpret_cast<volatile uint32_t *>(const_cast<int *>(cta_abort) + 1);
     auto bar_full = [&](int s) { return bars + 8u * s; };
     auto bar_done = [&](int s) { return bars + 8u * (kStages + s); };
     auto bar_agg = [&](int g) { return bars + 8u * (2 * kStages + g); };
@@ -381,18 +380,24 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         for (int g = 0; g < kGens; ++g) { mbar_init(bar_agg(g), kW); mbar_init(bar_carry(g), 1); mbar_init(bar_sum(g), 1); }
         *cta_abort = 0;
         asm volatile("griddepcontrol.wait;" ::: "memory");      // the previous launch and its writes are complete
-        *epoch_s = ld_volatile(&p.hdr->epoch) + 1u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async();
     }
     __syncthreads();
     FSS_TRACE_LIFE(1, false);
-    const uint32_t epoch = *epoch_s;
     const Ctl ctl{p.hdr, p.status, cta_abort};
+    // This launch's epoch (tags of its descriptors) is only needed by the summary and look-back
+    // warps, which read it themselves: the producer's first loads do not wait for this round trip.
+    // (The header's epoch changes only after every CTA of the launch has finished.)
+    uint32_t epoch = 0;
+    if (warp == kSummaryWarp || warp >= kLookbackWarp0) epoch = ld_volatile(&p.hdr->epoch) + 1u;
 
     if (warp == kProducerWarp) {
         // ============================================================ producer
         if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_alpha) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+            if (kBackward) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_h) : "memory");
             TileIter ld_it, st_it;
             ld_it.init(p, first);
             st_it.init(p, first);
@@ -845,7 +850,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             p.hdr->done = 0;
             p.hdr->abort = 0;
             __threadfence();
-            p.hdr->epoch = epoch;
+            p.hdr->epoch = ld_volatile(&p.hdr->epoch) + 1u;
         }
     }
 }

@@ -98,6 +98,8 @@ struct Params {
     const float *h_prev;     // backward only
     int continuation;
     int32_t tile_rows;       // rows per tile: 64 * split
+    uint32_t max_spins;      // iterations a wait may take before it gives up
+    int mute_first_block;    // test hook: row block 0 publishes no descriptors (its successors' waits run out)
     int64_t grid;            // CTAs of the launch, and grid = grid_q * ncols + grid_r
     int32_t grid_q, grid_r;
 
@@ -272,6 +274,7 @@ struct Ctl {
     Header *hdr;
     int32_t *status;
     volatile int *cta_abort;   // shared-memory copy of the abort flag
+    uint32_t max_spins;
 
     __device__ __forceinline__ bool aborted() const {
         return *cta_abort != 0 || ld_volatile(&hdr->abort) != 0;
@@ -283,7 +286,7 @@ struct Ctl {
     }
     // false = the wait was abandoned (timeout here, or abort raised elsewhere)
     __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, int32_t code) const {
-        for (uint32_t it = 0; it < kMaxSpins; ++it) {
+        for (uint32_t it = 0; it < max_spins; ++it) {
             if (mbar_try_wait(bar, parity)) return *cta_abort == 0;
             if ((it & 63u) == 63u && aborted()) { *cta_abort = 1; return false; }
         }
@@ -385,7 +388,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     }
     __syncthreads();
     FSS_TRACE_LIFE(1, false);
-    const Ctl ctl{p.hdr, p.status, cta_abort};
+    const Ctl ctl{p.hdr, p.status, cta_abort, p.max_spins};
     // This launch's epoch (tags of its descriptors) is only needed by the summary and look-back
     // warps, which read it themselves: the producer's first loads do not wait for this round trip.
     // (The header's epoch changes only after every CTA of the launch has finished.)
@@ -439,7 +442,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 for (int64_t j = i; j < issued; ++j) {
                     const uint32_t bar = bar_full((int)(j % kStages));
                     const uint32_t par = (uint32_t)((j / kStages) & 1);
-                    for (uint32_t it = 0; it < kMaxSpins && !mbar_try_wait(bar, par); ++it) {}
+                    for (uint32_t it = 0; it < p.max_spins && !mbar_try_wait(bar, par); ++it) {}
                 }
             }
             tma_wait_all();
@@ -460,6 +463,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             const int g = (int)(i % kGens);
             const int64_t k = it.k;
             const bool last_block = it.s + 1 == (int32_t)p.S;
+            const int32_t it_s = it.s;
             it.advance(p);
             if (!ctl.wait(bar_agg(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
             float pc[2 * V];
@@ -493,7 +497,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             sum_at(g, 1, lane) = sc;
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_sum(g));
-            if (!last_block && q == 0) AggPk::store(p.packets + k * kTilePackets + cl, pc, tag_agg);
+            if (!last_block && q == 0 && !(p.mute_first_block && it_s == 0))
+                AggPk::store(p.packets + k * kTilePackets + cl, pc, tag_agg);
             FSS_TRACE_EV(i, kEvSum);
         }
     } else if (warp >= kLookbackWarp0) {
@@ -548,7 +553,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                     typename IncPk::Raw again;
                     IncPk::load_raw(inc_packets(k - p.ncols), again);
                     hit = __all_sync(0xffffffffu, IncPk::decode(again, cur, tag_inc));
-                    if (!hit && (++polls & 31u) == 0u && __any_sync(0xffffffffu, ctl.aborted())) break;
+                    if (!hit && (++polls & 31u) == 0u && (polls >= p.max_spins || __any_sync(0xffffffffu, ctl.aborted()))) break;
                 }
             }
             if (!ctl.wait(bar_sum(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
@@ -636,7 +641,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                     if (adv == 0) {
                         ++spins;
                         if ((spins & 15u) == 0u && __any_sync(0xffffffffu, ctl.aborted())) { ok = false; break; }
-                        if (spins >= kMaxSpins) {
+                        if (spins >= p.max_spins) {
                             if (lane == 0) ctl.give_up(FSS_STATUS_LOOKBACK_TIMEOUT);
                             ok = false;
                             break;
@@ -665,7 +670,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 out[v] = fmaf(Pt[v], cin[v], Ct[v]);
                 if (kProd) out[kProd ? V + v : v] = Pt[v] * pin[v];
             }
-            if (s + 1 < (int32_t)p.S && q == 0) IncPk::store(inc_packets(k), out, tag_inc);
+            if (s + 1 < (int32_t)p.S && q == 0 && !(p.mute_first_block && s == 0)) IncPk::store(inc_packets(k), out, tag_inc);
 
             if (ch_ok && q == 0) {
                 if (kProd && p.block_prod) {
@@ -1007,6 +1012,8 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     p.packets = reinterpret_cast<uint4 *>(ws.packets);
     p.status = ctx->status;
     p.continuation = (ctx->flags & FSS_FLAG_CONTINUATION) ? 1 : 0;
+    p.max_spins = (ctx->flags & FSS_FLAG_TEST_SHORT_WAITS) ? 4096u : kMaxSpins;
+    p.mute_first_block = (ctx->flags & FSS_FLAG_TEST_MUTE_FIRST_BLOCK) ? 1 : 0;
 
     const unsigned grid = (unsigned)(p.ntiles < resident ? p.ntiles : resident);
     p.grid = grid;

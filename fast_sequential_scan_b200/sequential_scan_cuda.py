@@ -88,7 +88,7 @@ def _blocks(t: Optional[torch.Tensor], name: str) -> Optional[int]:
 
 
 def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_last=None,
-                 prod=None, block_prod=None, block_state=None) -> None:
+                 prod=None, block_prod=None, block_state=None, _extra_flags: int = 0) -> None:
     """h <- scan(alpha, beta) into a caller-owned tensor, with the optional boundary state."""
     dtype = alpha.dtype
     if dtype not in _DTYPES:
@@ -105,7 +105,7 @@ def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_
     L = _lib.lib()
     with torch.cuda.device(alpha.device):
         ws = workspace.get(alpha.device, L.fss_workspace_bytes(B, T, D, _DTYPES[dtype]))
-        ctx = _ctx(alpha.device, ws, algo, _lib.FLAG_CONTINUATION if continuation else 0)
+        ctx = _ctx(alpha.device, ws, algo, (_lib.FLAG_CONTINUATION if continuation else 0) | _extra_flags)
         state = None
         if any(x is not None for x in (h_in, h_last, prod, block_prod, block_state)):
             state = _lib.ForwardState(_vec(h_in, B, D, "h_in"), _vec(h_last, B, D, "h_last"),

@@ -88,6 +88,13 @@ typedef struct fss_scan_ctx {
 /* Treat the tensors as rows s..s+T-1 of a longer sequence: row 0 DOES read alpha_0 (forward
  * h_0 = a_0*h_in + b_0; the returned product includes a_0) instead of the h_0 = b_0 rule.      */
 #define FSS_FLAG_CONTINUATION 1
+/* Test hooks for the bounded waits of the single-pass kernels (no effect on results otherwise):
+ * SHORT_WAITS lets every wait give up after a few thousand polls instead of ~a second;
+ * MUTE_FIRST_BLOCK makes the tiles of the first row block publish no descriptors, so that the
+ * tiles after them wait for something that never arrives, give up, set the status word to
+ * FSS_STATUS_LOOKBACK_TIMEOUT and leave (their outputs are then undefined). */
+#define FSS_FLAG_TEST_SHORT_WAITS 0x100
+#define FSS_FLAG_TEST_MUTE_FIRST_BLOCK 0x200
 
 /* Optional per-column state vectors, all fp32, contiguous [B, D]; any may be NULL. */
 typedef struct fss_forward_state {

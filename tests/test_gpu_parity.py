@@ -346,3 +346,32 @@ def test_boundary_state_vectors_continue_a_scan():
         native.forward_into(a[:, :400], b[:, :400], h1, algo=_algo_id(algo), h_last=last)
         native.forward_into(a[:, 400:], b[:, 400:], h2, algo=_algo_id(algo), continuation=True, h_in=last)
         assert torch.allclose(torch.cat([h1, h2], 1), full, rtol=1e-5, atol=1e-5), algo
+
+
+def test_bounded_waits_give_up_report_and_recover():
+    """Failure detection without a fault: the first row block is told to publish no descriptors
+    (a flag that nothing sets), waits are shortened; the tiles behind it must give up, set the
+    status word, leave the kernel, and the next ordinary launch must work again."""
+    pkg, native, _lib = _mods()
+    from fast_sequential_scan_b200 import workspace
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    shape = (2, 4096, 256)
+    a = torch.sigmoid(torch.randn(shape, generator=gen, device="cuda")).bfloat16()
+    b = torch.randn(shape, generator=gen, device="cuda").bfloat16()
+    h = torch.empty_like(a)
+    native.forward_into(a, b, h, algo=_lib.ALGO_LOOKBACK)             # sanity: healthy launch
+    pkg.check_status()
+    native.forward_into(a, b, h, algo=_lib.ALGO_LOOKBACK,
+                        _extra_flags=_lib.FLAG_TEST_SHORT_WAITS | _lib.FLAG_TEST_MUTE_FIRST_BLOCK)
+    torch.cuda.synchronize()                                          # the kernel must terminate by itself
+    ws = workspace.get.__globals__["_cache"]
+    # whichever bounded wait ran out first reports: the look-back itself (1) or a stage wait behind it (2)
+    assert any(int(w.status[0]) in (1, 2) for w in ws.values()), "no give-up was reported"
+    with pytest.raises(RuntimeError, match="fss_b200 kernel reported"):
+        pkg.check_status()
+    # recovered: same workspace, ordinary launch, correct result
+    ref = torch.empty_like(a)
+    native.forward_into(a, b, ref, algo=_lib.ALGO_CHUNKED)
+    native.forward_into(a, b, h, algo=_lib.ALGO_LOOKBACK)
+    pkg.check_status()
+    assert_parity(h, ref.float(), BF16_TOL, "h after recovery")

@@ -375,3 +375,28 @@ def test_bounded_waits_give_up_report_and_recover():
     native.forward_into(a, b, h, algo=_lib.ALGO_LOOKBACK)
     pkg.check_status()
     assert_parity(h, ref.float(), BF16_TOL, "h after recovery")
+
+
+def test_config5_full_length_on_one_gpu():
+    """The whole 524,288-row sequence of configuration 5 (2.1 G elements, 4.3 GB per tensor) on one
+    device: 64-bit offsets, 2,048 row blocks per column.  Oracle on a channel subset, all rows."""
+    _, native, _ = _mods()
+    import fast_sequential_scan_b200 as pkg
+    B, T, D = 1, 524288, 4096
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    a = (0.9 + 0.0999 * torch.rand(B, T, D, generator=gen, device="cuda")).bfloat16()
+    b = torch.randn(B, T, D, generator=gen, device="cuda").bfloat16()
+    g = torch.randn(B, T, D, generator=gen, device="cuda").bfloat16()
+    h = torch.empty_like(a)
+    native.forward_into(a, b, h)
+    da, db = torch.empty_like(a), torch.empty_like(a)
+    native.backward_into(a, h, g, da, db)
+    pkg.check_status()
+    idx = torch.tensor([0, 1, 127, 128, 2047, 2048, 4095], device="cuda")
+    sub = lambda t: t.index_select(2, idx).contiguous()
+    h_ref, _, _ = oracle.reference_values(sub(a), sub(b), None)
+    assert_parity(sub(h), h_ref, BF16_TOL, "h")
+    da_ref, db_ref = oracle.scan_backward_f32(sub(a).float().cpu().numpy(), sub(h).float().cpu().numpy(),
+                                              sub(g).float().cpu().numpy())
+    assert_parity(sub(db), torch.from_numpy(db_ref), BF16_TOL, "dbeta")
+    assert_parity(sub(da), torch.from_numpy(da_ref), BF16_TOL, "dalpha")

@@ -525,9 +525,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // use and, if it was not there yet, once more when the unit starts
         typename IncPk::Raw pre;
         bool have_pre = false;
-#ifndef FSS_NO_PRE
         if (lb < n_my && it.s > 0) { IncPk::load_raw(inc_packets(it.k - p.ncols), pre); have_pre = true; }
-#endif
 
         for (int64_t i = lb; i < n_my; i += kLookbackWarps) {
             const int g = (int)(i % kGens);

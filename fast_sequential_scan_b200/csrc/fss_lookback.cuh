@@ -1,32 +1,34 @@
 // FSS_ALGO_LOOKBACK: the single-pass path.  One persistent launch per direction; every tensor
 // byte crosses HBM once (forward 3 tensors, backward 5).
 //
-// Work unit: a tile of kTc = 64 rows x 256 bytes of channels (128 bf16 / 64 fp32 channels) of one
-// batch row.  Tiles are numbered row-block-major (all columns of the first row block, then the
-// next ...; the backward numbers row blocks from the end), CTA c of G takes tiles c, c+G, c+2G...
-// so a tile only ever depends on tiles with smaller numbers, which are always resident or done.
+// Work unit: a 16 KiB tile per tensor of one batch row: 64 rows x 256 bytes of channels, or
+// 128 x 128 / 256 x 64 when the problem has too few columns to fill the GPU otherwise (kSp = 2 / 4).
+// Tiles are numbered row-block-major (all columns of the first row block, then the next ...; the
+// backward numbers row blocks from the end), CTA c of G takes tiles c, c+G, c+2G... so a tile only
+// ever depends on tiles with smaller numbers, which are always resident or done.
 //
-// A CTA runs four roles, coupled only by shared-memory mbarriers:
+// A CTA (12 warps, one per SM) runs five roles, coupled only by shared-memory mbarriers:
 //   producer warp (1 thread)  TMA-loads the tiles of upcoming work units into a ring of stages
-//                             (cp.async.bulk.tensor, complete_tx on full[stage]) and refills a
-//                             stage as soon as its unit is finished.
-//   8 consumer warps          each owns 8 rows of the tile, each lane 8 bytes of channels.
-//                             pass 1: scan own rows from a zero state -> (P, C) to shared memory;
-//                             pass 2: re-scan from the true entering state and store the results
-//                             straight from registers (a warp writes 256 contiguous bytes per row).
-//                             Software-pipelined: pass 1 runs kLead units ahead of pass 2, so the
-//                             carry resolution below is off the critical path.
-//   summary warp              folds the 8 warp summaries of a unit into the tile summary and
-//                             publishes it at once, so that successors never wait for this tile's
-//                             own carry resolution.
+//                             (cp.async.bulk.tensor, complete_tx on full[stage]); when pass 2 has
+//                             finished a unit it TMA-stores the results from the same stage and
+//                             refills it.
+//   4 pass-1 warps            a tile has 4 * kSp row groups of 16 rows; lane (q, cl) of warp w owns
+//                             group q*4 + w and 8 bytes of channels.  Scans its rows from a zero
+//                             state as soon as the tile has landed and leaves (P, C) in shared memory.
+//   summary warp              folds the row-group summaries of a unit into per-group exclusive
+//                             prefixes and the tile summary, and publishes the latter at once, so
+//                             that successors never wait for this tile's own carry resolution.
 //   2 look-back warps         take units alternately: resolve the state entering the tile by
 //                             decoupled look-back over the global descriptors of its predecessors,
-//                             hand every consumer warp its entering state, publish the tile's
-//                             inclusive descriptor.
+//                             hand it to pass 2, publish the tile's inclusive descriptor.
 //                             A descriptor is a set of 8-byte cells {fp32 value, tag}, each moved
 //                             with relaxed gpu-scope 64-bit accesses: a cell whose tag carries this
 //                             launch's epoch is complete by itself -- no flag word, no fence, one L2
 //                             round trip per look-back step, several predecessors read at once.
+//   4 pass-2 warps            re-scan the rows from the true entering state and overwrite the
+//                             stage in place (beta -> h; grad -> dbeta, h -> dalpha).
+// The roles' loops are kept small on purpose (32-bit unit counters, no division, no unrolling
+// across units): the kernel is sensitive to instruction-cache misses.
 // Every wait is bounded; a wait that runs out records a status, raises the abort flag that all
 // other waits poll, and the CTA drains its copies and leaves.
 #pragma once
@@ -100,8 +102,10 @@ struct Params {
     int32_t tile_rows;       // rows per tile: 64 * split
     uint32_t max_spins;      // iterations a wait may take before it gives up
     int mute_first_block;    // test hook: row block 0 publishes no descriptors (its successors' waits run out)
-    int64_t grid;            // CTAs of the launch, and grid = grid_q * ncols + grid_r
-    int32_t grid_q, grid_r;
+    int64_t grid;            // CTAs of the launch
+    int32_t units_q, units_r;   // ntiles = units_q * grid + units_r: CTA x owns units_q + (x < units_r) tiles
+    int32_t grid_q;          // grid stride in whole row blocks, and the rest of it as (batch rows, channel groups):
+    int32_t grid_b, grid_cg; // grid = (grid_q * B + grid_b) * ncg + grid_cg
 
 };
 
@@ -269,6 +273,26 @@ template <> struct Lane<float> {
     static __device__ __forceinline__ Raw pack(const float (&x)[2]) { return make_float2(x[0], x[1]); }
 };
 
+// With 64-byte tile rows the two row groups that share a half-warp read the same 16 banks when
+// both are at row r.  The odd group therefore touches row r^1 in the instruction slot of row r
+// (pair_slot) and swaps each register pair afterwards (pair_fix), before stores likewise.
+template <int kRowStride, typename R>
+__device__ __forceinline__ R &pair_slot(R *tile, int row, int dsw) {
+    return tile[row * kRowStride + ((row & 1) ? -dsw : dsw)];
+}
+template <bool kOn, int N, typename R>
+__device__ __forceinline__ void pair_fix(R (&x)[N], bool odd) {
+    if (kOn) {
+#pragma unroll
+        for (int m = 0; m + 1 < N; m += 2) {
+            // field by field, so that each becomes one select and not a divergent branch
+            const auto lox = odd ? x[m + 1].x : x[m].x, loy = odd ? x[m + 1].y : x[m].y;
+            const auto hix = odd ? x[m].x : x[m + 1].x, hiy = odd ? x[m].y : x[m + 1].y;
+            x[m].x = lox; x[m].y = loy; x[m + 1].x = hix; x[m + 1].y = hiy;
+        }
+    }
+}
+
 // ------------------------------------------------------------------ bounded waits
 struct Ctl {
     Header *hdr;
@@ -284,8 +308,13 @@ struct Ctl {
         atomicExch(&hdr->abort, 1u);
         report_status(status, code);
     }
-    // false = the wait was abandoned (timeout here, or abort raised elsewhere)
+    // false = the wait was abandoned (timeout here, or abort raised elsewhere).  The common case
+    // is one successful try.  (An out-of-line slow path was measured: the call costs more than it saves.)
     __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, int32_t code) const {
+        if (mbar_try_wait(bar, parity)) return true;
+        return wait_slow(bar, parity, code);
+    }
+    __device__ __forceinline__ bool wait_slow(uint32_t bar, uint32_t parity, int32_t code) const {
         for (uint32_t it = 0; it < max_spins; ++it) {
             if (mbar_try_wait(bar, parity)) return *cta_abort == 0;
             if ((it & 63u) == 63u && aborted()) { *cta_abort = 1; return false; }
@@ -306,23 +335,27 @@ template <int kTensors, int kStages> struct Smem {
                                   kBarriers * 8 + 16;
 };
 
-// Position of a CTA's current work unit; advances by one grid stride without 64-bit division.
+// Position of a CTA's current work unit; advances by one grid stride with adds and compares only.
 struct TileIter {
-    int64_t k;        // linear tile number
-    int32_t s, col;   // row block in processing order, column (batch * channel group)
-    __device__ __forceinline__ void init(const Params &p, int64_t first) {
+    int64_t k;           // linear tile number
+    int32_t s, b, cg;    // row block in processing order, batch row, channel group
+    __device__ __forceinline__ void init(const Params &p, uint32_t first) {
         k = first;
-        s = (int32_t)(first / p.ncols);
-        col = (int32_t)(first - (int64_t)s * p.ncols);
+        s = (int32_t)(first / (uint32_t)p.ncols);
+        const uint32_t col = first - (uint32_t)s * (uint32_t)p.ncols;
+        b = (int32_t)(col / (uint32_t)p.ncg);
+        cg = (int32_t)(col - (uint32_t)b * (uint32_t)p.ncg);
     }
     __device__ __forceinline__ void advance(const Params &p) {
         k += p.grid;
         s += p.grid_q;
-        col += p.grid_r;
-        if (col >= (int32_t)p.ncols) { col -= (int32_t)p.ncols; s += 1; }
+        cg += p.grid_cg;
+        b += p.grid_b;
+        if (cg >= (int32_t)p.ncg) { cg -= (int32_t)p.ncg; b += 1; }
+        if (b >= (int32_t)p.B) { b -= (int32_t)p.B; s += 1; }
     }
-    __device__ __forceinline__ int32_t batch(const Params &p) const { return col / (int32_t)p.ncg; }
-    __device__ __forceinline__ int32_t cgroup(const Params &p) const { return col % (int32_t)p.ncg; }
+    __device__ __forceinline__ int32_t batch(const Params &) const { return b; }
+    __device__ __forceinline__ int32_t cgroup(const Params &) const { return cg; }
     template <bool kBackward> __device__ __forceinline__ int32_t row0(const Params &p) const {
         return (kBackward ? ((int32_t)p.S - 1 - s) : s) * p.tile_rows;
     }
@@ -371,8 +404,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     const int q = lane / LPG, cl = lane % LPG;
     FSS_TRACE_LIFE(0, false);
     FSS_TRACE_LIFE(3, true);
-    const int64_t first = blockIdx.x;
-    const int64_t n_my = first < p.ntiles ? (p.ntiles - first + p.grid - 1) / p.grid : 0;
+    const uint32_t first = blockIdx.x;
+    TileIter it0;              // every role starts from the CTA's first unit
+    it0.init(p, first);
+    // units of this CTA; 32-bit on purpose: the per-unit stage and generation arithmetic stays short
+    const int n_my = p.units_q + ((int32_t)first < p.units_r ? 1 : 0);
 
     // Programmatic dependent launch: let the next launch on the stream start its own set-up as SMs
     // become free, and do everything that touches no global memory before waiting for the previous
@@ -401,10 +437,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_alpha) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
             if (kBackward) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_h) : "memory");
-            TileIter ld_it, st_it;
-            ld_it.init(p, first);
-            st_it.init(p, first);
-            auto issue = [&](int64_t i) {
+            TileIter ld_it = it0, st_it = it0;
+            auto issue = [&](int i) {
                 const int st = (int)(i % kStages);
                 const uint32_t base = smem_base + st * SM::kStageBytes;
                 const int32_t c0 = ld_it.cgroup(p) * Dc, c1 = ld_it.template row0<kBackward>(p), c2 = ld_it.batch(p);
@@ -414,9 +448,10 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 if (kBackward) tma_load_3d(base + 2 * kTileBytes, &map_h, bar_full(st), c0, c1 - 1, c2);
                 ld_it.advance(p);
             };
-            int64_t issued = 0;
+            int issued = 0;
             for (; issued < n_my && issued < kStages; ++issued) issue(issued);
-            int64_t i = 0;
+            int i = 0;
+#pragma unroll 1
             for (; i < n_my; ++i) {
                 const int st = (int)(i % kStages);
                 if (!ctl.wait(bar_done(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
@@ -439,7 +474,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             }
             // leave nothing in flight: loads that were issued but never consumed, and all stores
             if (i < n_my) {
-                for (int64_t j = i; j < issued; ++j) {
+                for (int j = i; j < issued; ++j) {
                     const uint32_t bar = bar_full((int)(j % kStages));
                     const uint32_t par = (uint32_t)((j / kStages) & 1);
                     for (uint32_t it = 0; it < p.max_spins && !mbar_try_wait(bar, par); ++it) {}
@@ -457,38 +492,74 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         constexpr int kTilePackets = (AggPk::kPackets + PacketGroup<(kProd ? 2 : 1) * V>::kPackets) * LPG;
         constexpr int kGroups = kW * kSp;          // row groups of a tile, in row order
         const uint32_t tag_agg = (epoch << 2) | kStateAggregate;
-        TileIter it;
-        it.init(p, first);
-        for (int64_t i = 0; i < n_my; ++i) {
+        TileIter it = it0;
+#pragma unroll 1
+        for (int i = 0; i < n_my; ++i) {
             const int g = (int)(i % kGens);
             const int64_t k = it.k;
             const bool last_block = it.s + 1 == (int32_t)p.S;
             const int32_t it_s = it.s;
             it.advance(p);
             if (!ctl.wait(bar_agg(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
-            float pc[2 * V];
+            FSS_TRACE_EV(i, kEvLbA);
+            // Lane (q, cl) owns the kW consecutive row groups q*kW .. q*kW+kW-1 (one per pass-1 warp):
+            // it folds them in scan order, the kSp lane groups are combined with one shuffle scan,
+            // and every slot then receives the map of all groups BEFORE it (its exclusive prefix).
+            // pc ends as the tile's own summary.
+            VecF own_p[kW], own_c[kW];
 #pragma unroll
-            for (int v = 0; v < V; ++v) { pc[v] = 1.0f; pc[V + v] = 0.0f; }
-            // every row group's slot receives the map of the groups BEFORE it (its exclusive prefix);
-            // all lanes with the same channel lane fold the same values, each writes its own slots
+            for (int w = 0; w < kW; ++w) { own_p[w] = agg_at(g, w, 0, lane); own_c[w] = agg_at(g, w, 1, lane); }
+            float iP[V], iC[V];                           // own groups, then inclusive over the lane groups
 #pragma unroll
-            for (int j = 0; j < kGroups; ++j) {
-                const int gamma = kBackward ? kGroups - 1 - j : j;
-                const int w = gamma / kSp, src = (gamma % kSp) * LPG + cl;
-                const VecF ap = agg_at(g, w, 0, src), ac = agg_at(g, w, 1, src);
-                if (kSp > 1) __syncwarp();          // every lane has read the slot before its owner rewrites it
-                if (gamma % kSp == q) {
-                    VecF ep, ec;
+            for (int v = 0; v < V; ++v) { iP[v] = 1.0f; iC[v] = 0.0f; }
 #pragma unroll
-                    for (int v = 0; v < V; ++v) { vec_set(ep, v, pc[v]); vec_set(ec, v, pc[V + v]); }
-                    agg_at(g, w, 0, lane) = ep;
-                    agg_at(g, w, 1, lane) = ec;
-                }
+            for (int ww = 0; ww < kW; ++ww) {
+                const int w = kBackward ? kW - 1 - ww : ww;
 #pragma unroll
                 for (int v = 0; v < V; ++v) {
-                    pc[V + v] = fmaf(vec_get(ap, v), pc[V + v], vec_get(ac, v));
-                    pc[v] *= vec_get(ap, v);
+                    iC[v] = fmaf(vec_get(own_p[w], v), iC[v], vec_get(own_c[w], v));
+                    iP[v] *= vec_get(own_p[w], v);
                 }
+            }
+#pragma unroll
+            for (int d = 1; d < kSp; d <<= 1) {
+                const bool valid = kBackward ? (q + d < kSp) : (q >= d);
+                const int src = (kBackward ? lane + d * LPG : lane - d * LPG) & 31;
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    const float oP = __shfl_sync(0xffffffffu, iP[v], src);
+                    const float oC = __shfl_sync(0xffffffffu, iC[v], src);
+                    if (valid) { iC[v] = fmaf(iP[v], oC, iC[v]); iP[v] *= oP; }       // earlier groups first, then these
+                }
+            }
+            float pc[2 * V], run[2 * V];                  // tile summary; map of the groups before this lane's
+            {
+                const bool has_prev = kBackward ? (q + 1 < kSp) : (q >= 1);
+                const int prev = (kBackward ? lane + LPG : lane - LPG) & 31;
+                const int last = (kBackward ? 0 : kSp - 1) * LPG + cl;      // lane group that ends the tile
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    const float eP = kSp > 1 ? __shfl_sync(0xffffffffu, iP[v], prev) : 1.0f;
+                    const float eC = kSp > 1 ? __shfl_sync(0xffffffffu, iC[v], prev) : 0.0f;
+                    run[v] = has_prev ? eP : 1.0f;
+                    run[V + v] = has_prev ? eC : 0.0f;
+                    pc[v] = kSp > 1 ? __shfl_sync(0xffffffffu, iP[v], last) : iP[v];
+                    pc[V + v] = kSp > 1 ? __shfl_sync(0xffffffffu, iC[v], last) : iC[v];
+                }
+            }
+#pragma unroll
+            for (int ww = 0; ww < kW; ++ww) {
+                const int w = kBackward ? kW - 1 - ww : ww;
+                VecF ep, ec;
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    vec_set(ep, v, run[v]);
+                    vec_set(ec, v, run[V + v]);
+                    run[V + v] = fmaf(vec_get(own_p[w], v), run[V + v], vec_get(own_c[w], v));
+                    run[v] *= vec_get(own_p[w], v);
+                }
+                agg_at(g, w, 0, lane) = ep;
+                agg_at(g, w, 1, lane) = ec;
             }
             VecF sp, sc;
 #pragma unroll
@@ -517,8 +588,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         auto agg_packets = [&](int64_t k) { return p.packets + k * kTilePackets + cl; };
         auto inc_packets = [&](int64_t k) { return p.packets + k * kTilePackets + AggPk::kPackets * LPG + cl; };
 
-        TileIter it;
-        it.init(p, first);
+        TileIter it = it0;
         for (int j = 0; j < lb; ++j) it.advance(p);
 
         // the predecessor's inclusive descriptor is fetched one of this warp's units ahead of its
@@ -527,7 +597,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         bool have_pre = false;
         if (lb < n_my && it.s > 0) { IncPk::load_raw(inc_packets(it.k - p.ncols), pre); have_pre = true; }
 
-        for (int64_t i = lb; i < n_my; i += kLookbackWarps) {
+#pragma unroll 1
+        for (int i = lb; i < n_my; i += kLookbackWarps) {
             const int g = (int)(i % kGens);
             const int64_t k = it.k;
             const int32_t s = it.s, b = it.batch(p);
@@ -697,11 +768,14 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // and leaves (P, C); never waits for a carry, only for the summary buffers to be free.
         using Raw = typename Lane<T>::Raw;
         constexpr int kRowStride = kRowB / (int)sizeof(Raw);
-        const int grp = warp * kSp + q;            // this lane's row group inside the tile
+        const int grp = q * kW + warp;             // this lane's row group inside the tile
+        constexpr bool kPairSwap = kRowB == 64;
+        const bool odd_grp = kPairSwap && (q & 1);
+        const int dsw = odd_grp ? kRowStride : 0;
         const uint32_t lane_off = (uint32_t)(grp * kR) * kRowB + (uint32_t)cl * kLaneBytes;
-        TileIter it;
-        it.init(p, first);
-        for (int64_t i = 0; i < n_my; ++i) {
+        TileIter it = it0;
+#pragma unroll 1
+        for (int i = 0; i < n_my; ++i) {
             const int st = (int)(i % kStages), g = (int)(i % kGens);
             const int32_t row0 = it.template row0<kBackward>(p);
             const bool head = (row0 == 0) && (grp == 0) && !p.continuation;
@@ -710,7 +784,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             const int nvalid = left >= kR ? kR : (left > 0 ? (int)left : 0);
             it.advance(p);
             if (i >= kGens) {      // the summary buffers of this generation are free once pass 2 of unit i-kGens is done
-                const int64_t o = i - kGens;
+                const int o = i - kGens;
                 if (!ctl.wait(bar_done((int)(o % kStages)), (uint32_t)((o / kStages) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
             }
             if (!ctl.wait(bar_full(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
@@ -728,12 +802,17 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             float P[V], C[V];
 #pragma unroll
             for (int v = 0; v < V; ++v) { P[v] = 1.0f; C[v] = 0.0f; }
-#pragma unroll
+#pragma unroll 1
             for (int hb = 0; hb < kR / kRh; ++hb) {
                 const int base = kBackward ? kR - kRh * (hb + 1) : kRh * hb;     // rows of this batch
                 Raw ra[kRh], rx[kRh];
 #pragma unroll
-                for (int r = 0; r < kRh; ++r) { ra[r] = a_t[(base + r) * kRowStride]; rx[r] = x_t[(base + r) * kRowStride]; }
+                for (int r = 0; r < kRh; ++r) {
+                    ra[r] = pair_slot<kRowStride>(a_t, base + r, dsw);
+                    rx[r] = pair_slot<kRowStride>(x_t, base + r, dsw);
+                }
+                pair_fix<kPairSwap>(ra, odd_grp);
+                pair_fix<kPairSwap>(rx, odd_grp);
 #pragma unroll
                 for (int j = 0; j < kRh; ++j) {
                     const int r = kBackward ? kRh - 1 - j : j;
@@ -756,6 +835,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_agg(g));
             if (warp == 0) FSS_TRACE_EV(i, kEvP1);
+            if (warp > 0) FSS_TRACE_EV(i, kEvLbA + warp);
         }
     } else {
         // ============================================================ pass 2
@@ -763,12 +843,15 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         using Raw = typename Lane<T>::Raw;
         constexpr int kRowStride = kRowB / (int)sizeof(Raw);
         const int w2 = warp - kPass2Warp0;
-        const int grp = w2 * kSp + q;
+        const int grp = q * kW + w2;
+        constexpr bool kPairSwap = kRowB == 64;
+        const bool odd_grp = kPairSwap && (q & 1);
+        const int dsw = odd_grp ? kRowStride : 0;
         const uint32_t lane_off = (uint32_t)(grp * kR) * kRowB + (uint32_t)cl * kLaneBytes;
         const int ch = cl * V;
-        TileIter it;
-        it.init(p, first);
-        for (int64_t i = 0; i < n_my; ++i) {
+        TileIter it = it0;
+#pragma unroll 1
+        for (int i = 0; i < n_my; ++i) {
             const int st = (int)(i % kStages), g = (int)(i % kGens);
             const bool head = (it.template row0<kBackward>(p) == 0) && (grp == 0);
             const int32_t b = it.batch(p);
@@ -787,12 +870,17 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
 #pragma unroll
                 for (int v = 0; v < V; ++v) stv[v] = fmaf(vec_get(ep, v), vec_get(vin, v), vec_get(ec, v));
             }
-#pragma unroll
+#pragma unroll 1
             for (int hb = 0; hb < kR / kRh; ++hb) {
                 const int base = kBackward ? kR - kRh * (hb + 1) : kRh * hb;
                 Raw ra[kRh], rx[kRh];
 #pragma unroll
-                for (int r = 0; r < kRh; ++r) { ra[r] = a_t[(base + r) * kRowStride]; rx[r] = x_t[(base + r) * kRowStride]; }
+                for (int r = 0; r < kRh; ++r) {
+                    ra[r] = pair_slot<kRowStride>(a_t, base + r, dsw);
+                    rx[r] = pair_slot<kRowStride>(x_t, base + r, dsw);
+                }
+                pair_fix<kPairSwap>(ra, odd_grp);
+                pair_fix<kPairSwap>(rx, odd_grp);
                 if (!kBackward) {
 #pragma unroll
                     for (int r = 0; r < kRh; ++r) {
@@ -801,12 +889,19 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                         Lane<T>::unpack(rx[r], x);
 #pragma unroll
                         for (int v = 0; v < V; ++v) stv[v] = fmaf(a[v], stv[v], x[v]);
-                        x_t[(base + r) * kRowStride] = Lane<T>::pack(stv);
+                        if (kPairSwap) rx[r] = Lane<T>::pack(stv);
+                        else x_t[(base + r) * kRowStride] = Lane<T>::pack(stv);
+                    }
+                    if (kPairSwap) {
+                        pair_fix<kPairSwap>(rx, odd_grp);
+#pragma unroll
+                        for (int r = 0; r < kRh; ++r) pair_slot<kRowStride>(x_t, base + r, dsw) = rx[r];
                     }
                 } else {
                     Raw rh[kRh];
 #pragma unroll
-                    for (int r = 0; r < kRh; ++r) rh[r] = h_t[(base + r) * kRowStride];
+                    for (int r = 0; r < kRh; ++r) rh[r] = pair_slot<kRowStride>(h_t, base + r, dsw);
+                    pair_fix<kPairSwap>(rh, odd_grp);
                     if (base == 0 && head && p.continuation && p.h_prev) {    // h_{-1} of a continued sequence
                         float hp[V];
 #pragma unroll
@@ -830,8 +925,20 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
 #pragma unroll
                             for (int v = 0; v < V; ++v) da[v] = 0.0f;
                         }
-                        x_t[(base + r) * kRowStride] = Lane<T>::pack(dh);
-                        h_t[(base + r) * kRowStride] = Lane<T>::pack(da);
+                        if (kPairSwap) { rx[r] = Lane<T>::pack(dh); rh[r] = Lane<T>::pack(da); }
+                        else {
+                            x_t[(base + r) * kRowStride] = Lane<T>::pack(dh);
+                            h_t[(base + r) * kRowStride] = Lane<T>::pack(da);
+                        }
+                    }
+                    if (kPairSwap) {
+                        pair_fix<kPairSwap>(rx, odd_grp);
+                        pair_fix<kPairSwap>(rh, odd_grp);
+#pragma unroll
+                        for (int r = 0; r < kRh; ++r) {
+                            pair_slot<kRowStride>(x_t, base + r, dsw) = rx[r];
+                            pair_slot<kRowStride>(h_t, base + r, dsw) = rh[r];
+                        }
                     }
                 }
             }
@@ -1015,8 +1122,11 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
 
     const unsigned grid = (unsigned)(p.ntiles < resident ? p.ntiles : resident);
     p.grid = grid;
+    p.units_q = (int32_t)(p.ntiles / grid);
+    p.units_r = (int32_t)(p.ntiles % grid);
     p.grid_q = (int32_t)(grid / p.ncols);
-    p.grid_r = (int32_t)(grid % p.ncols);
+    p.grid_b = (int32_t)((grid % p.ncols) / p.ncg);
+    p.grid_cg = (int32_t)((grid % p.ncols) % p.ncg);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
@@ -1025,9 +1135,13 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    // Opt-in (FSS_B200_PDL=1): measured on B200 it shortens back-to-back launches of tiny problems
-    // by ~10 % but slows some long backward launches, so it is off unless asked for.
-    static const bool use_pdl = [] { const char *e = getenv("FSS_B200_PDL"); return e && e[0] == '1'; }();
+    // Programmatic dependent launch lets the next launch on the stream set itself up while this one
+    // drains.  Measured on B200 it shortens back-to-back launches of short problems (up to 14 % at
+    // one or two tiles per CTA) but slows long backward launches by a few per cent, so it is used
+    // only when a CTA has at most kPdlMaxUnits tiles.  FSS_B200_PDL=0 / 1 forces it off / on.
+    constexpr int64_t kPdlMaxUnits = 8;
+    static const int pdl_env = [] { const char *e = getenv("FSS_B200_PDL"); return !e ? -1 : (e[0] == '1' ? 1 : 0); }();
+    const bool use_pdl = pdl_env >= 0 ? pdl_env == 1 : p.ntiles <= kPdlMaxUnits * (int64_t)grid;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
     e = cudaLaunchKernelEx(&cfg, scan_kernel<T, kBackward, kProd, kSp>, m_alpha, m_x, m_h, m_o0, m_o1, p);

@@ -16,6 +16,7 @@ LIB_PATH = PKG / "libfss_b200.so"
 DTYPE_BF16, DTYPE_F32 = 0, 1
 ALGO_AUTO, ALGO_CHUNKED, ALGO_LOOKBACK = 0, 1, 2
 FLAG_CONTINUATION = 1
+E_LAYOUT = -5      # FSS_E_LAYOUT
 FLAG_TEST_SHORT_WAITS, FLAG_TEST_MUTE_FIRST_BLOCK = 0x100, 0x200
 
 ALGO_BY_NAME = {"auto": ALGO_AUTO, "chunked": ALGO_CHUNKED, "lookback": ALGO_LOOKBACK}

@@ -156,11 +156,19 @@ static int backward_typed(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t
                           const fss_view *dalpha, const fss_view *dbeta,
                           const fss_backward_state *st) {
     int algo = ctx->algo;
+    // grad_beta written over h (what the reference's bf16 backward always does,
+    // csrc/sequential_scan_kernel.cu:197).  Safe in the look-back kernel: row t of h is read by
+    // the tile that holds row t and, as h_{t-1}, by the tile that holds row t+1; the latter is
+    // earlier in the backward tile order, and this tile's results leave only after its carry
+    // arrived, i.e. after that earlier tile's loads.  The chunked kernels give no such order.
+    const bool inplace = dbeta->ptr == h->ptr;
+    if (inplace && (dbeta->stride_b != h->stride_b || dbeta->stride_t != h->stride_t)) return FSS_E_LAYOUT;
     if (algo != FSS_ALGO_CHUNKED) {
         const bool ok = lookback::layout_ok<T>(B, Tn, D, {alpha, h, grad, dalpha, dbeta});
         if (!ok && algo == FSS_ALGO_LOOKBACK) return FSS_E_LAYOUT;
         algo = ok ? FSS_ALGO_LOOKBACK : FSS_ALGO_CHUNKED;
     }
+    if (inplace && algo == FSS_ALGO_CHUNKED) return FSS_E_LAYOUT;
     if (algo == FSS_ALGO_LOOKBACK)
         return lookback::backward<T>(ctx, plan_workspace(ctx->workspace, ctx->workspace_bytes), B, Tn, D, alpha, h, grad,
                                      dalpha, dbeta, st, &g_cuda_error);

@@ -80,7 +80,7 @@ struct Header {      // first bytes of the workspace
     uint32_t epoch;  // number of look-back launches that have completed on this workspace
     uint32_t done;   // CTAs of the running launch that have finished
     uint32_t abort;  // raised by the first wait that gives up
-    uint32_t pad;
+    uint32_t ticket; // tiles handed out beyond the first kStages per CTA (reset by the last CTA)
 };
 
 struct Params {
@@ -103,9 +103,11 @@ struct Params {
     uint32_t max_spins;      // iterations a wait may take before it gives up
     int mute_first_block;    // test hook: row block 0 publishes no descriptors (its successors' waits run out)
     int64_t grid;            // CTAs of the launch
-    int32_t units_q, units_r;   // ntiles = units_q * grid + units_r: CTA x owns units_q + (x < units_r) tiles
-    int32_t grid_q;          // grid stride in whole row blocks, and the rest of it as (batch rows, channel groups):
-    int32_t grid_b, grid_cg; // grid = (grid_q * B + grid_b) * ncg + grid_cg
+    // fixed tile order (CTA x takes tiles x, x+G, ...): ntiles = units_q * grid + units_r, so CTA x
+    // owns units_q + (x < units_r) tiles; one grid stride = grid_q row blocks + grid_b batch rows +
+    // grid_cg channel groups
+    int32_t units_q, units_r;
+    int32_t grid_q, grid_b, grid_cg;
 
 };
 
@@ -330,35 +332,99 @@ template <int kTensors, int kStages> struct Smem {
     // summaries: [generation][warp][P|C][lane] as 8-byte (fp32 x2) or 16-byte (fp32 x4) entries
     static constexpr int kAggBytes = kGens * kW * 2 * 32 * 16;
     static constexpr int kSumBytes = kGens * 3 * 32 * 16;      // [generation][tile P | tile C | entering state][lane]
-    static constexpr int kBarriers = 2 * kStages + 3 * kGens;
+    static constexpr int kBarriers = 3 * kStages + 3 * kGens;
     static constexpr int kBytes = 128 /* alignment slack */ + kStages * kStageBytes + kAggBytes + kSumBytes +
-                                  kBarriers * 8 + 16;
+                                  kBarriers * 8 + 16 + kStages * 16 /* unit descriptors */;
 };
 
-// Position of a CTA's current work unit; advances by one grid stride with adds and compares only.
-struct TileIter {
-    int64_t k;           // linear tile number
-    int32_t s, b, cg;    // row block in processing order, batch row, channel group
-    __device__ __forceinline__ void init(const Params &p, uint32_t first) {
-        k = first;
-        s = (int32_t)(first / (uint32_t)p.ncols);
-        const uint32_t col = first - (uint32_t)s * (uint32_t)p.ncols;
-        b = (int32_t)(col / (uint32_t)p.ncg);
-        cg = (int32_t)(col - (uint32_t)b * (uint32_t)p.ncg);
-    }
-    __device__ __forceinline__ void advance(const Params &p) {
-        k += p.grid;
-        s += p.grid_q;
-        cg += p.grid_cg;
-        b += p.grid_b;
-        if (cg >= (int32_t)p.ncg) { cg -= (int32_t)p.ncg; b += 1; }
-        if (b >= (int32_t)p.B) { b -= (int32_t)p.B; s += 1; }
-    }
-    __device__ __forceinline__ int32_t batch(const Params &) const { return b; }
-    __device__ __forceinline__ int32_t cgroup(const Params &) const { return cg; }
+// A work unit as the producer describes it to the other roles (one 16-byte shared-memory slot per
+// stage): tile number, row block in processing order, batch row, channel group.  k < 0 ends the CTA.
+struct Unit {
+    int32_t k, s, b, cg;
     template <bool kBackward> __device__ __forceinline__ int32_t row0(const Params &p) const {
         return (kBackward ? ((int32_t)p.S - 1 - s) : s) * p.tile_rows;
     }
+};
+__device__ __forceinline__ Unit unit_of_tile(const Params &p, int64_t tile) {
+    Unit u;
+    u.k = (int32_t)tile;
+    u.s = (int32_t)((uint32_t)tile / (uint32_t)p.ncols);
+    const uint32_t col = (uint32_t)tile - (uint32_t)u.s * (uint32_t)p.ncols;
+    u.b = (int32_t)(col / (uint32_t)p.ncg);
+    u.cg = (int32_t)(col - (uint32_t)u.b * (uint32_t)p.ncg);
+    return u;
+}
+
+// How a role learns which tile its next unit is.
+//   fixed order (kTickets = false): arithmetic only -- CTA x works on tiles x, x+G, x+2G, ...
+//   tickets (kTickets = true): the producer describes every unit in a shared-memory slot per stage
+//     (see the producer) and arrives on info[stage]; a role reads the descriptor of its next unit
+//     while it still waits for the data of the current one, and only blocks if that was too early.
+template <bool kTickets, int kStages> struct UnitCursor {
+    const Params &p;
+    const Ctl &ctl;
+    const Unit *units;
+    uint32_t bar_info0;
+    int stride;          // units between two of this role's units (look-back warps: their number)
+    Unit cur, nxt;       // fixed order: unit i / i + stride.  tickets: nxt valid when `have`
+    bool have;
+    int n_my;
+
+    __device__ __forceinline__ UnitCursor(const Params &p_, const Ctl &ctl_, const Unit *units_, uint32_t bar_info0_)
+        : p(p_), ctl(ctl_), units(units_), bar_info0(bar_info0_) {}
+
+    __device__ __forceinline__ void step(Unit &u, int n) const {      // fixed order: n grid strides on
+        for (int j = 0; j < n; ++j) {
+            u.k += (int32_t)p.grid;
+            u.s += p.grid_q;
+            u.cg += p.grid_cg;
+            u.b += p.grid_b;
+            if (u.cg >= (int32_t)p.ncg) { u.cg -= (int32_t)p.ncg; u.b += 1; }
+            if (u.b >= (int32_t)p.B) { u.b -= (int32_t)p.B; u.s += 1; }
+        }
+    }
+    __device__ __forceinline__ bool try_read(int j, Unit &out) const {   // warp-uniform
+        const int sj = j % kStages;
+        if (!__all_sync(0xffffffffu, mbar_test_wait(bar_info0 + 8u * sj, (uint32_t)((j / kStages) & 1)))) return false;
+        out = units[sj];
+        return true;
+    }
+    // start at unit `first_unit` of the CTA
+    // u0: the CTA's first unit (tile blockIdx.x), worked out once per thread before the roles part
+    __device__ __forceinline__ void init(const Unit &u0, int first_unit, int stride_) {
+        stride = stride_;
+        have = false;
+        if (!kTickets) {
+            n_my = p.units_q + ((int32_t)blockIdx.x < p.units_r ? 1 : 0);
+            nxt = u0;
+            step(nxt, first_unit);
+            have = first_unit < n_my;
+        } else {
+            have = try_read(first_unit, nxt);
+        }
+    }
+    // Unit i into `cur`; false = no more units (or the wait was abandoned).  Then looks ahead to unit
+    // i + stride: next_known() says whether `nxt` already describes a real unit.
+    __device__ __forceinline__ bool advance(int i) {
+        if (!kTickets) {
+            if (i >= n_my) return false;
+            cur = nxt;
+            step(nxt, stride);
+            have = i + stride < n_my;
+            return true;
+        }
+        if (have) {
+            cur = nxt;
+        } else {
+            const int si = i % kStages;
+            if (!ctl.wait(bar_info0 + 8u * si, (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) return false;
+            cur = units[si];
+        }
+        if (cur.k < 0) return false;
+        have = try_read(i + stride, nxt);
+        return true;
+    }
+    __device__ __forceinline__ bool next_known() const { return have && nxt.k >= 0; }
 };
 
 // ------------------------------------------------------------------ the kernel
@@ -366,7 +432,7 @@ struct TileIter {
 // Backward: (alpha, grad, h shifted one row down) are loaded; dbeta is stored from grad's slot,
 // dalpha from h's slot.  Results are written in place in shared memory and leave through TMA
 // stores issued by the producer, so the consumer warps never stall on the global write path.
-template <typename T, bool kBackward, bool kProd, int kSp>
+template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant__ CUtensorMap map_x,
             const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_out0,
@@ -391,6 +457,9 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     const uint32_t bars = smem_base + kStages * SM::kStageBytes + SM::kAggBytes + SM::kSumBytes;
     volatile int *cta_abort = reinterpret_cast<volatile int *>(smem_raw + kStages * SM::kStageBytes +
                                                                SM::kAggBytes + SM::kSumBytes + SM::kBarriers * 8);
+    Unit *units = reinterpret_cast<Unit *>(smem_raw + kStages * SM::kStageBytes + SM::kAggBytes + SM::kSumBytes +
+                                           SM::kBarriers * 8 + 16);
+    auto bar_info = [&](int s) { return bars + 8u * (2 * kStages + 3 * kGens + s); };
     auto bar_full = [&](int s) { return bars + 8u * s; };
     auto bar_done = [&](int s) { return bars + 8u * (kStages + s); };
     auto bar_agg = [&](int g) { return bars + 8u * (2 * kStages + g); };
@@ -405,17 +474,13 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     FSS_TRACE_LIFE(0, false);
     FSS_TRACE_LIFE(3, true);
     const uint32_t first = blockIdx.x;
-    TileIter it0;              // every role starts from the CTA's first unit
-    it0.init(p, first);
-    // units of this CTA; 32-bit on purpose: the per-unit stage and generation arithmetic stays short
-    const int n_my = p.units_q + ((int32_t)first < p.units_r ? 1 : 0);
-
+    const Unit u0 = unit_of_tile(p, first);
     // Programmatic dependent launch: let the next launch on the stream start its own set-up as SMs
     // become free, and do everything that touches no global memory before waiting for the previous
     // launch to finish (both instructions do nothing for an ordinary launch).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_done(s), kW); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_done(s), kW); mbar_init(bar_info(s), 1); }
         for (int g = 0; g < kGens; ++g) { mbar_init(bar_agg(g), kW); mbar_init(bar_carry(g), 1); mbar_init(bar_sum(g), 1); }
         *cta_abort = 0;
         asm volatile("griddepcontrol.wait;" ::: "memory");      // the previous launch and its writes are complete
@@ -425,6 +490,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     __syncthreads();
     FSS_TRACE_LIFE(1, false);
     const Ctl ctl{p.hdr, p.status, cta_abort, p.max_spins};
+    using Cursor = UnitCursor<kTickets, kStages>;
     // This launch's epoch (tags of its descriptors) is only needed by the summary and look-back
     // warps, which read it themselves: the producer's first loads do not wait for this round trip.
     // (The header's epoch changes only after every CTA of the launch has finished.)
@@ -437,45 +503,88 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_alpha) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
             if (kBackward) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_h) : "memory");
-            TileIter ld_it = it0, st_it = it0;
-            auto issue = [&](int i) {
-                const int st = (int)(i % kStages);
+            // Which tile a unit is.  Fixed order: CTA x takes tiles x, x+G, x+2G, ...  Tickets: the same
+            // for the first kStages units, after that every refill takes the next tile from a global
+            // counter, so an SM that the memory system serves faster takes more tiles and all CTAs
+            // finish together (worth it for long, HBM-bound launches; the descriptors cost a little
+            // on short ones).  Tickets are handed out in increasing order and each CTA works through
+            // its own in order, so a tile still only depends on tiles some resident CTA has taken.
+            const int64_t G = p.grid;
+            uint32_t hand = 0;            // ticket requested one refill ahead (hides the atomic's latency)
+            int issued = 0;               // real units whose loads were started
+            int next = 0;                 // slots described so far: the units, then end markers
+            bool ended = false;
+            Unit nu;
+            // prepare() works out what slot `next` will hold: the next unit, or, once the tiles have
+            // run out, an end marker.  post() publishes it and starts the unit's loads.  With tickets,
+            // markers keep being posted as stages free up, because the look-back warps take units
+            // alternately and each has to meet one.  prepare() runs while the stage is still busy, so
+            // its arithmetic and the ticket's round trip stay off the refill path.
+            Cursor fixed(p, ctl, units, bar_info(0));
+            if (!kTickets) fixed.init(u0, 0, 1);
+            auto prepare = [&]() {
+                if (!kTickets) {
+                    ended = !fixed.advance(next);
+                    nu = fixed.cur;
+                    if (ended) nu.k = -1;
+                    return;
+                }
+                int64_t tile = 0;
+                if (!ended) {
+                    if (issued < kStages) {
+                        tile = (int64_t)first + (int64_t)issued * G;
+                        if (issued == kStages - 1) hand = atomicAdd(&p.hdr->ticket, 1u);
+                    } else {
+                        tile = G * kStages + hand;
+                        hand = atomicAdd(&p.hdr->ticket, 1u);
+                    }
+                    ended = tile >= p.ntiles;
+                }
+                if (ended) { nu.k = -1; nu.s = nu.b = nu.cg = 0; }
+                else nu = unit_of_tile(p, tile);
+            };
+            auto post = [&]() {
+                const int st = next % kStages;
+                ++next;
+                units[st] = nu;           // the producer itself reads it back when it stores the unit
+                if (kTickets) mbar_arrive(bar_info(st));
+                if (nu.k < 0) return;
                 const uint32_t base = smem_base + st * SM::kStageBytes;
-                const int32_t c0 = ld_it.cgroup(p) * Dc, c1 = ld_it.template row0<kBackward>(p), c2 = ld_it.batch(p);
+                const int32_t c0 = nu.cg * Dc, c1 = nu.template row0<kBackward>(p), c2 = nu.b;
                 mbar_arrive_expect_tx(bar_full(st), SM::kStageBytes);
                 tma_load_3d(base, &map_alpha, bar_full(st), c0, c1, c2);
                 tma_load_3d(base + kTileBytes, &map_x, bar_full(st), c0, c1, c2);
                 if (kBackward) tma_load_3d(base + 2 * kTileBytes, &map_h, bar_full(st), c0, c1 - 1, c2);
-                ld_it.advance(p);
+                ++issued;
             };
-            int issued = 0;
-            for (; issued < n_my && issued < kStages; ++issued) issue(issued);
-            int i = 0;
+            // One loop for both the initial fill (slots 0 .. kStages-1) and the steady state, in which
+            // slot i + kStages is described when unit i leaves its stage.
+            int i = -kStages;
 #pragma unroll 1
-            for (; i < n_my; ++i) {
-                const int st = (int)(i % kStages);
-                if (!ctl.wait(bar_done(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
+            for (; i < issued; ++i) {
+                const int st = (i + kStages) % kStages;
                 const uint32_t base = smem_base + st * SM::kStageBytes;
-                const int32_t c0 = st_it.cgroup(p) * Dc, c1 = st_it.template row0<kBackward>(p), c2 = st_it.batch(p);
-                st_it.advance(p);
-                if (!kBackward) {
-                    tma_store_3d(&map_out0, base + kTileBytes, c0, c1, c2);          // h
-                } else {
-                    tma_store_3d(&map_out0, base + 2 * kTileBytes, c0, c1, c2);      // dalpha
-                    tma_store_3d(&map_out1, base + kTileBytes, c0, c1, c2);          // dbeta
+                prepare();                            // for slot i + kStages, which lives in this stage
+                if (i >= 0) {
+                    const Unit u = units[st];
+                    const int32_t c0 = u.cg * Dc, c1 = u.template row0<kBackward>(p), c2 = u.b;
+                    if (!ctl.wait(bar_done(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
+                    if (!kBackward) {
+                        tma_store_3d(&map_out0, base + kTileBytes, c0, c1, c2);          // h
+                    } else {
+                        tma_store_3d(&map_out0, base + 2 * kTileBytes, c0, c1, c2);      // dalpha
+                        tma_store_3d(&map_out1, base + kTileBytes, c0, c1, c2);          // dbeta
+                    }
+                    tma_commit();
+                    if (nu.k >= 0) tma_wait_read_all();   // the stage may be overwritten once the store has read it
                 }
-                tma_commit();
-                if (issued < n_my) {
-                    tma_wait_read_all();      // the stage may be overwritten once the store has read it
-                    issue(issued);
-                    ++issued;
-                }
-                FSS_TRACE_EV(i, kEvRefill);
+                post();
+                if (i >= 0) FSS_TRACE_EV(i, kEvRefill);
             }
             // leave nothing in flight: loads that were issued but never consumed, and all stores
-            if (i < n_my) {
-                for (int j = i; j < issued; ++j) {
-                    const uint32_t bar = bar_full((int)(j % kStages));
+            if (i < issued) {
+                for (int j = i < 0 ? 0 : i; j < issued; ++j) {
+                    const uint32_t bar = bar_full(j % kStages);
                     const uint32_t par = (uint32_t)((j / kStages) & 1);
                     for (uint32_t it = 0; it < p.max_spins && !mbar_try_wait(bar, par); ++it) {}
                 }
@@ -490,16 +599,17 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // carry resolution.  This warp never waits on anything outside its CTA.
         using AggPk = PacketGroup<2 * V, LPG>;
         constexpr int kTilePackets = (AggPk::kPackets + PacketGroup<(kProd ? 2 : 1) * V>::kPackets) * LPG;
-        constexpr int kGroups = kW * kSp;          // row groups of a tile, in row order
         const uint32_t tag_agg = (epoch << 2) | kStateAggregate;
-        TileIter it = it0;
+        Cursor cursor(p, ctl, units, bar_info(0));
+        cursor.init(u0, 0, 1);
 #pragma unroll 1
-        for (int i = 0; i < n_my; ++i) {
-            const int g = (int)(i % kGens);
-            const int64_t k = it.k;
-            const bool last_block = it.s + 1 == (int32_t)p.S;
-            const int32_t it_s = it.s;
-            it.advance(p);
+        for (int i = 0;; ++i) {
+            const int g = i % kGens;
+            if (!cursor.advance(i)) break;
+            const Unit u = cursor.cur;
+            const int64_t k = u.k;
+            const bool last_block = u.s + 1 == (int32_t)p.S;
+            const int32_t it_s = u.s;
             if (!ctl.wait(bar_agg(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
             FSS_TRACE_EV(i, kEvLbA);
             // Lane (q, cl) owns the kW consecutive row groups q*kW .. q*kW+kW-1 (one per pass-1 warp):
@@ -588,29 +698,33 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         auto agg_packets = [&](int64_t k) { return p.packets + k * kTilePackets + cl; };
         auto inc_packets = [&](int64_t k) { return p.packets + k * kTilePackets + AggPk::kPackets * LPG + cl; };
 
-        TileIter it = it0;
-        for (int j = 0; j < lb; ++j) it.advance(p);
-
-        // the predecessor's inclusive descriptor is fetched one of this warp's units ahead of its
-        // use and, if it was not there yet, once more when the unit starts
+        // The predecessor's inclusive descriptor is fetched one of this warp's units ahead of its use
+        // (as soon as the producer has described that unit) and, if it was not there yet, once more
+        // when the unit starts.
         typename IncPk::Raw pre;
         bool have_pre = false;
-        if (lb < n_my && it.s > 0) { IncPk::load_raw(inc_packets(it.k - p.ncols), pre); have_pre = true; }
+        Cursor cursor(p, ctl, units, bar_info(0));
+        cursor.init(u0, lb, kLookbackWarps);
+        auto first_look = [&]() {         // start reading the inclusive state before this warp's next unit
+            have_pre = cursor.next_known() && cursor.nxt.s > 0;
+            if (have_pre) IncPk::load_raw(inc_packets((int64_t)cursor.nxt.k - p.ncols), pre);
+        };
+        first_look();
 
 #pragma unroll 1
-        for (int i = lb; i < n_my; i += kLookbackWarps) {
-            const int g = (int)(i % kGens);
-            const int64_t k = it.k;
-            const int32_t s = it.s, b = it.batch(p);
-            const int64_t dch = (int64_t)it.cgroup(p) * Dc + ch;     // channel in the tensor
+        for (int i = lb;; i += kLookbackWarps) {
+            const int g = i % kGens;
+            const bool had_pre = have_pre;
+            if (!cursor.advance(i)) break;
+            const Unit u = cursor.cur;
+            const int64_t k = u.k;
+            const int32_t s = u.s, b = u.b;
+            const int64_t dch = (int64_t)u.cg * Dc + ch;     // channel in the tensor
             const bool ch_ok = dch < p.D;
-            for (int j = 0; j < kLookbackWarps; ++j) it.advance(p);  // -> this warp's next unit
             float cur[NI];
             bool hit = false;
-            if (have_pre) hit = __all_sync(0xffffffffu, IncPk::decode(pre, cur, tag_inc));
-            // first look for this warp's next unit (decoded when that unit starts)
-            have_pre = i + kLookbackWarps < n_my && it.s > 0;
-            if (have_pre) IncPk::load_raw(inc_packets(it.k - p.ncols), pre);
+            if (had_pre) hit = __all_sync(0xffffffffu, IncPk::decode(pre, cur, tag_inc));
+            first_look();                  // for this warp's next unit (decoded when that unit starts)
             // While pass 1 and the summary warp are still working on this unit, keep asking for the
             // predecessor's inclusive state: this warp has nothing else to do, and in the common case
             // the answer is there before the summary is, so the carry costs no extra round trip.
@@ -773,16 +887,18 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         const bool odd_grp = kPairSwap && (q & 1);
         const int dsw = odd_grp ? kRowStride : 0;
         const uint32_t lane_off = (uint32_t)(grp * kR) * kRowB + (uint32_t)cl * kLaneBytes;
-        TileIter it = it0;
+        Cursor cursor(p, ctl, units, bar_info(0));
+        cursor.init(u0, 0, 1);
 #pragma unroll 1
-        for (int i = 0; i < n_my; ++i) {
-            const int st = (int)(i % kStages), g = (int)(i % kGens);
-            const int32_t row0 = it.template row0<kBackward>(p);
+        for (int i = 0;; ++i) {
+            const int st = i % kStages, g = i % kGens;
+            if (!cursor.advance(i)) break;
+            const Unit u = cursor.cur;
+            const int32_t row0 = u.template row0<kBackward>(p);
             const bool head = (row0 == 0) && (grp == 0) && !p.continuation;
             // rows of this group that exist in the sequence (fewer than kR only in the last row block)
             const int64_t left = p.T - row0 - (int64_t)grp * kR;
             const int nvalid = left >= kR ? kR : (left > 0 ? (int)left : 0);
-            it.advance(p);
             if (i >= kGens) {      // the summary buffers of this generation are free once pass 2 of unit i-kGens is done
                 const int o = i - kGens;
                 if (!ctl.wait(bar_done((int)(o % kStages)), (uint32_t)((o / kStages) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
@@ -849,14 +965,16 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         const int dsw = odd_grp ? kRowStride : 0;
         const uint32_t lane_off = (uint32_t)(grp * kR) * kRowB + (uint32_t)cl * kLaneBytes;
         const int ch = cl * V;
-        TileIter it = it0;
+        Cursor cursor(p, ctl, units, bar_info(0));
+        cursor.init(u0, 0, 1);
 #pragma unroll 1
-        for (int i = 0; i < n_my; ++i) {
-            const int st = (int)(i % kStages), g = (int)(i % kGens);
-            const bool head = (it.template row0<kBackward>(p) == 0) && (grp == 0);
-            const int32_t b = it.batch(p);
-            const int64_t dch = (int64_t)it.cgroup(p) * Dc + ch;
-            it.advance(p);
+        for (int i = 0;; ++i) {
+            const int st = i % kStages, g = i % kGens;
+            if (!cursor.advance(i)) break;
+            const Unit u = cursor.cur;
+            const bool head = (u.template row0<kBackward>(p) == 0) && (grp == 0);
+            const int32_t b = u.b;
+            const int64_t dch = (int64_t)u.cg * Dc + ch;
             const Raw *a_t = reinterpret_cast<const Raw *>(smem_raw + st * SM::kStageBytes + lane_off);
             Raw *x_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + kTileBytes + lane_off);
             Raw *h_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + 2 * kTileBytes + lane_off);
@@ -958,6 +1076,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         const uint32_t prev = atomicAdd(&p.hdr->done, 1u);
         if (prev + 1 == gridDim.x) {
             p.hdr->done = 0;
+            p.hdr->ticket = 0;
             p.hdr->abort = 0;
             __threadfence();
             p.hdr->epoch = ld_volatile(&p.hdr->epoch) + 1u;
@@ -976,6 +1095,15 @@ inline int choose_split(int dtype, int64_t B, int64_t T, int64_t D) {
     int s = 1;
     while (s < 4 && cols * s < 2 * 148 && row_bytes >= kRowBytes / s && T >= 2 * kTc * s * 2) s *= 2;
     return s;
+}
+// Tile order: tickets (tiles handed out by a global counter, see the producer) once a tensor is
+// larger than the L2 can hold between the forward and the backward launch -- such launches are
+// HBM-bound from end to end and gain 1-5 % from the balancing; shorter ones lose 2-4 % to the
+// unit descriptors, so they keep the fixed order.  FSS_B200_TICKETS=0 / 1 forces the choice.
+inline bool choose_tickets(int dtype, int64_t B, int64_t T, int64_t D) {
+    static const int env = [] { const char *e = getenv("FSS_B200_TICKETS"); return !e ? -1 : (e[0] == '1' ? 1 : 0); }();
+    if (env >= 0) return env == 1;
+    return B * T * D * (dtype == FSS_DTYPE_BF16 ? 2 : 4) >= (int64_t)96 << 20;
 }
 inline int64_t block_rows(int dtype, int64_t B, int64_t T, int64_t D) { return (int64_t)kTc * choose_split(dtype, B, T, D); }
 
@@ -1058,14 +1186,14 @@ inline bool make_map(CUtensorMap *map, const fss_view *v, int64_t B, int64_t Tn,
 }
 
 // CTAs that fit the device at once (one per SM with these shared-memory sizes), per device.
-template <typename T, bool kBackward, bool kProd, int kSp> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
+template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
     static std::mutex mu;
     static int cached[64];
     static bool have[64];
     std::lock_guard<std::mutex> lock(mu);
     if (device < 0 || device >= 64) { *err = cudaErrorInvalidDevice; return 0; }
     if (!have[device]) {
-        auto kern = scan_kernel<T, kBackward, kProd, kSp>;
+        auto kern = scan_kernel<T, kBackward, kProd, kSp, kTickets>;
         *err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (*err != cudaSuccess) return 0;
         int per_sm = 0, sms = 0;
@@ -1080,7 +1208,7 @@ template <typename T, bool kBackward, bool kProd, int kSp> inline int resident_c
     return cached[device];
 }
 
-template <typename T, bool kBackward, bool kProd, int kSp>
+template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets>
 inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t Tn, int64_t D,
                   const fss_view *alpha, const fss_view *x, const fss_view *h, const fss_view *out0,
                   const fss_view *out1, Params p, std::string *err_text) {
@@ -1103,7 +1231,7 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) { *err_text = cudaGetErrorString(e); return FSS_E_DEVICE; }
-    const int resident = resident_ctas<T, kBackward, kProd, kSp>(device, smem_bytes, &e);
+    const int resident = resident_ctas<T, kBackward, kProd, kSp, kTickets>(device, smem_bytes, &e);
     if (e != cudaSuccess || resident < 1) { *err_text = cudaGetErrorString(e); return FSS_E_LAUNCH; }
 
     p.B = B; p.T = Tn; p.D = D;
@@ -1112,6 +1240,7 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     p.S = ceil_div(Tn, (int64_t)kTc * kSp);
     p.tile_rows = kTc * kSp;
     p.ntiles = p.ncols * p.S;
+    if (p.ntiles > 0x7fffffffLL) return FSS_E_SHAPE;      // tile numbers travel as 32-bit values
     if ((size_t)p.ntiles * (packets_per_tile<T>(kProd) / kSp) * 16 > ws.packet_bytes) return FSS_E_WORKSPACE;
     p.hdr = reinterpret_cast<Header *>(ws.hdr);
     p.packets = reinterpret_cast<uint4 *>(ws.packets);
@@ -1144,7 +1273,7 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     const bool use_pdl = pdl_env >= 0 ? pdl_env == 1 : p.ntiles <= kPdlMaxUnits * (int64_t)grid;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, scan_kernel<T, kBackward, kProd, kSp>, m_alpha, m_x, m_h, m_o0, m_o1, p);
+    e = cudaLaunchKernelEx(&cfg, scan_kernel<T, kBackward, kProd, kSp, kTickets>, m_alpha, m_x, m_h, m_o0, m_o1, p);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { *err_text = std::string("look-back launch: ") + cudaGetErrorString(e); return FSS_E_LAUNCH; }
     return FSS_OK;
@@ -1155,11 +1284,16 @@ inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t 
                   const fss_view *alpha, const fss_view *x, const fss_view *h, const fss_view *out0,
                   const fss_view *out1, Params p, std::string *err_text) {
     const int dtype = sizeof(T) == 2 ? FSS_DTYPE_BF16 : FSS_DTYPE_F32;
+    const bool tickets = kBackward && choose_tickets(dtype, B, Tn, D);    // measured: the forward never gains
+#define FSS_LAUNCH_SPLIT(SP)                                                                                       \
+    return tickets ? launch_split<T, kBackward, kProd, SP, true>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, err_text) \
+                   : launch_split<T, kBackward, kProd, SP, false>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, err_text)
     switch (choose_split(dtype, B, Tn, D)) {
-    case 4: return launch_split<T, kBackward, kProd, 4>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, err_text);
-    case 2: return launch_split<T, kBackward, kProd, 2>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, err_text);
-    default: return launch_split<T, kBackward, kProd, 1>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, err_text);
+    case 4: FSS_LAUNCH_SPLIT(4);
+    case 2: FSS_LAUNCH_SPLIT(2);
+    default: FSS_LAUNCH_SPLIT(1);
     }
+#undef FSS_LAUNCH_SPLIT
 }
 
 template <typename T>

@@ -6,54 +6,99 @@
 * :class:`SequentialScanSingle` / :func:`scan_single` -- fp32, no autocast handling
   (reference: scan_cuda.py:36-54).
 
-Both save ``(alpha, h)`` and compute the gradients with the reverse scan
-``dh_t = g_t + alpha_{t+1} dh_{t+1}``, ``dbeta = dh``, ``dalpha_t = dh_t h_{t-1}``.
+Both compute the gradients with the reverse scan ``dh_t = g_t + alpha_{t+1} dh_{t+1}``,
+``dbeta = dh``, ``dalpha_t = dh_t h_{t-1}``.  What they keep for it is chosen by ``backward_mode``:
+
+``"saved"`` (default)
+    save ``(alpha, h)``; ``grad_beta`` is a fresh tensor, ``h`` stays valid after ``backward``.
+``"inplace"``
+    save ``(alpha, h)``; ``grad_beta`` is written over ``h``'s storage, so the backward allocates one
+    tensor instead of two and ``h`` must not be read after ``backward``.  This is what the reference's
+    bf16 backward always does (csrc/sequential_scan_kernel.cu:197, ``grad_beta = h_saved``).
+``"recompute"``
+    save ``(alpha, beta)`` only; the backward first scans them again into a temporary ``h`` (6 more
+    bytes of traffic per element in bf16) and then overwrites that temporary with ``grad_beta``.
+    The forward output is not kept alive by the graph, which matters when the caller drops it.
 """
 from __future__ import annotations
 
-from typing import Any, Tuple
+from typing import Any, Optional, Tuple
 
 import torch
 from torch.autograd import Function
 
 from .sequential_scan_cuda import scan_backward, scan_backward_half, scan_forward, scan_forward_half
 
+BACKWARD_MODES = ("saved", "inplace", "recompute")
+_default_mode = "saved"
+
+
+def set_backward_mode(mode: str) -> str:
+    """Set the process-wide default ``backward_mode``; returns the previous one."""
+    global _default_mode
+    if mode not in BACKWARD_MODES:
+        raise ValueError(f"backward_mode must be one of {BACKWARD_MODES}, got {mode!r}")
+    previous, _default_mode = _default_mode, mode
+    return previous
+
+
+def _resolve(mode: Optional[str]) -> str:
+    mode = _default_mode if mode is None else mode
+    if mode not in BACKWARD_MODES:
+        raise ValueError(f"backward_mode must be one of {BACKWARD_MODES}, got {mode!r}")
+    return mode
+
+
+def _forward(ctx: Any, fwd, alpha: torch.Tensor, beta: torch.Tensor, mode: Optional[str]) -> torch.Tensor:
+    ctx.backward_mode = _resolve(mode)
+    h = fwd(alpha, beta)
+    if ctx.backward_mode == "recompute":
+        ctx.save_for_backward(alpha, beta)
+    else:
+        ctx.save_for_backward(alpha, h)
+    return h
+
+
+def _backward(ctx: Any, fwd, bwd, grad_output: torch.Tensor):
+    if ctx.backward_mode == "recompute":
+        alpha, beta = ctx.saved_tensors
+        h = fwd(alpha, beta)                       # a temporary nobody else sees: reuse it for grad_beta
+        alpha_grad, beta_grad = bwd(alpha, h, grad_output, True)
+    else:
+        alpha, h = ctx.saved_tensors
+        alpha_grad, beta_grad = bwd(alpha, h, grad_output, ctx.backward_mode == "inplace")
+    return alpha_grad, beta_grad, None             # trailing None as in the reference (scan_cuda.py:33)
+
 
 class SequentialScan(Function):
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
-    def forward(ctx: Any, input_alpha: torch.Tensor, input_beta: torch.Tensor) -> torch.Tensor:
-        h = scan_forward_half(input_alpha, input_beta)
-        ctx.save_for_backward(input_alpha, h)
-        return h
+    def forward(ctx: Any, input_alpha: torch.Tensor, input_beta: torch.Tensor,
+                backward_mode: Optional[str] = None) -> torch.Tensor:
+        return _forward(ctx, scan_forward_half, input_alpha, input_beta, backward_mode)
 
     @staticmethod
     @torch.amp.custom_bwd(device_type="cuda")
-    def backward(ctx: Any, grad_output: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        input_alpha, h = ctx.saved_tensors
-        alpha_grad, beta_grad = scan_backward_half(input_alpha, h, grad_output)
-        return alpha_grad, beta_grad
+    def backward(ctx: Any, grad_output: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, None]:
+        return _backward(ctx, scan_forward_half, scan_backward_half, grad_output)
 
 
 class SequentialScanSingle(Function):
     @staticmethod
-    def forward(ctx: Any, input_alpha: torch.Tensor, input_beta: torch.Tensor) -> torch.Tensor:
-        h = scan_forward(input_alpha, input_beta)
-        ctx.save_for_backward(input_alpha, h)
-        return h
+    def forward(ctx: Any, input_alpha: torch.Tensor, input_beta: torch.Tensor,
+                backward_mode: Optional[str] = None) -> torch.Tensor:
+        return _forward(ctx, scan_forward, input_alpha, input_beta, backward_mode)
 
     @staticmethod
-    def backward(ctx: Any, grad_output: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        input_alpha, h = ctx.saved_tensors
-        alpha_grad, beta_grad = scan_backward(input_alpha, h, grad_output)
-        return alpha_grad, beta_grad
+    def backward(ctx: Any, grad_output: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, None]:
+        return _backward(ctx, scan_forward, scan_backward, grad_output)
 
 
-def scan(alpha: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
+def scan(alpha: torch.Tensor, beta: torch.Tensor, *, backward_mode: Optional[str] = None) -> torch.Tensor:
     """bf16 scan ``h_0 = beta_0; h_t = alpha_t * h_{t-1} + beta_t`` over ``[batch, seq, d_model]``."""
-    return SequentialScan.apply(alpha, beta)
+    return SequentialScan.apply(alpha, beta, backward_mode)
 
 
-def scan_single(alpha: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
+def scan_single(alpha: torch.Tensor, beta: torch.Tensor, *, backward_mode: Optional[str] = None) -> torch.Tensor:
     """fp32 variant of :func:`scan`."""
-    return SequentialScanSingle.apply(alpha, beta)
+    return SequentialScanSingle.apply(alpha, beta, backward_mode)

@@ -159,9 +159,19 @@ def _forward(alpha: torch.Tensor, beta: torch.Tensor, dtype: torch.dtype) -> tor
     return h
 
 
-def _backward(alpha_saved, h_saved, grad_out, dtype) -> List[torch.Tensor]:
+def _backward(alpha_saved, h_saved, grad_out, dtype, inplace_grad_beta: bool = False) -> List[torch.Tensor]:
     _check_tensor("alpha_saved", alpha_saved, None, dtype)
     grad_alpha = torch.empty(alpha_saved.shape, dtype=dtype, device=alpha_saved.device)
+    if inplace_grad_beta and h_saved.is_contiguous():
+        # grad_beta overwrites h_saved (reference: csrc/sequential_scan_kernel.cu:197 does this
+        # unconditionally for bf16).  Only the single-pass kernel can; if the layout sends the
+        # call to the chunked kernels the library refuses and a separate buffer is used instead.
+        try:
+            backward_into(alpha_saved, h_saved, grad_out, grad_alpha, h_saved)
+            return [grad_alpha, h_saved]
+        except _lib.FssError as e:
+            if e.code != _lib.E_LAYOUT:
+                raise
     grad_beta = torch.empty(alpha_saved.shape, dtype=dtype, device=alpha_saved.device)
     backward_into(alpha_saved, h_saved, grad_out, grad_alpha, grad_beta)
     return [grad_alpha, grad_beta]
@@ -172,9 +182,10 @@ def scan_forward(alpha: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
     return _forward(alpha, beta, torch.float32)
 
 
-def scan_backward(alpha_saved, h_saved, grad_out) -> List[torch.Tensor]:
-    """fp32 backward, ``[grad_alpha, grad_beta]`` (reference: csrc/sequential_scan_kernel.cu:60-124)."""
-    return _backward(alpha_saved, h_saved, grad_out, torch.float32)
+def scan_backward(alpha_saved, h_saved, grad_out, inplace_grad_beta: bool = False) -> List[torch.Tensor]:
+    """fp32 backward, ``[grad_alpha, grad_beta]`` (reference: csrc/sequential_scan_kernel.cu:60-124).
+    With ``inplace_grad_beta`` the second result is ``h_saved`` itself, overwritten."""
+    return _backward(alpha_saved, h_saved, grad_out, torch.float32, inplace_grad_beta)
 
 
 def scan_forward_half(alpha: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
@@ -182,9 +193,10 @@ def scan_forward_half(alpha: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
     return _forward(alpha, beta, torch.bfloat16)
 
 
-def scan_backward_half(alpha_saved, h_saved, grad_out) -> List[torch.Tensor]:
-    """bf16 backward (reference: csrc/sequential_scan_kernel.cu:189-268)."""
-    return _backward(alpha_saved, h_saved, grad_out, torch.bfloat16)
+def scan_backward_half(alpha_saved, h_saved, grad_out, inplace_grad_beta: bool = False) -> List[torch.Tensor]:
+    """bf16 backward (reference: csrc/sequential_scan_kernel.cu:189-268).  ``grad_beta`` is a fresh
+    tensor unless ``inplace_grad_beta`` asks for the reference's aliasing (csrc/sequential_scan_kernel.cu:197)."""
+    return _backward(alpha_saved, h_saved, grad_out, torch.bfloat16, inplace_grad_beta)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -134,7 +134,12 @@ int fss_workspace_init(void *workspace, size_t bytes, void *stream);
 int fss_scan_forward(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
                      const fss_view *alpha, const fss_view *beta, const fss_view *h);
 /* fp32 backward.  Replaces scan_backward (csrc/sequential_scan.cpp:4-6,15;
- * csrc/sequential_scan_kernel.cu:60-124).  h is the saved forward output. */
+ * csrc/sequential_scan_kernel.cu:60-124).  h is the saved forward output.
+ * In all backward entry points grad_beta may be the very same view as h (same pointer and
+ * strides): the gradient then overwrites the saved output, as the reference's bf16 backward
+ * does implicitly (csrc/sequential_scan_kernel.cu:197).  Only the look-back algorithm can do
+ * this; when the call resolves to FSS_ALGO_CHUNKED it returns FSS_E_LAYOUT and launches
+ * nothing.  Any other overlap between the five tensors is not allowed. */
 int fss_scan_backward(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
                       const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
                       const fss_view *grad_alpha, const fss_view *grad_beta);
@@ -143,7 +148,8 @@ int fss_scan_backward(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
 int fss_scan_forward_half(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
                           const fss_view *alpha, const fss_view *beta, const fss_view *h);
 /* bf16 backward.  Replaces scan_backward_half (csrc/sequential_scan.cpp:9-11,21;
- * csrc/sequential_scan_kernel.cu:189-268).  grad_beta is its own buffer here. */
+ * csrc/sequential_scan_kernel.cu:189-268).  grad_beta is its own buffer unless the caller
+ * passes h's view for it (see fss_scan_backward). */
 int fss_scan_backward_half(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D,
                            const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
                            const fss_view *grad_alpha, const fss_view *grad_beta);

@@ -253,6 +253,65 @@ def test_non_default_stream_and_saved_output_untouched():
     assert_parity(h, h_ref, BF16_TOL, "h on side stream")
 
 
+@pytest.mark.parametrize("mode", ["inplace", "recompute"])
+@pytest.mark.parametrize("fp32", [False, True])
+@pytest.mark.parametrize("shape", [(2, 1024, 768), (4, 3000, 2048), (3, 257, 100), (2, 65, 7)])
+def test_memory_saving_backward_modes(shape, fp32, mode):
+    """The reference's bf16 backward writes grad_beta over the saved h
+    (csrc/sequential_scan_kernel.cu:197); here that is the opt-in mode "inplace", and "recompute"
+    keeps (alpha, beta) instead of h.  Both must give bit-for-bit the gradients of the default
+    mode -- the same kernels run on the same values -- on TMA-eligible layouts and on layouts
+    that fall back to the chunked kernels (where "inplace" quietly uses a separate buffer)."""
+    pkg, native, _ = _mods()
+    fn = pkg.scan_cu_single if fp32 else pkg.scan_cu
+    dtype = torch.float32 if fp32 else torch.bfloat16
+    gen = torch.Generator().manual_seed(11)
+    a0 = torch.sigmoid(torch.randn(shape, generator=gen)).to(dtype).cuda()
+    b0 = torch.randn(shape, generator=gen).to(dtype).cuda()
+    g = torch.randn(shape, generator=gen).to(dtype).cuda()
+
+    def run(m):
+        a, b = a0.clone().requires_grad_(), b0.clone().requires_grad_()
+        h = fn(a, b, backward_mode=m)
+        h_keep = h.detach().clone()
+        h.backward(g)
+        return h, h_keep, a.grad, b.grad
+
+    h_ref, h_ref_keep, da_ref, db_ref = run("saved")
+    assert torch.equal(h_ref, h_ref_keep)                   # default mode leaves the output alone
+    h, h_keep, da, db = run(mode)
+    pkg.check_status()
+    assert torch.equal(h_keep, h_ref_keep)
+    assert torch.equal(da, da_ref) and torch.equal(db, db_ref)
+    if mode == "inplace" and native.tma_eligible(a0, b0, g):
+        assert torch.equal(h.detach(), db_ref)              # h's storage now holds grad_beta
+    if mode == "recompute":
+        assert torch.equal(h.detach(), h_ref_keep)          # the returned output was never touched
+
+
+def test_inplace_grad_beta_through_the_c_abi():
+    """grad_beta == h is accepted by the single-pass kernel and refused (FSS_E_LAYOUT, nothing
+    launched) when the call resolves to the chunked kernels."""
+    _, native, _lib = _mods()
+    gen = torch.Generator().manual_seed(3)
+    shape = (2, 2048, 1024)
+    a = torch.rand(shape, generator=gen).to(torch.bfloat16).cuda()
+    b = torch.randn(shape, generator=gen).to(torch.bfloat16).cuda()
+    g = torch.randn(shape, generator=gen).to(torch.bfloat16).cuda()
+    h = torch.empty_like(a)
+    native.forward_into(a, b, h)
+    da_ref, db_ref = torch.empty_like(a), torch.empty_like(a)
+    native.backward_into(a, h, g, da_ref, db_ref)
+    h2, da = h.clone(), torch.empty_like(a)
+    with pytest.raises(_lib.FssError) as err:
+        native.backward_into(a, h2, g, da, h2, algo=_algo_id("chunked"))
+    assert err.value.code == _lib.E_LAYOUT and torch.equal(h2, h)
+    native.backward_into(a, h2, g, da, h2, algo=_algo_id("lookback"))
+    assert torch.equal(da, da_ref) and torch.equal(h2, db_ref)
+    got = native.scan_backward_half(a, h.clone(), g, inplace_grad_beta=True)
+    assert torch.equal(got[0], da_ref) and torch.equal(got[1], db_ref)
+
+
 @pytest.mark.parametrize("shape", [(4, 4096, 2048), (2, 8192, 1024), (1, 16384, 512)])
 def test_lookback_descriptors_survive_reuse_with_different_data(shape):
     """Consecutive launches on one workspace with DIFFERENT inputs of one shape: a stale tile

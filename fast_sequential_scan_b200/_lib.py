@@ -64,6 +64,8 @@ SIGNATURES = {
                                     _P(ForwardState)]),
     "fss_scan_backward_ex": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64] + [_P(View)] * 5
                              + [_P(BackwardState)]),
+    "fss_scan_forward_gated": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View),
+                                       c_void_p, _P(View), _P(ForwardState)]),
     "fss_block_rows": (c_int64, [c_int, c_int64, c_int64, c_int64, c_int]),
     "fss_seqpar_compose": (c_int, [_P(ScanCtx), c_int, c_int, c_int, c_int64, c_void_p, c_void_p]),
     "fss_seqpar_fixup_forward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View),

@@ -242,6 +242,30 @@ FSS_API int fss_scan_forward_ex(const fss_scan_ctx *ctx, int dtype, int64_t B, i
                : forward_typed<float>(ctx, dtype, B, T, D, alpha, beta, h, state);
 }
 
+FSS_API int fss_scan_forward_gated(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                                   const fss_view *r, const fss_view *i, const fss_view *x,
+                                   const float *lambda, const fss_view *h, const fss_forward_state *state) {
+    int rc;
+    if ((rc = check_ctx(ctx))) return rc;
+    if ((rc = check_shape(dtype, B, T, D))) return rc;
+    if (B == 0 || T == 0 || D == 0) return FSS_OK;
+    if (!lambda) return FSS_E_NULL;
+    for (const fss_view *v : {r, i, x, h})
+        if ((rc = check_view(v, B, T, D))) return rc;
+    if (state && (state->prod || state->block_prod || state->block_state)) return FSS_E_ARGS;
+    if (ctx->algo == FSS_ALGO_CHUNKED) return FSS_E_LAYOUT;       // single-pass kernel only
+    if ((rc = need_workspace(ctx, B, T, D, dtype))) return rc;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    const WsPlan ws = plan_workspace(ctx->workspace, ctx->workspace_bytes);
+    if (dtype == FSS_DTYPE_BF16) {
+        if (!lookback::layout_ok<bf16>(B, T, D, {r, i, x, h})) return FSS_E_LAYOUT;
+        return lookback::forward_gated<bf16>(ctx, ws, B, T, D, r, i, x, lambda, h, state, &g_cuda_error);
+    }
+    if (!lookback::layout_ok<float>(B, T, D, {r, i, x, h})) return FSS_E_LAYOUT;
+    return lookback::forward_gated<float>(ctx, ws, B, T, D, r, i, x, lambda, h, state, &g_cuda_error);
+}
+
 FSS_API int fss_scan_backward_ex(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
                                  const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
                                  const fss_view *grad_alpha, const fss_view *grad_beta,

@@ -98,6 +98,7 @@ struct Params {
     float *block_prod;       // [B, S, D]
     float *block_state;      // [B, S, D]
     const float *h_prev;     // backward only
+    const float *lambda;     // gated forward only: [D]
     int continuation;
     int32_t tile_rows;       // rows per tile: 64 * split
     uint32_t max_spins;      // iterations a wait may take before it gives up
@@ -427,18 +428,49 @@ template <bool kTickets, int kStages> struct UnitCursor {
     __device__ __forceinline__ bool next_known() const { return have && nxt.k >= 0; }
 };
 
+// ------------------------------------------------------------------ gate front-end
+// RG-LRU gates evaluated in the kernel (gated forward):  a = exp(c * sigmoid(r)) with
+// c = -8 * softplus(lambda) per channel, b = sqrt(1 - a^2) * sigmoid(i) * x.  bf16 I/O rounds a and
+// b to 8 mantissa bits anyway, so it takes the 1-MUFU forms (tanh.approx, ex2.approx, sqrt.approx:
+// 4 special-function operations per element keep the kernel under the HBM time); fp32 I/O uses
+// the accurate library functions.
+template <typename T> struct Gate;
+template <> struct Gate<bf16> {
+    static __device__ __forceinline__ float sigmoid(float z) {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * z));
+        return fmaf(0.5f, t, 0.5f);
+    }
+    static __device__ __forceinline__ float exp_neg(float z) { return __expf(z); }
+    static __device__ __forceinline__ float root(float z) {
+        float r;
+        asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(z));
+        return r;
+    }
+};
+template <> struct Gate<float> {
+    static __device__ __forceinline__ float sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+    static __device__ __forceinline__ float exp_neg(float z) { return expf(z); }
+    static __device__ __forceinline__ float root(float z) { return sqrtf(z); }
+};
+__device__ __forceinline__ float gate_scale(float lambda) {      // -8 * softplus(lambda)
+    return -8.0f * (lambda > 20.0f ? lambda : log1pf(expf(lambda)));
+}
+
 // ------------------------------------------------------------------ the kernel
 // Forward: tiles of (alpha, beta) are loaded, h is stored from beta's stage slot.
 // Backward: (alpha, grad, h shifted one row down) are loaded; dbeta is stored from grad's slot,
 // dalpha from h's slot.  Results are written in place in shared memory and leave through TMA
 // stores issued by the producer, so the consumer warps never stall on the global write path.
-template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets>
+template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets, bool kGate = false>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant__ CUtensorMap map_x,
             const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_out0,
             const __grid_constant__ CUtensorMap map_out1, const Params p) {
-    constexpr int kTensors = kBackward ? 3 : 2;
-    constexpr int kStages = kBackward ? kStagesBwd : kStagesFwd;
+    static_assert(!(kGate && (kBackward || kProd || kTickets)), "the gate front-end exists for the plain forward only");
+    constexpr bool kThree = kBackward || kGate;      // tensors loaded per unit: 3, else 2
+    constexpr int kTensors = kThree ? 3 : 2;
+    constexpr int kStages = kThree ? kStagesBwd : kStagesFwd;
     using SM = Smem<kTensors, kStages>;
     constexpr int V = Cfg<T>::V;
     // Tile shape: kSp = 1: 64 rows x 256 bytes; 2: 128 x 128; 4: 256 x 64 (same 16 KiB).  A warp then
@@ -502,7 +534,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_alpha) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-            if (kBackward) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_h) : "memory");
+            if (kThree) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_h) : "memory");
             // Which tile a unit is.  Fixed order: CTA x takes tiles x, x+G, x+2G, ...  Tickets: the same
             // for the first kStages units, after that every refill takes the next tile from a global
             // counter, so an SM that the memory system serves faster takes more tiles and all CTAs
@@ -555,6 +587,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 tma_load_3d(base, &map_alpha, bar_full(st), c0, c1, c2);
                 tma_load_3d(base + kTileBytes, &map_x, bar_full(st), c0, c1, c2);
                 if (kBackward) tma_load_3d(base + 2 * kTileBytes, &map_h, bar_full(st), c0, c1 - 1, c2);
+                if (kGate) tma_load_3d(base + 2 * kTileBytes, &map_h, bar_full(st), c0, c1, c2);      // input gate
                 ++issued;
             };
             // One loop for both the initial fill (slots 0 .. kStages-1) and the steady state, in which
@@ -906,13 +939,22 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             if (!ctl.wait(bar_full(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
             if (warp == 0) FSS_TRACE_EV(i, kEvFull);
             Raw *a_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + lane_off);
-            const Raw *x_t = reinterpret_cast<const Raw *>(smem_raw + st * SM::kStageBytes + kTileBytes + lane_off);
+            Raw *x_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + kTileBytes + lane_off);
+            // gated forward: the alpha slot arrives holding r, the third slot i; this pass turns them
+            // into alpha and beta in place (rounded to the I/O type, as if they had come from memory)
+            const Raw *i_t = reinterpret_cast<const Raw *>(smem_raw + st * SM::kStageBytes + 2 * kTileBytes + lane_off);
+            float gsc[V];
+            if (kGate) {
+                const int64_t dch = (int64_t)u.cg * Dc + cl * V;
+#pragma unroll
+                for (int v = 0; v < V; ++v) gsc[v] = dch + v < p.D ? gate_scale(p.lambda[dch + v]) : 0.0f;
+            }
             // row 0 of the whole sequence: alpha_0 is not part of the recurrence
-            if (head) a_t[0] = Lane<T>::zero();
+            if (!kGate && head) a_t[0] = Lane<T>::zero();
             // rows past the end of the sequence arrive zero-filled; alpha = 1 (beta, grad = 0) makes
             // them the identity for both passes, so the state after the tile is the state after
             // the last real row
-            if (nvalid < kR) {
+            if (!kGate && nvalid < kR) {
                 for (int r = nvalid; r < kR; ++r) a_t[r * kRowStride] = Lane<T>::one();
             }
             float P[V], C[V];
@@ -929,6 +971,40 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 }
                 pair_fix<kPairSwap>(ra, odd_grp);
                 pair_fix<kPairSwap>(rx, odd_grp);
+                if (kGate) {
+                    Raw rg[kRh];
+#pragma unroll
+                    for (int r = 0; r < kRh; ++r) rg[r] = pair_slot<kRowStride>(i_t, base + r, dsw);
+                    pair_fix<kPairSwap>(rg, odd_grp);
+#pragma unroll
+                    for (int r = 0; r < kRh; ++r) {
+                        float rr[V], ii[V], xx[V], a[V], b[V];
+                        Lane<T>::unpack(ra[r], rr);
+                        Lane<T>::unpack(rg[r], ii);
+                        Lane<T>::unpack(rx[r], xx);
+                        const bool first_row = head && base + r == 0;       // alpha_0 is not part of the recurrence
+                        const bool past_end = base + r >= nvalid;           // identity rows after the sequence
+#pragma unroll
+                        for (int v = 0; v < V; ++v) {
+                            a[v] = Gate<T>::exp_neg(gsc[v] * Gate<T>::sigmoid(rr[v]));
+                            b[v] = Gate<T>::root(fmaf(-a[v], a[v], 1.0f)) * Gate<T>::sigmoid(ii[v]) * xx[v];
+                            if (first_row) a[v] = 0.0f;
+                            if (past_end) { a[v] = 1.0f; b[v] = 0.0f; }
+                        }
+                        ra[r] = Lane<T>::pack(a);
+                        rx[r] = Lane<T>::pack(b);
+                    }
+                    Raw wa[kRh], wx[kRh];
+#pragma unroll
+                    for (int r = 0; r < kRh; ++r) { wa[r] = ra[r]; wx[r] = rx[r]; }
+                    pair_fix<kPairSwap>(wa, odd_grp);
+                    pair_fix<kPairSwap>(wx, odd_grp);
+#pragma unroll
+                    for (int r = 0; r < kRh; ++r) {
+                        pair_slot<kRowStride>(a_t, base + r, dsw) = wa[r];
+                        pair_slot<kRowStride>(x_t, base + r, dsw) = wx[r];
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < kRh; ++j) {
                     const int r = kBackward ? kRh - 1 - j : j;
@@ -1186,14 +1262,14 @@ inline bool make_map(CUtensorMap *map, const fss_view *v, int64_t B, int64_t Tn,
 }
 
 // CTAs that fit the device at once (one per SM with these shared-memory sizes), per device.
-template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
+template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets, bool kGate> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
     static std::mutex mu;
     static int cached[64];
     static bool have[64];
     std::lock_guard<std::mutex> lock(mu);
     if (device < 0 || device >= 64) { *err = cudaErrorInvalidDevice; return 0; }
     if (!have[device]) {
-        auto kern = scan_kernel<T, kBackward, kProd, kSp, kTickets>;
+        auto kern = scan_kernel<T, kBackward, kProd, kSp, kTickets, kGate>;
         *err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (*err != cudaSuccess) return 0;
         int per_sm = 0, sms = 0;
@@ -1208,12 +1284,12 @@ template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets> inline
     return cached[device];
 }
 
-template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets>
+template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets, bool kGate = false>
 inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t Tn, int64_t D,
                   const fss_view *alpha, const fss_view *x, const fss_view *h, const fss_view *out0,
                   const fss_view *out1, Params p, std::string *err_text) {
-    constexpr int kTensors = kBackward ? 3 : 2;
-    constexpr int kStages = kBackward ? kStagesBwd : kStagesFwd;
+    constexpr int kTensors = (kBackward || kGate) ? 3 : 2;
+    constexpr int kStages = (kBackward || kGate) ? kStagesBwd : kStagesFwd;
     constexpr int smem_bytes = Smem<kTensors, kStages>::kBytes;
     constexpr int Dc = Cfg<T>::Dc / kSp;
 
@@ -1224,6 +1300,9 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     if (kBackward) {
         if (!make_map<T>(&m_h, h, B, Tn, D, kSp, err_text) || !make_map<T>(&m_o1, out1, B, Tn, D, kSp, err_text))
             return FSS_E_TENSORMAP;
+    } else if (kGate) {
+        if (!make_map<T>(&m_h, h, B, Tn, D, kSp, err_text)) return FSS_E_TENSORMAP;      // the input gate
+        m_o1 = m_o0;
     } else {
         m_h = m_alpha; m_o1 = m_o0;
     }
@@ -1231,7 +1310,7 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) { *err_text = cudaGetErrorString(e); return FSS_E_DEVICE; }
-    const int resident = resident_ctas<T, kBackward, kProd, kSp, kTickets>(device, smem_bytes, &e);
+    const int resident = resident_ctas<T, kBackward, kProd, kSp, kTickets, kGate>(device, smem_bytes, &e);
     if (e != cudaSuccess || resident < 1) { *err_text = cudaGetErrorString(e); return FSS_E_LAUNCH; }
 
     p.B = B; p.T = Tn; p.D = D;
@@ -1273,7 +1352,7 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     const bool use_pdl = pdl_env >= 0 ? pdl_env == 1 : p.ntiles <= kPdlMaxUnits * (int64_t)grid;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, scan_kernel<T, kBackward, kProd, kSp, kTickets>, m_alpha, m_x, m_h, m_o0, m_o1, p);
+    e = cudaLaunchKernelEx(&cfg, scan_kernel<T, kBackward, kProd, kSp, kTickets, kGate>, m_alpha, m_x, m_h, m_o0, m_o1, p);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { *err_text = std::string("look-back launch: ") + cudaGetErrorString(e); return FSS_E_LAUNCH; }
     return FSS_OK;
@@ -1312,6 +1391,27 @@ inline int forward(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t
     if (p.prod_out || p.block_prod)
         return launch<T, false, true>(ctx, ws, B, Tn, D, alpha, beta, nullptr, h, nullptr, p, err_text);
     return launch<T, false, false>(ctx, ws, B, Tn, D, alpha, beta, nullptr, h, nullptr, p, err_text);
+}
+
+// Forward scan whose alpha and beta are computed in the kernel from the recurrence gate r, the input
+// gate i, the input x and the per-channel parameter lambda (see Gate).
+template <typename T>
+inline int forward_gated(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t Tn, int64_t D,
+                         const fss_view *r, const fss_view *i, const fss_view *x, const float *lambda,
+                         const fss_view *h, const fss_forward_state *st, std::string *err_text) {
+    Params p{};
+    const bool cont = ctx->flags & FSS_FLAG_CONTINUATION;
+    if (st) {
+        p.state_in = cont ? st->h_in : nullptr;
+        p.state_out = st->h_last;
+    }
+    p.lambda = lambda;
+    const int dtype = sizeof(T) == 2 ? FSS_DTYPE_BF16 : FSS_DTYPE_F32;
+    switch (choose_split(dtype, B, Tn, D)) {
+    case 4: return launch_split<T, false, false, 4, false, true>(ctx, ws, B, Tn, D, r, x, i, h, nullptr, p, err_text);
+    case 2: return launch_split<T, false, false, 2, false, true>(ctx, ws, B, Tn, D, r, x, i, h, nullptr, p, err_text);
+    default: return launch_split<T, false, false, 1, false, true>(ctx, ws, B, Tn, D, r, x, i, h, nullptr, p, err_text);
+    }
 }
 
 template <typename T>

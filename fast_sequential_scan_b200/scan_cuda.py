@@ -27,7 +27,8 @@ from typing import Any, Optional, Tuple
 import torch
 from torch.autograd import Function
 
-from .sequential_scan_cuda import scan_backward, scan_backward_half, scan_forward, scan_forward_half
+from .sequential_scan_cuda import (gates_reference, scan_backward, scan_backward_half, scan_forward,
+                                   scan_forward_gated, scan_forward_half)
 
 BACKWARD_MODES = ("saved", "inplace", "recompute")
 _default_mode = "saved"
@@ -102,3 +103,38 @@ def scan(alpha: torch.Tensor, beta: torch.Tensor, *, backward_mode: Optional[str
 def scan_single(alpha: torch.Tensor, beta: torch.Tensor, *, backward_mode: Optional[str] = None) -> torch.Tensor:
     """fp32 variant of :func:`scan`."""
     return SequentialScanSingle.apply(alpha, beta, backward_mode)
+
+
+class GatedSequentialScan(Function):
+    """``h = scan(alpha, beta)`` with ``alpha = exp(-8 softplus(lam) sigmoid(r))`` and
+    ``beta = sqrt(1 - alpha^2) sigmoid(i) x`` (the RG-LRU of Hawk / Griffin, the use case the reference's
+    README.md:3 names; the reference has no such entry point).  The forward computes the gates inside
+    the scan kernel, so alpha and beta never reach memory; the backward materialises them once with
+    torch, runs the reverse scan kernel and chains through the gate formulas with autograd."""
+
+    @staticmethod
+    def forward(ctx: Any, r: torch.Tensor, i: torch.Tensor, x: torch.Tensor, lam: torch.Tensor) -> torch.Tensor:
+        h = scan_forward_gated(r, i, x, lam)
+        ctx.save_for_backward(r, i, x, lam, h)
+        return h
+
+    @staticmethod
+    def backward(ctx: Any, grad_output: torch.Tensor):
+        r, i, x, lam, h = ctx.saved_tensors
+        with torch.enable_grad():
+            leaves = [t.detach().requires_grad_() for t in (r, i, x, lam)]
+            alpha, beta = gates_reference(*leaves)
+        bwd = scan_backward_half if h.dtype == torch.bfloat16 else scan_backward
+        alpha_grad, beta_grad = bwd(alpha.detach(), h, grad_output.contiguous())
+        needed = [k for k, need in enumerate(ctx.needs_input_grad) if need]
+        grads = torch.autograd.grad((alpha, beta), [leaves[k] for k in needed], (alpha_grad, beta_grad))
+        out = [None] * 4
+        for k, gk in zip(needed, grads):
+            out[k] = gk
+        return tuple(out)
+
+
+def scan_gated(r: torch.Tensor, i: torch.Tensor, x: torch.Tensor, lam: torch.Tensor) -> torch.Tensor:
+    """Gated scan over ``[batch, seq, d_model]`` tensors ``r, i, x`` (bf16 or fp32) and the fp32
+    per-channel parameter ``lam`` of ``d_model`` values; see :class:`GatedSequentialScan`."""
+    return GatedSequentialScan.apply(r, i, x, lam)

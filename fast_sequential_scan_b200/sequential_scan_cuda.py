@@ -118,6 +118,63 @@ def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_
     _lib.check(rc, "fss_scan_forward_ex")
 
 
+def gates_reference(r, i, x, lam):
+    """alpha, beta of the gated recurrence with plain torch operations, in the dtype of ``r``:
+    ``alpha = exp(-8 softplus(lam) sigmoid(r))``, ``beta = sqrt(1 - alpha^2) sigmoid(i) x`` (evaluated in
+    fp32, rounded once).  Used where the fused kernel cannot run and by the backward of the gated scan."""
+    rf, jf, xf = r.float(), i.float(), x.float()
+    a = torch.exp(-8.0 * torch.nn.functional.softplus(lam.float()) * torch.sigmoid(rf))
+    b = torch.sqrt(1.0 - a * a) * torch.sigmoid(jf) * xf
+    return a.to(r.dtype), b.to(r.dtype)
+
+
+def forward_gated_into(r, i, x, lam, h, *, continuation=False, h_in=None, h_last=None) -> None:
+    """h <- scan(alpha, beta) with alpha, beta computed from the gates inside the kernel
+    (``fss_scan_forward_gated``).  Raises :class:`FssError` with ``E_LAYOUT`` for layouts the
+    single-pass kernel cannot take."""
+    dtype = r.dtype
+    if dtype not in _DTYPES:
+        raise RuntimeError(f"r: unsupported dtype {dtype} (bf16 or fp32)")
+    _check_tensor("r", r, None, dtype)
+    _check_tensor("i", i, r, dtype)
+    _check_tensor("x", x, r, dtype)
+    _check_tensor("h", h, r, dtype)
+    B, T, D = r.shape
+    if lam.dtype != torch.float32 or lam.shape != (D,) or lam.device != r.device or not lam.is_contiguous():
+        raise RuntimeError("lam: expected a contiguous fp32 vector of d_model values on the inputs' device")
+    if r.numel() == 0:
+        return
+    rr, ii, xx = _rowwise(r), _rowwise(i), _rowwise(x)
+    if _rowwise(h) is not h:
+        raise RuntimeError("h: output must have unit channel stride and non-overlapping rows")
+    L = _lib.lib()
+    with torch.cuda.device(r.device):
+        ws = workspace.get(r.device, L.fss_workspace_bytes(B, T, D, _DTYPES[dtype]))
+        ctx = _ctx(r.device, ws, None, _lib.FLAG_CONTINUATION if continuation else 0)
+        state = None
+        if h_in is not None or h_last is not None:
+            state = _lib.ForwardState(_vec(h_in, B, D, "h_in"), _vec(h_last, B, D, "h_last"), None, None, None)
+        views = [_view(t) for t in (rr, ii, xx, h)]
+        rc = L.fss_scan_forward_gated(ctypes.byref(ctx), _DTYPES[dtype], B, T, D, ctypes.byref(views[0]),
+                                      ctypes.byref(views[1]), ctypes.byref(views[2]), lam.data_ptr(),
+                                      ctypes.byref(views[3]), ctypes.byref(state) if state is not None else None)
+    _lib.check(rc, "fss_scan_forward_gated")
+
+
+def scan_forward_gated(r, i, x, lam) -> torch.Tensor:
+    """Gated forward scan; falls back to torch gates + the plain scan when the layout is not
+    eligible for the fused kernel."""
+    h = torch.empty(r.shape, dtype=r.dtype, device=r.device)
+    try:
+        forward_gated_into(r, i, x, lam, h)
+    except _lib.FssError as e:
+        if e.code != _lib.E_LAYOUT:
+            raise
+        a, b = gates_reference(r, i, x, lam)
+        forward_into(a, b, h)
+    return h
+
+
 def backward_into(alpha, h, grad_out, grad_alpha, grad_beta, *, algo=None, continuation=False,
                   u_in=None, h_prev=None, u_out=None, block_prod=None, block_state=None) -> None:
     dtype = alpha.dtype

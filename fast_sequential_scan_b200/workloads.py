@@ -75,3 +75,14 @@ def make_inputs(w: Workload, device="cpu", seed: int = 0, shape=None
     g = n()
     dt = w.torch_dtype
     return a.to(dt), b.to(dt), g.to(dt)
+
+
+def make_gate_inputs(w: Workload, device="cpu", seed: int = 0, shape=None):
+    """(r, i, x, lam) for the gated forward of a workload's shape: the raw quantities the "hawk"
+    gates of :func:`make_inputs` are computed from (lam ~ U(-4.3, -0.5) per channel, r, i, x ~ N(0, 1))."""
+    shape = tuple(shape) if shape is not None else (w.batch, w.seq, w.d_model)
+    dev = torch.device(device)
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    lam = -4.3 + 3.8 * torch.rand((shape[-1],), generator=gen, device=dev)
+    r, i, x = (torch.randn(shape, generator=gen, device=dev).to(w.torch_dtype) for _ in range(3))
+    return r, i, x, lam

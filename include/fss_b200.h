@@ -166,6 +166,21 @@ int fss_scan_backward_ex(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t 
                          const fss_view *grad_alpha, const fss_view *grad_beta,
                          const fss_backward_state *state);
 
+/* ---- forward scan with the gates of a real-gated linear recurrent unit computed in the kernel ---
+ * No counterpart in the reference, whose callers materialise alpha and beta first (the gates are
+ * the use case its README.md:3 names).  Per element, with lambda[D] fp32 per channel:
+ *     alpha = exp(-8 * softplus(lambda) * sigmoid(r)),  beta = sqrt(1 - alpha^2) * sigmoid(i) * x,
+ * both rounded to `dtype` exactly as if they had been stored and re-read, then h = scan(alpha, beta)
+ * with the usual first-row rule (h_0 = beta_0 unless FSS_FLAG_CONTINUATION).  Reads r, i, x and
+ * writes h: 4 tensor passes instead of the 8 of a gate kernel followed by the scan.
+ * bf16 evaluates the gates with the hardware approximations (a and b are rounded to 8 bits
+ * anyway), fp32 with the accurate functions.  Single-pass kernel only: layouts it cannot take,
+ * and FSS_ALGO_CHUNKED, return FSS_E_LAYOUT; the caller then computes alpha and beta itself.
+ * state may carry h_in / h_last; prod, block_prod and block_state must be NULL (FSS_E_ARGS). */
+int fss_scan_forward_gated(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                           const fss_view *r, const fss_view *i, const fss_view *x,
+                           const float *lambda, const fss_view *h, const fss_forward_state *state);
+
 /* ---- sequence-parallel pieces (no counterpart in the reference, which never splits T) ---- */
 /* Rows per block of the block_prod outputs for this problem and algorithm (> 0). */
 int64_t fss_block_rows(int dtype, int64_t B, int64_t T, int64_t D, int algo);

@@ -179,6 +179,21 @@ def bf16_storage_values(alpha, beta, grad=None, fused: bool = True):
     return to_t(h), to_t(da), to_t(db)
 
 
+def gated_alpha_beta(r, i, x, lam):
+    """alpha, beta of the gated recurrence, evaluated in float64 with numpy and rounded ONCE to the
+    I/O dtype of ``r`` (torch tensors in, torch tensors out):
+        alpha = exp(-8 softplus(lam) sigmoid(r)),   beta = sqrt(1 - alpha^2) sigmoid(i) x
+    The formula is the Hawk / Griffin RG-LRU the reference's README.md:3 names as its use case; the
+    reference itself has no code for it (its callers pass alpha and beta)."""
+    import torch
+    rf, jf, xf = (t.detach().cpu().to(torch.float64).numpy() for t in (r, i, x))
+    lf = lam.detach().cpu().to(torch.float64).numpy()
+    sig = lambda z: 1.0 / (1.0 + np.exp(-z))
+    a = np.exp(-8.0 * np.log1p(np.exp(lf)) * sig(rf))
+    b = np.sqrt(1.0 - a * a) * sig(jf) * xf
+    return torch.from_numpy(a).to(r.dtype), torch.from_numpy(b).to(r.dtype)
+
+
 def torch_loop_scan(alpha, beta):
     """The recurrence as differentiable torch ops (step-by-step, like common.py:46-59)."""
     import torch

@@ -312,6 +312,61 @@ def test_inplace_grad_beta_through_the_c_abi():
     assert torch.equal(got[0], da_ref) and torch.equal(got[1], db_ref)
 
 
+@pytest.mark.parametrize("fp32", [False, True])
+@pytest.mark.parametrize("shape", [(2, 1024, 768), (4, 1000, 2048), (16, 512, 2560), (1, 4096, 128), (3, 70, 24), (2, 33, 7)])
+def test_gated_forward_matches_the_oracle(shape, fp32):
+    """Gates computed in the kernel against the float64 gate formulas rounded once to the I/O type and
+    scanned by the oracle.  The unfused route (torch gates + plain scan) is held to the same bound."""
+    pkg, native, _ = _mods()
+    from fast_sequential_scan_b200.workloads import Workload, make_gate_inputs
+    w = Workload("t", *shape, "hawk", "f32" if fp32 else "bf16")
+    r, i, x, lam = make_gate_inputs(w, "cpu", seed=5)
+    a_ref, b_ref = oracle.gated_alpha_beta(r, i, x, lam)
+    h_ref, _, _ = oracle.reference_values(a_ref, b_ref)
+    rc, ic, xc, lc = r.cuda(), i.cuda(), x.cuda(), lam.cuda()
+    h = pkg.scan_gated(rc, ic, xc, lc)
+    pkg.check_status()
+    # fp32: the gate formulas lose a few ulp in fp32 and the recurrence amplifies that by up to
+    # 1/(1-alpha); 1e-4 covers it (the plain fp32 scan, whose inputs are exact, keeps 1e-5)
+    tol = 1e-4 if fp32 else BF16_TOL
+    assert_parity(h.float().cpu(), h_ref, tol, "gated h")
+    a_t, b_t = native.gates_reference(rc, ic, xc, lc)
+    h_unfused = (pkg.scan_cu_single if fp32 else pkg.scan_cu)(a_t, b_t)
+    assert_parity(h_unfused.float().cpu(), h_ref, tol, "unfused h")
+    if not fp32 and native.tma_eligible(rc, ic, xc):
+        # bf16: both routes round alpha, beta to 8 bits; they agree wherever the approximations
+        # do not flip a rounding, so the two results stay far inside the tolerance of each other
+        assert_parity(h.float().cpu(), h_unfused.float().cpu(), tol, "gated vs unfused")
+
+
+def test_gated_scan_gradients_and_state():
+    """Backward of the gated scan (torch gates + reverse-scan kernel + autograd through the gate
+    formulas) against autograd of the all-torch formulation; boundary state through the C ABI."""
+    pkg, native, _ = _mods()
+    from fast_sequential_scan_b200.workloads import Workload, make_gate_inputs
+    w = Workload("t", 2, 512, 256, "hawk", "f32")
+    r, i, x, lam = (t.cuda() for t in make_gate_inputs(w, "cpu", seed=9))
+    g = torch.randn(r.shape, generator=torch.Generator().manual_seed(1)).cuda()
+    leaves = [t.clone().requires_grad_() for t in (r, i, x, lam)]
+    pkg.scan_gated(*leaves).backward(g)
+    ref_leaves = [t.clone().requires_grad_() for t in (r, i, x, lam)]
+    a, b = native.gates_reference(*ref_leaves)
+    pkg.scan_cu_single(a, b).backward(g)
+    for got, ref, name in zip(leaves, ref_leaves, "r i x lam".split()):
+        assert_parity(got.grad.cpu(), ref.grad.cpu(), 1e-4, f"d{name}")
+    # two halves with h_last -> h_in equal one pass
+    h_full = torch.empty_like(r)
+    native.forward_gated_into(r, i, x, lam, h_full)
+    half = r.shape[1] // 2
+    h_a, h_b = torch.empty_like(r[:, :half]), torch.empty_like(r[:, half:])
+    last = torch.empty(r.shape[0], r.shape[2], device="cuda")
+    native.forward_gated_into(r[:, :half].contiguous(), i[:, :half].contiguous(), x[:, :half].contiguous(), lam, h_a, h_last=last)
+    native.forward_gated_into(r[:, half:].contiguous(), i[:, half:].contiguous(), x[:, half:].contiguous(), lam, h_b,
+                              continuation=True, h_in=last)
+    pkg.check_status()
+    assert_parity(torch.cat([h_a, h_b], 1).cpu(), h_full.cpu(), 1e-5, "continued gated scan")
+
+
 @pytest.mark.parametrize("shape", [(4, 4096, 2048), (2, 8192, 1024), (1, 16384, 512)])
 def test_lookback_descriptors_survive_reuse_with_different_data(shape):
     """Consecutive launches on one workspace with DIFFERENT inputs of one shape: a stale tile

@@ -94,3 +94,22 @@ def test_restatement_matches_compiled_reference_loop(shape):
     assert np.array_equal(job.get(job.DBETA).view(np.uint32), db.view(np.uint32))
     assert np.array_equal(job.get(job.DALPHA).view(np.uint32), da.view(np.uint32))
     job.close()
+
+
+def test_gate_formulas_of_the_oracle_against_torch():
+    """float64 numpy gates == torch float64 gates, and the package's fp32 torch gates round to the
+    same I/O values except where fp32 evaluation flips a rounding (rare, one unit in the last place)."""
+    import torch
+    from oracle import oracle
+    gen = torch.Generator().manual_seed(2)
+    r, i, x = (torch.randn(3, 50, 16, generator=gen) for _ in range(3))
+    lam = -4.3 + 3.8 * torch.rand(16, generator=gen)
+    a, b = oracle.gated_alpha_beta(r, i, x, lam)
+    r64, i64, x64, l64 = (t.double() for t in (r, i, x, lam))
+    a64 = torch.exp(-8.0 * torch.nn.functional.softplus(l64) * torch.sigmoid(r64))
+    b64 = torch.sqrt(1 - a64 * a64) * torch.sigmoid(i64) * x64
+    assert torch.equal(a, a64.float()) and torch.equal(b, b64.float())
+    assert float(a.min()) > 0.0 and float(a.max()) < 1.0
+    rb, ib, xb = (t.to(torch.bfloat16) for t in (r, i, x))
+    ab, bb = oracle.gated_alpha_beta(rb, ib, xb, lam)
+    assert ab.dtype == torch.bfloat16 and bb.dtype == torch.bfloat16

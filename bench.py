@@ -43,7 +43,7 @@ def parse_args():
     p.add_argument("--workload", default="c2")
     p.add_argument("--algo", default="auto", choices=["auto", "chunked", "lookback"])
     p.add_argument("--shape", default=None, help="override batch,seq,d_model of the workload (same gates and dtype)")
-    p.add_argument("--mode", default="shard", choices=["shard", "seqpar"])
+    p.add_argument("--mode", default="shard", choices=["shard", "seqpar", "gated"])
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-graphs", action="store_true", help="launch every step from Python instead of replaying CUDA graphs")
     p.add_argument("--no-cpu", action="store_true")
@@ -250,6 +250,62 @@ def run_seqpar(args, world, rank, dev):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------ gated forward mode
+def run_gated(args, dev):
+    """Forward scan with the gates computed in the kernel (fss_scan_forward_gated) on the workload's
+    shape, beside the unfused route (torch gate formulas, then the plain forward scan).  One GPU."""
+    import torch
+    import fast_sequential_scan_b200 as pkg
+    from fast_sequential_scan_b200 import sequential_scan_cuda as native
+    from fast_sequential_scan_b200.workloads import CONFIGS, make_gate_inputs
+    w = CONFIGS[args.workload if args.workload != "c2" else "c4_bf16"]
+    esize = 2 if w.dtype == "bf16" else 4
+    sets = min(16, max(3, -(-3 * L2_BYTES // (4 * w.elems * esize))))
+    bufs = []
+    for s in range(sets):
+        r, i, x, lam = make_gate_inputs(w, dev, seed=s)
+        bufs.append((r, i, x, lam, torch.empty_like(r)))
+
+    def fused(s):
+        r, i, x, lam, h = bufs[s % sets]
+        native.forward_gated_into(r, i, x, lam, h)
+
+    def unfused(s):
+        r, i, x, lam, h = bufs[s % sets]
+        a, b = native.gates_reference(r, i, x, lam)
+        native.forward_into(a, b, h)
+
+    def timed(fn):
+        for s in range(max(3, args.warmup)):
+            fn(s)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(args.steps):
+            fn(s)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    ms, ms_unfused = timed(fused), timed(unfused)
+    pkg.check_status()
+    peak, kind = peaks()
+    gbs = w.elems * 4 * esize / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "gated scan fwd elems/s", "value": w.elems / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+        "config": {"workload": f"{w.name}: gated forward scan, B{w.batch} T{w.seq} D{w.d_model}, r,i,x~N(0,1), "
+                               "lambda~U(-4.3,-0.5)",
+                   "l2": f"rotating {sets} disjoint buffer sets", "launch": "one C-ABI launch per step from Python"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                     "traffic": None, "peak_kind": f"of {kind}",
+                     "algorithmic_bytes": w.elems * 4 * esize, "per": "read r, i, x; write h"},
+        "unfused": {"ms_per_step": ms_unfused, "what": "torch gate formulas (fp32 math, rounded once) + plain forward scan",
+                    "speedup": ms_unfused / ms},
+        "gpu_launches": args.steps}), flush=True)
+
+
 # ------------------------------------------------------------------ GPU arm
 def main():
     args = parse_args()
@@ -272,6 +328,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     if args.mode == "seqpar":
         run_seqpar(args, world, rank, dev)
+        return
+    if args.mode == "gated":
+        if rank == 0:
+            run_gated(args, dev)
         return
 
     w = CONFIGS[args.workload]

@@ -432,8 +432,8 @@ template <bool kTickets, int kStages> struct UnitCursor {
 // RG-LRU gates evaluated in the kernel (gated forward):  a = exp(c * sigmoid(r)) with
 // c = -8 * softplus(lambda) per channel, b = sqrt(1 - a^2) * sigmoid(i) * x.  bf16 I/O rounds a and
 // b to 8 mantissa bits anyway, so it takes the 1-MUFU forms (tanh.approx, ex2.approx, sqrt.approx:
-// 4 special-function operations per element keep the kernel under the HBM time); fp32 I/O uses
-// the accurate library functions.
+// 4 special-function operations per element); fp32 I/O uses the fp32 ex2 / rcp / sqrt approximations (5 per element).  Measured on B200 the bf16 kernel is bound by the
+// special-function unit at about half of the HBM rate.
 template <typename T> struct Gate;
 template <> struct Gate<bf16> {
     static __device__ __forceinline__ float sigmoid(float z) {
@@ -441,7 +441,12 @@ template <> struct Gate<bf16> {
         asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * z));
         return fmaf(0.5f, t, 0.5f);
     }
-    static __device__ __forceinline__ float exp_neg(float z) { return __expf(z); }
+    static __device__ __forceinline__ float prescale(float c) { return c * 1.4426950408889634f; }   // exp(z) = 2^(z log2 e)
+    static __device__ __forceinline__ float exp_scaled(float z) {
+        float r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(z));
+        return r;
+    }
     static __device__ __forceinline__ float root(float z) {
         float r;
         asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(z));
@@ -449,9 +454,25 @@ template <> struct Gate<bf16> {
     }
 };
 template <> struct Gate<float> {
-    static __device__ __forceinline__ float sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
-    static __device__ __forceinline__ float exp_neg(float z) { return expf(z); }
-    static __device__ __forceinline__ float root(float z) { return sqrtf(z); }
+    // ex2 / rcp / sqrt of the special-function unit on fp32 operands: each within about 2^-22
+    // relative, far inside what the recurrence amplifies anyway (tanh.approx, good to 2^-11, is not)
+    static __device__ __forceinline__ float sigmoid(float z) {
+        float e, r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * z));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+        return r;
+    }
+    static __device__ __forceinline__ float prescale(float c) { return c * 1.4426950408889634f; }
+    static __device__ __forceinline__ float exp_scaled(float z) {
+        float r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(z));
+        return r;
+    }
+    static __device__ __forceinline__ float root(float z) {
+        float r;
+        asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(z));
+        return r;
+    }
 };
 __device__ __forceinline__ float gate_scale(float lambda) {      // -8 * softplus(lambda)
     return -8.0f * (lambda > 20.0f ? lambda : log1pf(expf(lambda)));
@@ -932,6 +953,13 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             // rows of this group that exist in the sequence (fewer than kR only in the last row block)
             const int64_t left = p.T - row0 - (int64_t)grp * kR;
             const int nvalid = left >= kR ? kR : (left > 0 ? (int)left : 0);
+            // gated forward: this lane's channel scales, fetched while the tile is still on its way
+            float gsc[V];
+            if (kGate) {
+                const int64_t dch = (int64_t)u.cg * Dc + cl * V;
+#pragma unroll
+                for (int v = 0; v < V; ++v) gsc[v] = dch + v < p.D ? Gate<T>::prescale(gate_scale(p.lambda[dch + v])) : 0.0f;
+            }
             if (i >= kGens) {      // the summary buffers of this generation are free once pass 2 of unit i-kGens is done
                 const int o = i - kGens;
                 if (!ctl.wait(bar_done((int)(o % kStages)), (uint32_t)((o / kStages) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
@@ -943,12 +971,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             // gated forward: the alpha slot arrives holding r, the third slot i; this pass turns them
             // into alpha and beta in place (rounded to the I/O type, as if they had come from memory)
             const Raw *i_t = reinterpret_cast<const Raw *>(smem_raw + st * SM::kStageBytes + 2 * kTileBytes + lane_off);
-            float gsc[V];
-            if (kGate) {
-                const int64_t dch = (int64_t)u.cg * Dc + cl * V;
-#pragma unroll
-                for (int v = 0; v < V; ++v) gsc[v] = dch + v < p.D ? gate_scale(p.lambda[dch + v]) : 0.0f;
-            }
             // row 0 of the whole sequence: alpha_0 is not part of the recurrence
             if (!kGate && head) a_t[0] = Lane<T>::zero();
             // rows past the end of the sequence arrive zero-filled; alpha = 1 (beta, grad = 0) makes
@@ -972,6 +994,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 pair_fix<kPairSwap>(ra, odd_grp);
                 pair_fix<kPairSwap>(rx, odd_grp);
                 if (kGate) {
+                    const bool edge_rows = __any_sync(0xffffffffu, head || nvalid < kR);
                     Raw rg[kRh];
 #pragma unroll
                     for (int r = 0; r < kRh; ++r) rg[r] = pair_slot<kRowStride>(i_t, base + r, dsw);
@@ -982,14 +1005,19 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                         Lane<T>::unpack(ra[r], rr);
                         Lane<T>::unpack(rg[r], ii);
                         Lane<T>::unpack(rx[r], xx);
-                        const bool first_row = head && base + r == 0;       // alpha_0 is not part of the recurrence
-                        const bool past_end = base + r >= nvalid;           // identity rows after the sequence
 #pragma unroll
                         for (int v = 0; v < V; ++v) {
-                            a[v] = Gate<T>::exp_neg(gsc[v] * Gate<T>::sigmoid(rr[v]));
+                            a[v] = Gate<T>::exp_scaled(gsc[v] * Gate<T>::sigmoid(rr[v]));
                             b[v] = Gate<T>::root(fmaf(-a[v], a[v], 1.0f)) * Gate<T>::sigmoid(ii[v]) * xx[v];
-                            if (first_row) a[v] = 0.0f;
-                            if (past_end) { a[v] = 1.0f; b[v] = 0.0f; }
+                        }
+                        if (edge_rows) {       // warp-uniform and rare: first row of the sequence, rows after its end
+                            const bool first_row = head && base + r == 0;   // alpha_0 is not part of the recurrence
+                            const bool past_end = base + r >= nvalid;       // identity rows after the sequence
+#pragma unroll
+                            for (int v = 0; v < V; ++v) {
+                                if (first_row) a[v] = 0.0f;
+                                if (past_end) { a[v] = 1.0f; b[v] = 0.0f; }
+                            }
                         }
                         ra[r] = Lane<T>::pack(a);
                         rx[r] = Lane<T>::pack(b);

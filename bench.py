@@ -27,7 +27,7 @@ if str(ROOT) not in sys.path:
 
 # DRAM bytes (read + write) per launch of the backward kernel from the committed ncu capture
 # (profiles/lookback_c2_ncu_full.md); only known for the workload that was captured
-NCU_TRAFFIC = {("c2", "lookback"): 128.9e6}
+NCU_TRAFFIC = {("c2", "lookback"): 127.9e6}
 
 METRIC = "scan fwd+bwd elems/s"
 UNIT = "elems/s"
@@ -450,7 +450,7 @@ def main():
     ach_bwd = bwd_bytes / (ms_bwd * 1e-3) / 1e9
     ach_fwd = fwd_bytes / (ms_fwd * 1e-3) / 1e9
     ach_step = (bwd_bytes + fwd_bytes) / (ms_step * 1e-3) / 1e9
-    kernel_bwd = "fss::lookback::scan_backward_kernel" if took_lookback else "fss::chunked::chunk_scan_backward (+summary, compose)"
+    kernel_bwd = "fss::lookback::scan_kernel<bf16, backward> (single pass)" if took_lookback else "fss::chunked::chunk_scan_backward (+summary, compose)"
     roofline = {"bound": "hbm", "kernel": kernel_bwd, "achieved": ach_bwd, "peak": peak, "unit": "GB/s",
                 "frac": ach_bwd / peak,
                 "traffic": NCU_TRAFFIC.get((args.workload if not args.shape else "", "lookback" if took_lookback else "chunked")),

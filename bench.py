@@ -196,7 +196,7 @@ def run_reference_arm(args):
 
 # ------------------------------------------------------------------ sequence-parallel mode
 def run_seqpar(args, world, rank, dev):
-    """BASELINE config 5 style: every rank holds 65,536 rows of a (65,536 * N)-row sequence; a step
+    """Sequence-parallel configuration (c5): every rank holds 65,536 rows of a (65,536 * N)-row sequence; a step
     is the sequence-parallel forward (local scan, all-gather of carries, fix-up) plus backward."""
     import torch
     import torch.distributed as dist

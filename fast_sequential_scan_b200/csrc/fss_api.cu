@@ -331,12 +331,24 @@ static seqpar::Geometry fixup_geometry(int64_t B, int64_t T, int64_t D, int64_t 
     return g;
 }
 
+// multiprocessors of the current device (cached per device; 148 if the query fails)
+static int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        cached[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+    }
+    return cached[dev];
+}
+
 template <typename T, int V>
 static int fixup_forward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *alpha,
                                 const fss_view *beta, const fss_view *h, const float *carry_in, const float *bp,
                                 const float *bs, int64_t R) {
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
-    seqpar::fixup_forward<T, V><<<(unsigned)(g.vblocks * g.NB * B), seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
+    seqpar::fixup_forward<T, V><<<seqpar::fixup_grid(g, sm_count()), seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
         g, make_view<const T>(alpha), make_view<const T>(beta), make_view<T>(h), carry_in, bp, bs);
     return launch_check("seqpar forward fix-up launch");
 }
@@ -346,7 +358,7 @@ static int fixup_backward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn,
                                  const fss_view *h, const fss_view *grad, const fss_view *da, const fss_view *db,
                                  const float *u_in, const float *h_prev, const float *bp, const float *bs, int64_t R) {
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
-    seqpar::fixup_backward<T, V><<<(unsigned)(g.vblocks * g.NB * B), seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
+    seqpar::fixup_backward<T, V><<<seqpar::fixup_grid(g, sm_count()), seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
         g, make_view<const T>(alpha), make_view<const T>(h), make_view<const T>(grad), make_view<T>(da),
         make_view<T>(db), u_in, h_prev, bp, bs, (ctx->flags & FSS_FLAG_CONTINUATION) != 0);
     return launch_check("seqpar backward fix-up launch");

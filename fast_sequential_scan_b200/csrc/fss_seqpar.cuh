@@ -44,11 +44,32 @@ struct Geometry {
     int64_t nvec, vblocks;   // channel vectors per row, CTAs along the channel axis (32 vectors each)
 };
 
-__device__ __forceinline__ void decode_block(const Geometry &g, int64_t &vb, int64_t &j, int64_t &b) {
-    int64_t id = blockIdx.x;
+__device__ __forceinline__ void decode_block(const Geometry &g, int64_t id, int64_t &vb, int64_t &j, int64_t &b) {
     vb = id % g.vblocks; id /= g.vblocks;
     j = id % g.NB;
     b = id / g.NB;
+}
+// V consecutive floats, as 16-byte loads when the address allows it (one sector per 8 floats
+// instead of one per float: the liveness check below is all loads)
+template <int V> __device__ __forceinline__ void load_floats(const float *__restrict__ p, float (&out)[V]) {
+    if (V % 4 == 0 && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+#pragma unroll
+        for (int i = 0; i < V / 4; ++i) {
+            const float4 q = reinterpret_cast<const float4 *>(p)[i];
+            out[4 * i] = q.x; out[4 * i + 1] = q.y; out[4 * i + 2] = q.z; out[4 * i + 3] = q.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) out[i] = p[i];
+    }
+}
+// The grid is at most a few CTAs per SM and every CTA walks the (block, channel group, batch row)
+// candidates with a grid stride: almost all candidates are dead (their check costs one round of
+// loads), and launching a CTA per candidate cost more than checking them.
+inline unsigned fixup_grid(const Geometry &g, int sms) {
+    const int64_t total = g.vblocks * g.NB * g.B;
+    const int64_t cap = (int64_t)sms * (2048 / kFixThreads);
+    return (unsigned)(total < cap ? total : cap);
 }
 
 // Re-scan of the blocks that the entering state still reaches (forward).  A block is live when
@@ -60,26 +81,37 @@ __global__ void __launch_bounds__(kFixThreads)
 fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, const float *__restrict__ carry_in,
               const float *__restrict__ block_prod, const float *__restrict__ block_state) {
     __shared__ float sP[kWarps][32][V], sC[kWarps][32][V];
-    int64_t vb, j, b;
-    decode_block(g, vb, j, b);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t total = g.vblocks * g.NB * g.B;
+    for (int64_t id = blockIdx.x; id < total; id += gridDim.x) {
+    int64_t vb, j, b;
+    decode_block(g, id, vb, j, b);
     const int64_t v = vb * 32 + lane;
     const bool has = v < g.nvec;
     const int64_t d0 = v * V;
-    float st[V];
+    float st[V];         // what the entering state adds to this block: (product before it) * carry
     bool live = false;
 #pragma unroll
     for (int i = 0; i < V; ++i) st[i] = 0.0f;
+    const int64_t o = (b * g.NB + j - 1) * g.D + d0;
     if (has) {
+        float pr[V];
+        load_floats<V>(carry_in + b * g.D + d0, st);
+        if (j > 0) {
+            load_floats<V>(block_prod + o, pr);
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-            const int64_t o = (b * g.NB + j - 1) * g.D + d0 + i;
-            const float w = (j == 0 ? 1.0f : block_prod[o]) * carry_in[b * g.D + d0 + i];
-            st[i] = (j == 0 ? 0.0f : block_state[o]) + w;
-            live |= (w != 0.0f);
+            for (int i = 0; i < V; ++i) st[i] *= pr[i];
         }
+#pragma unroll
+        for (int i = 0; i < V; ++i) live |= (st[i] != 0.0f);
     }
-    if (!__syncthreads_or(live)) return;   // the zero-state result of this block is already exact
+    if (!__syncthreads_or(live)) continue;   // the zero-state result of this block is already exact
+    if (has && j > 0) {
+        float bs[V];
+        load_floats<V>(block_state + o, bs);
+#pragma unroll
+        for (int i = 0; i < V; ++i) st[i] += bs[i];
+    }
     const int64_t r0 = j * g.R, r1 = min(g.T, r0 + g.R);
     const int64_t per = (g.R + kWarps - 1) / kWarps;
     const int64_t w0 = min(r1, r0 + warp * per), w1 = min(r1, w0 + per);
@@ -99,19 +131,22 @@ fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, co
 #pragma unroll
     for (int i = 0; i < V; ++i) { sP[warp][lane][i] = P[i]; sC[warp][lane][i] = C[i]; }
     __syncthreads();
-    if (!has) return;
-    for (int w = 0; w < warp; ++w) {
+    if (has) {
+        for (int w = 0; w < warp; ++w) {
 #pragma unroll
-        for (int i = 0; i < V; ++i) st[i] = fmaf(sP[w][lane][i], st[i], sC[w][lane][i]);
-    }
+            for (int i = 0; i < V; ++i) st[i] = fmaf(sP[w][lane][i], st[i], sC[w][lane][i]);
+        }
 #pragma unroll 4
-    for (int64_t t = w0; t < w1; ++t) {
-        float a[V], x[V];
-        Frag<T, V>::load(alpha.row(b, t) + d0, a);
-        Frag<T, V>::load(beta.row(b, t) + d0, x);
+        for (int64_t t = w0; t < w1; ++t) {
+            float a[V], x[V];
+            Frag<T, V>::load(alpha.row(b, t) + d0, a);
+            Frag<T, V>::load(beta.row(b, t) + d0, x);
 #pragma unroll
-        for (int i = 0; i < V; ++i) st[i] = fmaf(a[i], st[i], x[i]);
-        Frag<T, V>::store(h.row(b, t) + d0, st);
+            for (int i = 0; i < V; ++i) st[i] = fmaf(a[i], st[i], x[i]);
+            Frag<T, V>::store(h.row(b, t) + d0, st);
+        }
+    }
+    __syncthreads();      // the summaries are read above; the next candidate may overwrite them
     }
 }
 
@@ -123,9 +158,11 @@ fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> g
                View<T> dbeta, const float *__restrict__ u_in, const float *__restrict__ h_prev,
                const float *__restrict__ block_prod, const float *__restrict__ block_state, bool continuation) {
     __shared__ float sP[kWarps][32][V], sC[kWarps][32][V];
-    int64_t vb, j, b;
-    decode_block(g, vb, j, b);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t total = g.vblocks * g.NB * g.B;
+    for (int64_t id = blockIdx.x; id < total; id += gridDim.x) {
+    int64_t vb, j, b;
+    decode_block(g, id, vb, j, b);
     const int64_t v = vb * 32 + lane;
     const bool has = v < g.nvec;
     const int64_t d0 = v * V;
@@ -133,17 +170,26 @@ fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> g
     bool live = false;
 #pragma unroll
     for (int i = 0; i < V; ++i) u[i] = 0.0f;
+    const bool lastb = j == g.NB - 1;
+    const int64_t o = (b * g.NB + j + 1) * g.D + d0;
     if (has) {
-        const bool lastb = j == g.NB - 1;
+        float pr[V];
+        load_floats<V>(u_in + b * g.D + d0, u);
+        if (!lastb) {
+            load_floats<V>(block_prod + o, pr);
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-            const int64_t o = (b * g.NB + j + 1) * g.D + d0 + i;
-            const float w = (lastb ? 1.0f : block_prod[o]) * u_in[b * g.D + d0 + i];
-            u[i] = (lastb ? 0.0f : block_state[o]) + w;
-            live |= (w != 0.0f);
+            for (int i = 0; i < V; ++i) u[i] *= pr[i];
         }
+#pragma unroll
+        for (int i = 0; i < V; ++i) live |= (u[i] != 0.0f);
     }
-    if (!__syncthreads_or(live)) return;
+    if (!__syncthreads_or(live)) continue;
+    if (has && !lastb) {
+        float bs[V];
+        load_floats<V>(block_state + o, bs);
+#pragma unroll
+        for (int i = 0; i < V; ++i) u[i] += bs[i];
+    }
     const int64_t r0 = j * g.R, r1 = min(g.T, r0 + g.R);
     const int64_t per = (g.R + kWarps - 1) / kWarps;
     // warp 0 takes the last rows of the block, warp 1 the rows before them, ...
@@ -169,7 +215,7 @@ fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> g
 #pragma unroll
     for (int i = 0; i < V; ++i) { sP[warp][lane][i] = P[i]; sC[warp][lane][i] = C[i]; }
     __syncthreads();
-    if (!has) return;
+    if (has) {
     for (int w = 0; w < warp; ++w) {
 #pragma unroll
         for (int i = 0; i < V; ++i) u[i] = fmaf(sP[w][lane][i], u[i], sC[w][lane][i]);
@@ -194,6 +240,9 @@ fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> g
         }
         Frag<T, V>::store(dbeta.row(b, t) + d0, dh);
         Frag<T, V>::store(dalpha.row(b, t) + d0, da);
+    }
+    }
+    __syncthreads();      // the summaries are read above; the next candidate may overwrite them
     }
 }
 

@@ -467,22 +467,53 @@ def main():
         out_db = torch.empty(ha.shape, dtype=dt).pin_memory()
         out_h = torch.empty(ha.shape, dtype=dt).pin_memory()
 
+        # Three streams, two device buffer sets: the host-to-device copies of step i+1 and the
+        # device-to-host copies of step i-1 run while step i computes (PCIe is full duplex).  Every
+        # copy and every launch of a step is inside the timed region; the timing stream waits for
+        # the last device-to-host copy of every step.
+        s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        dsets = [tuple(torch.empty(ha.shape, dtype=dt, device=dev) for _ in range(3)) for _ in range(2)]
+        computed = [None, None]          # event: the compute that last read buffer set k is done
+        scan_fn = pkg.scan_cu if w.dtype == "bf16" else pkg.scan_cu_single
+
         def e2e_step(i):
-            a = ha.to(dev, non_blocking=True).requires_grad_(True)
-            b = hb.to(dev, non_blocking=True).requires_grad_(True)
-            g = hg.to(dev, non_blocking=True)
-            h = (pkg.scan_cu if w.dtype == "bf16" else pkg.scan_cu_single)(a, b)
-            h.backward(g)
-            out_h.copy_(h.detach(), non_blocking=True)
-            out_da.copy_(a.grad, non_blocking=True)
-            out_db.copy_(b.grad, non_blocking=True)
+            k = i % 2
+            da_, db_, dg_ = dsets[k]
+            with torch.cuda.stream(s_in):
+                if computed[k] is not None:
+                    s_in.wait_event(computed[k])
+                da_.copy_(ha, non_blocking=True)
+                db_.copy_(hb, non_blocking=True)
+                dg_.copy_(hg, non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(arrived)
+                a = da_.detach().requires_grad_(True)
+                b = db_.detach().requires_grad_(True)
+                h = scan_fn(a, b)
+                h.backward(dg_)
+                done = torch.cuda.Event()
+                done.record(s_cmp)
+                computed[k] = done
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for t in (h, a.grad, b.grad):
+                    t.record_stream(s_out)
+                out_h.copy_(h.detach(), non_blocking=True)
+                out_da.copy_(a.grad, non_blocking=True)
+                out_db.copy_(b.grad, non_blocking=True)
+                left = torch.cuda.Event()
+                left.record(s_out)
+            torch.cuda.current_stream().wait_event(left)
 
         e_steps = max(3, min(args.steps, 20))
         ms_e2e = timed(e2e_step, e_steps, 3, graphs=False)
         e2e = {"value": total_elems / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e, "steps": e_steps,
                "h2d_bytes_per_step": 3 * tensor_bytes, "d2h_bytes_per_step": 3 * tensor_bytes,
                "api": "scan_cu(alpha, beta); h.backward(grad) on tensors copied from pinned host memory; "
-                      "h, dalpha, dbeta copied back"}
+                      "h, dalpha, dbeta copied back; copies of neighbouring steps overlap the compute "
+                      "(3 streams, 2 device buffer sets)"}
         pkg.check_status()
 
     cpu = None

@@ -1371,13 +1371,15 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    // Programmatic dependent launch lets the next launch on the stream set itself up while this one
-    // drains.  Measured on B200 it shortens back-to-back launches of short problems (up to 14 % at
-    // one or two tiles per CTA) but slows long backward launches by a few per cent, so it is used
-    // only when a CTA has at most kPdlMaxUnits tiles.  FSS_B200_PDL=0 / 1 forces it off / on.
+    // Programmatic dependent launch: a launch with this attribute may start its set-up while the
+    // launch before it on the stream drains (it still waits for that launch's completion before it
+    // touches global memory).  Measured on B200: forward launches always gain (1-2 % on c2 / c3);
+    // backward launches gain only when they are short (up to 14 % at one or two tiles per CTA) and
+    // lose about 3 % when they are long, so those keep the ordinary launch.  FSS_B200_PDL=0 / 1
+    // forces it off / on for both directions.
     constexpr int64_t kPdlMaxUnits = 8;
     static const int pdl_env = [] { const char *e = getenv("FSS_B200_PDL"); return !e ? -1 : (e[0] == '1' ? 1 : 0); }();
-    const bool use_pdl = pdl_env >= 0 ? pdl_env == 1 : p.ntiles <= kPdlMaxUnits * (int64_t)grid;
+    const bool use_pdl = pdl_env >= 0 ? pdl_env == 1 : (!kBackward || p.ntiles <= kPdlMaxUnits * (int64_t)grid);
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
     e = cudaLaunchKernelEx(&cfg, scan_kernel<T, kBackward, kProd, kSp, kTickets, kGate>, m_alpha, m_x, m_h, m_o0, m_o1, p);

@@ -643,7 +643,9 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                     for (uint32_t it = 0; it < p.max_spins && !mbar_try_wait(bar, par); ++it) {}
                 }
             }
-            tma_wait_all();
+            // the stores only have to be done READING shared memory before the CTA may leave; the
+            // writes themselves are complete when the grid is
+            tma_wait_read_all();
         }
     } else if (warp == kSummaryWarp) {
         // ============================================================ summary

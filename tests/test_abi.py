@@ -86,3 +86,35 @@ def test_python_surface_mirrors_the_reference_names():
         assert hasattr(scan_cuda, name)
     for name in ("scan_forward", "scan_backward", "scan_forward_half", "scan_backward_half"):
         assert callable(getattr(native, name))
+
+
+def test_backward_mode_switch_validates_its_argument():
+    from fast_sequential_scan_b200 import scan_cuda
+    assert scan_cuda.BACKWARD_MODES == ("saved", "inplace", "recompute")
+    previous = scan_cuda.set_backward_mode("recompute")
+    try:
+        assert previous == "saved" and scan_cuda._resolve(None) == "recompute"
+        assert scan_cuda._resolve("inplace") == "inplace"
+        with pytest.raises(ValueError):
+            scan_cuda.set_backward_mode("in-place")
+        with pytest.raises(ValueError):
+            scan_cuda._resolve("keep")
+    finally:
+        scan_cuda.set_backward_mode(previous)
+
+
+def test_reference_arm_of_the_bench_prints_the_contract_line():
+    """`bench.py --impl reference` runs on host cores only; one JSON line with the agreed keys."""
+    import json
+    import subprocess
+    import sys
+    root = Path(__file__).resolve().parent.parent
+    out = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference", "--workload", "c1",
+                          "--steps", "2", "--warmup", "1"], capture_output=True, text=True, timeout=300, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["higher_is_better"] is True and line["value"] > 0
+    for key in ("metric", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "config", "cpu_baseline", "e2e"):
+        assert key in line
+    assert line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0

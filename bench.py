@@ -5,14 +5,25 @@
     python bench.py --impl reference ...      # the reference's CPU loop on the host cores
 
 One JSON line on stdout (rank 0).  A *step* is one forward scan plus one backward scan of the
-workload; ``value`` is elements (batch*seq*d_model, summed over ranks) per second with all
-tensors resident in HBM, ``e2e`` the same through ``scan_cu`` + ``.backward`` from pinned host
-buffers with the copies inside the timed region.  With N > 1 every rank owns a full-size channel
-shard of a d_model*N problem (weak scaling, no collective on the data path).
+workload.  ``value`` is elements (batch*seq*d_model, summed over ranks) per second with all tensors
+resident in HBM: K steps are replayed from CUDA graphs of the library's own C-ABI launches, the
+K-step replay is repeated R times inside one barrier/synchronise bracket, every repeat is timed
+with CUDA events, reduced with max over ranks, and the median over the repeats is reported (with
+the min and max beside it).  ``e2e`` is the same metric through ``scan_cu`` + ``.backward`` from
+pinned host buffers with the copies inside the timed region.
+
+With N > 1 every rank owns a full-size channel shard of a d_model*N problem (weak scaling, no
+collective on the data path) for ``value``; the line also carries two records of their own:
+``strong`` -- the stated split of the workload (d_model/N channels per GPU, strided views of the
+full tensors) -- and ``seqpar`` -- the long-context configuration, 65,536 rows of one sequence per
+GPU, local scan + NCCL all-gather of the carries + fix-up -- each with an untimed parity check
+against the CPU checker.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
+import importlib.util
 import json
 import os
 import statistics
@@ -25,20 +36,18 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-# DRAM bytes (read + write) per launch of the backward kernel from the committed ncu capture
-# (profiles/lookback_c2_ncu_full.md); only known for the workload that was captured
-NCU_TRAFFIC = {("c2", "lookback"): 127.9e6}
-
 METRIC = "scan fwd+bwd elems/s"
 UNIT = "elems/s"
 L2_BYTES = 126 * 1024 * 1024
+SIDE_WORKLOADS = ["c1", "c3_512", "c3_1000", "c3_3000", "c3_4096", "c3_8192", "c4_bf16", "c4_f32", "c5_rank"]
 
 
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=200)
-    p.add_argument("--warmup", type=int, default=20)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--repeats", type=int, default=50, help="timed repeats of the K-step replay (median reported)")
     p.add_argument("--impl", default="b200", choices=["b200", "reference"])
     p.add_argument("--workload", default="c2")
     p.add_argument("--algo", default="auto", choices=["auto", "chunked", "lookback"])
@@ -47,7 +56,7 @@ def parse_args():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-graphs", action="store_true", help="launch every step from Python instead of replaying CUDA graphs")
     p.add_argument("--no-cpu", action="store_true")
-    p.add_argument("--no-soak", action="store_true", help="skip the extra steps that only feed the clock sampler")
+    p.add_argument("--no-side", action="store_true", help="skip the api / workloads / gated / strong / seqpar records")
     p.add_argument("--cpu-seconds", type=float, default=12.0)
     return p.parse_args()
 
@@ -62,6 +71,46 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def load_workloads():
+    """The workload table, loaded by file path: importing the package would load the CUDA library,
+    which the reference arm must not do."""
+    spec = importlib.util.spec_from_file_location("fss_b200_workloads",
+                                                  ROOT / "fast_sequential_scan_b200" / "workloads.py")
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def kernel_revision() -> str:
+    """Hash of the kernel sources; a profiler capture is only attributed to the sources it was taken from."""
+    h = hashlib.sha256()
+    for f in sorted((ROOT / "fast_sequential_scan_b200" / "csrc").glob("*.cu*")):
+        h.update(f.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def captured_traffic(workload: str, kernel: str):
+    """DRAM bytes (read + write) per launch from the committed profiler summary of this workload, if
+    that summary was taken from the kernel sources that are being timed now; else None."""
+    path = ROOT / "profiles" / "dram_traffic.txt"
+    if not path.is_file():
+        return None
+    rev = kernel_revision()
+    for line in path.read_text().splitlines():
+        parts = line.split()
+        if len(parts) >= 4 and not line.startswith("#") and parts[0] == rev and parts[1] == workload and parts[2] == kernel:
+            try:
+                return float(parts[3])
+            except ValueError:
+                return None
+    return None
+
+
+def stats(ms_list):
+    return {"median": statistics.median(ms_list), "min": min(ms_list), "max": max(ms_list)}
+
+
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
@@ -73,14 +122,14 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50", "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
 
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
@@ -105,13 +154,10 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU legs
-def cpu_reference_leg(w, seconds: float, threads: int):
+def cpu_reference_leg(w, make_inputs, seconds: float, threads: int):
     """The reference's own C++ loop (oracle/_ref) on the host cores, else the C restatement.
-    Returns (elems_per_s, kind, cores, sample_text)."""
-    import numpy as np
-    import torch
+    Returns (elems_per_s, kind, cores, sample_text, seconds_per_step)."""
     from oracle import oracle
-    from fast_sequential_scan_b200.workloads import make_inputs
 
     a, b, g = (x.float().numpy() for x in make_inputs(w, "cpu", 0))
     job = None
@@ -145,19 +191,80 @@ def cpu_reference_leg(w, seconds: float, threads: int):
     return w.elems * reps / t_total, kind, threads, sample, t_total / reps
 
 
+def cpu_torch_loop_leg(w, make_inputs, repeats: int = 3):
+    """The reference's sequential PyTorch scan (sequential_scan/common.py:46-59: one slice update per
+    row, gradients by autograd through the loop) as restated in the CPU checker, fp32, on the host
+    cores: one warm-up (the first backward is several times slower), then the median of ``repeats``."""
+    import torch
+    from oracle import oracle
+    a, b, g = (x.float() for x in make_inputs(w, "cpu", 0))
+    times = []
+    for it in range(repeats + 1):
+        ar, br = a.clone().requires_grad_(True), b.clone().requires_grad_(True)
+        t0 = time.perf_counter()
+        h = oracle.torch_loop_scan(ar, br)
+        h.backward(g)
+        dt = time.perf_counter() - t0
+        if it:
+            times.append(dt)
+    sec = statistics.median(times)
+    return {"value": w.elems / sec, "unit": UNIT, "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
+            "kind": "port", "seconds_per_step": sec,
+            "sample": f"median of {repeats} x full {w.name} workload (B{w.batch} T{w.seq} D{w.d_model}) fwd + autograd bwd, fp32, "
+                      "sequential PyTorch loop, after one warm-up"}
+
+
+def reference_gpu_record(w, make_inputs, steps: int):
+    """The reference's own CUDA kernels (compiled from its headers into oracle/_ref/libfss_refgpu.so)
+    timed on this GPU with CUDA events, when a GPU and that library are present."""
+    try:
+        import torch
+        from oracle import oracle
+        if not torch.cuda.is_available():
+            return {"unavailable": "no CUDA device visible to the reference arm"}
+        if not oracle.RefGpu.available():
+            return {"unavailable": "oracle/_ref/libfss_refgpu.so was not built (needs the reference checkout)"}
+        if w.d_model not in oracle.RefGpu.WIDTHS:
+            return {"unavailable": f"the reference's launchers have no case for d_model {w.d_model}"}
+        ref = oracle.RefGpu()
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(dev)
+        a, b, g = make_inputs(w, dev, 0)
+        h, da = torch.empty_like(a), torch.empty_like(a)
+        db = torch.empty_like(a)
+
+        def step():
+            ref.forward(a, b, h)
+            # fp32 keeps a separate grad_beta, bf16 writes it over h (csrc/sequential_scan_kernel.cu:68,197)
+            ref.backward(a, h, g, da, db if w.dtype == "f32" else h)
+
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = max(3, min(steps, 10))
+        e0.record()
+        for _ in range(n):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n
+        return {"value": w.elems / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "steps": n,
+                "what": "the reference's sequential_scan_forward/backward kernels (one CTA per batch row), "
+                        "compiled for sm_100a with its own flags, same workload, tensors resident on the device"}
+    except Exception as e:      # informational record: never fail the arm over it
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
+
 def run_reference_arm(args):
-    from fast_sequential_scan_b200.workloads import CONFIGS
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    w = CONFIGS[args.workload]
+    wl = load_workloads()
+    w = wl.CONFIGS[args.workload]
     cores = os.cpu_count() or 1
-    # each step = one bounded fwd+bwd sample; warm-up steps are run and discarded
-    per_step_seconds = 0.0
     from oracle import oracle
-    import numpy as np
-    from fast_sequential_scan_b200.workloads import make_inputs
-    a, b, g = (x.float().numpy() for x in make_inputs(w, "cpu", 0))
+    a, b, g = (x.float().numpy() for x in wl.make_inputs(w, "cpu", 0))
     job = oracle.RefLib().job(w.batch, w.seq, w.d_model) if oracle.RefLib.available() else None
     threads = max(1, min(cores, w.batch)) if job is not None else 1
     if job is not None:
@@ -186,124 +293,322 @@ def run_reference_arm(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{w.name}: B{w.batch} T{w.seq} D{w.d_model} {w.gates} gates, fp32 on CPU",
                    "note": "CPU arm runs the single-GPU workload once regardless of --gpus"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "host_cpus": cores,
                          "sample": f"{steps} x full {w.name} workload fwd+bwd ({how})"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        # informational, not part of `value`: the reference's CUDA kernels on this box's GPU
+        "reference_gpu_kernels": reference_gpu_record(w, wl.make_inputs, steps),
     }
     print(json.dumps(line), flush=True)
 
 
-# ------------------------------------------------------------------ sequence-parallel mode
-def run_seqpar(args, world, rank, dev):
-    """Sequence-parallel configuration (c5): every rank holds 65,536 rows of a (65,536 * N)-row sequence; a step
-    is the sequence-parallel forward (local scan, all-gather of carries, fix-up) plus backward."""
-    import torch
-    import torch.distributed as dist
-    import fast_sequential_scan_b200 as pkg
-    from fast_sequential_scan_b200 import distributed as fd
-    from fast_sequential_scan_b200.workloads import CONFIGS, make_inputs
-    w = CONFIGS["c5_rank"]
-    a, b, g = make_inputs(w, dev, seed=rank)
-    ops = fd.NativeOps()
-    group = None        # default group; with one rank no process group exists and the gather is the identity
+# ------------------------------------------------------------------ device timing helpers
+class Harness:
+    """Timing of a step function on one stream: warm-up, optional CUDA-graph capture of K steps,
+    R timed repeats of the K-step replay in one barrier/synchronise bracket."""
 
-    def step():
-        h, saved = fd.seqpar_forward(a, b, group, ops)
-        fd.seqpar_backward(a, h, g, saved, group, ops)
+    def __init__(self, torch, dist, dev, world, use_graphs):
+        self.torch, self.dist, self.dev, self.world, self.use_graphs = torch, dist, dev, world, use_graphs
+        self.side = torch.cuda.Stream(dev)
 
-    for _ in range(max(3, args.warmup)):
-        step()
-    if world > 1:
-        dist.barrier()
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def _capture(self, fn, first, count):
+        g = self.torch.cuda.CUDAGraph()
+        with self.torch.cuda.graph(g, stream=self.side):
+            for i in range(count):
+                fn(first + i)
+        return g
+
+    def timed(self, fn, steps, warmup, repeats, sets, graphs=None):
+        """Per-repeat device time per step (ms), max over ranks; list of `repeats` values."""
+        torch = self.torch
+        graphs = self.use_graphs if graphs is None else graphs
+        with torch.cuda.stream(self.side):
+            for i in range(max(warmup, 3)):
+                fn(i)
+        self.side.synchronize()
+        if graphs:
+            full, rem = divmod(steps, sets)
+            g_full = self._capture(fn, 0, sets) if full else None
+            g_rem = self._capture(fn, 0, rem) if rem else None
+
+            def replay():
+                for _ in range(full):
+                    g_full.replay()
+                if rem:
+                    g_rem.replay()
+        else:
+            def replay():
+                for i in range(steps):
+                    fn(i)
+        with torch.cuda.stream(self.side):
+            replay()
+        self.barrier()
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(repeats)]
+        with torch.cuda.stream(self.side):
+            for e0, e1 in pairs:
+                e0.record()
+                replay()
+                e1.record()
+        self.barrier()
+        ms = [e0.elapsed_time(e1) / steps for e0, e1 in pairs]
+        if self.world > 1:
+            t = torch.tensor(ms, device=self.dev, dtype=torch.float64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            ms = [float(x) for x in t.tolist()]
+        return ms
+
+
+def make_sets(torch, w, make_inputs, dev, seed0, per_set_bytes=None):
+    """Enough disjoint buffer sets that no step finds its inputs in L2 (3x the L2 in rotation)."""
+    esize = 2 if w.dtype == "bf16" else 4
+    per = per_set_bytes or 6 * w.elems * esize
+    sets = min(16, max(3, -(-3 * L2_BYTES // per)))
+    bufs = []
+    for s in range(sets):
+        a, b, g = make_inputs(w, dev, seed=seed0 + s)
+        bufs.append(dict(a=a, b=b, g=g, h=torch.empty_like(a), da=torch.empty_like(a), db=torch.empty_like(a)))
+    return bufs
+
+
+def step_fns(native, bufs, algo):
+    n = len(bufs)
+
+    def fwd(s):
+        x = bufs[s % n]
+        native.forward_into(x["a"], x["b"], x["h"], algo=algo)
+
+    def bwd(s):
+        x = bufs[s % n]
+        native.backward_into(x["a"], x["h"], x["g"], x["da"], x["db"], algo=algo)
+
+    return fwd, bwd
+
+
+def side_workload(hs, native, make_inputs, w, dev, algo, peak, steps=10, repeats=5):
+    """Short run of one more benchmark configuration: step time and fraction of the HBM peak."""
+    torch = hs.torch
+    bufs = make_sets(torch, w, make_inputs, dev, 7000)
+    fwd, bwd = step_fns(native, bufs, algo)
+    ms = stats(hs.timed(lambda i: (fwd(i), bwd(i)), steps, 3, repeats, len(bufs)))
+    gbs = w.elems * w.bytes_per_elem() / (ms["median"] * 1e-3) / 1e9
+    del bufs
+    torch.cuda.empty_cache()
+    return {"workload": w.name, "shape": [w.batch, w.seq, w.d_model], "dtype": w.dtype, "ms_per_step": ms["median"],
+            "ms_per_step_min": ms["min"], "ms_per_step_max": ms["max"], "elems_per_s": w.elems / (ms["median"] * 1e-3),
+            "achieved_gbs": gbs, "frac": gbs / peak, "steps": steps, "repeats": repeats}
+
+
+def api_record(torch, pkg, w, bufs, ms_graph_step, steps=200):
+    """The drop-in call sequence with tensors resident on the device and no graphs:
+    ``h = scan_cu(alpha, beta); h.backward(grad)`` -- what the reference's own benchmark times
+    (benchmark.py:92-106).  Device time per step from CUDA events, host time per step from the wall
+    clock of the enqueue loop (shorter than the launch queue, so it is pure host cost)."""
+    fn = pkg.scan_cu if w.dtype == "bf16" else pkg.scan_cu_single
+    leaves = [(x["a"].detach().requires_grad_(True), x["b"].detach().requires_grad_(True), x["g"]) for x in bufs]
+    n = len(leaves)
+
+    def step(i):
+        a, b, g = leaves[i % n]
+        a.grad = b.grad = None               # no accumulation kernels: only the two scan launches per step
+        fn(a, b).backward(g)
+
+    for i in range(20):
+        step(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
     e0.record()
-    for _ in range(args.steps):
-        step()
+    for i in range(steps):
+        step(i)
     e1.record()
-    if world > 1:
-        dist.barrier()
+    host = (time.perf_counter() - t0) / steps
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    t = torch.tensor([ms], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    pkg.check_status()
-    peak, kind = peaks()
-    total = w.elems * world
-    gbs = w.elems * 16 / (ms * 1e-3) / 1e9
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "value": total / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"c5: sequence-parallel fwd+bwd scan, B1 T{w.seq * world} D{w.d_model}, "
-                                   f"{w.seq} rows per GPU, a~U(0.9,0.9999)",
-                       "parallelism": f"sequence split x{world}: local scan, all-gather of (prod, carry), fix-up",
-                       "l2": "per-rank working set 1.6 GB >> L2"},
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
-                         "traffic": None, "peak_kind": f"of {kind}", "per": "GPU, fwd+bwd 16 B/elem, fix-up traffic not counted"},
-            "gpu_launches": None}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    dev_ms = e0.elapsed_time(e1) / steps
+    return {"call": "h = scan_cu(alpha, beta); h.backward(grad)  (eager autograd API, tensors on the device, no CUDA graphs)",
+            "us_per_step": dev_ms * 1e3, "host_us_per_step": host * 1e6, "steps": steps,
+            "graph_replay_us_per_step": ms_graph_step * 1e3, "vs_graph_replay": dev_ms / ms_graph_step,
+            "elems_per_s": w.elems / (dev_ms * 1e-3)}
 
 
-# ------------------------------------------------------------------ gated forward mode
-def run_gated(args, dev):
-    """Forward scan with the gates computed in the kernel (fss_scan_forward_gated) on the workload's
-    shape, beside the unfused route (torch gate formulas, then the plain forward scan).  One GPU."""
-    import torch
-    import fast_sequential_scan_b200 as pkg
-    from fast_sequential_scan_b200 import sequential_scan_cuda as native
-    from fast_sequential_scan_b200.workloads import CONFIGS, make_gate_inputs
-    w = CONFIGS[args.workload if args.workload != "c2" else "c4_bf16"]
-    esize = 2 if w.dtype == "bf16" else 4
+def gated_record(hs, native, wl, dev, peak, steps=10, repeats=5):
+    """Forward scan with the gates computed in the kernel (fss_scan_forward_gated), c4 shape, bf16."""
+    torch = hs.torch
+    w = wl.CONFIGS["c4_bf16"]
+    esize = 2
     sets = min(16, max(3, -(-3 * L2_BYTES // (4 * w.elems * esize))))
     bufs = []
     for s in range(sets):
-        r, i, x, lam = make_gate_inputs(w, dev, seed=s)
+        r, i, x, lam = wl.make_gate_inputs(w, dev, seed=s)
         bufs.append((r, i, x, lam, torch.empty_like(r)))
 
     def fused(s):
         r, i, x, lam, h = bufs[s % sets]
         native.forward_gated_into(r, i, x, lam, h)
 
-    def unfused(s):
-        r, i, x, lam, h = bufs[s % sets]
-        a, b = native.gates_reference(r, i, x, lam)
-        native.forward_into(a, b, h)
+    ms = stats(hs.timed(fused, steps, 3, repeats, sets))
+    gbs = w.elems * 4 * esize / (ms["median"] * 1e-3) / 1e9
+    del bufs
+    torch.cuda.empty_cache()
+    return {"workload": "c4_bf16 gated forward (r, i, x, lambda -> h)", "ms_per_launch": ms["median"],
+            "elems_per_s": w.elems / (ms["median"] * 1e-3), "achieved_gbs": gbs, "frac": gbs / peak,
+            "algorithmic_bytes": w.elems * 4 * esize, "per": "read r, i, x; write h"}
 
-    def timed(fn):
-        for s in range(max(3, args.warmup)):
-            fn(s)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+# ------------------------------------------------------------------ multi-GPU records
+def strong_record(hs, native, fd, wl, w, dev, rank, world, algo, peak, steps, repeats):
+    """The workload as ONE problem whose channels are split over the ranks (d_model / N per GPU):
+    every rank scans strided channel views of the full tensors.  Parity: this rank's shard against
+    the CPU checker (channels are independent, so the shard's oracle is exact)."""
+    torch = hs.torch
+    from oracle import oracle
+    esize = 2 if w.dtype == "bf16" else 4
+    shard_bytes = 6 * w.elems * esize // world
+    sets = min(16, max(3, -(-3 * L2_BYTES // shard_bytes)))
+    bufs = []
+    for s in range(sets):
+        a, b, g = wl.make_inputs(w, dev, seed=500 + s)            # the same full problem on every rank
+        full = dict(a=a, b=b, g=g, h=torch.empty_like(a), da=torch.empty_like(a), db=torch.empty_like(a))
+        bufs.append({k: fd.shard_channels(v, rank, world) for k, v in full.items()})
+    fwd, bwd = step_fns(native, bufs, algo)
+    ms = stats(hs.timed(lambda i: (fwd(i), bwd(i)), steps, 3, repeats, sets))
+    x = bufs[0]
+    fwd(0); bwd(0)
+    torch.cuda.synchronize()
+    tol = 1e-2 if w.dtype == "bf16" else 1e-5
+    sub = slice(0, min(32, x["a"].shape[-1]))
+    cut = lambda t: t[..., sub].contiguous()
+    h_ref, _, _ = oracle.reference_values(cut(x["a"]), cut(x["b"]), None)
+    da_ref, db_ref = oracle.scan_backward_f32(cut(x["a"]).float().cpu().numpy(), cut(x["h"]).float().cpu().numpy(),
+                                              cut(x["g"]).float().cpu().numpy())
+    ratios = [oracle.mixed_error_ratio(cut(x["h"]), h_ref, tol),
+              oracle.mixed_error_ratio(cut(x["da"]), torch.from_numpy(da_ref), tol),
+              oracle.mixed_error_ratio(cut(x["db"]), torch.from_numpy(db_ref), tol)]
+    ok = torch.tensor([1.0 if max(ratios) <= 1.0 else 0.0, max(ratios)], device=dev)
+    hs.dist.all_reduce(ok[:1], op=hs.dist.ReduceOp.MIN)
+    hs.dist.all_reduce(ok[1:], op=hs.dist.ReduceOp.MAX)
+    gbs = (w.elems // world) * w.bytes_per_elem() / (ms["median"] * 1e-3) / 1e9
+    return {"workload": f"{w.name}: ONE B{w.batch} T{w.seq} D{w.d_model} problem, d_model/{world} = {w.d_model // world} "
+                        "channels per GPU (strided views, no collective)",
+            "scaling": "strong", "ms_per_step": ms["median"], "ms_per_step_min": ms["min"], "ms_per_step_max": ms["max"],
+            "elems_per_s": w.elems / (ms["median"] * 1e-3), "per_gpu_achieved_gbs": gbs, "per_gpu_frac": gbs / peak,
+            "l2": f"rotating {sets} buffer sets ({sets * shard_bytes / 1e6:.0f} MB touched per GPU)",
+            "parity_ok": bool(ok[0].item() == 1.0), "parity_max_ratio": float(ok[1].item()), "parity_tol": tol,
+            "parity": "h, dalpha, dbeta of every rank's shard (first 32 channels, all rows) against the CPU checker"}
+
+
+def seqpar_record(hs, native, fd, wl, dev, rank, world, peak, steps, warmup):
+    """Long-context configuration: every rank holds 65,536 rows of one (65,536*N)-row sequence.
+    A step is the sequence-parallel forward (local scan, all-gather of the carries, fix-up) plus the
+    mirrored backward.  Also times each rank's undivided scan of the same rows, splits the step into
+    phases with CUDA events, and checks parity against the CPU checker on a channel subset."""
+    torch, dist = hs.torch, hs.dist
+    from oracle import oracle
+    w = wl.CONFIGS["c5_rank"]
+    a, b, g = wl.make_inputs(w, dev, seed=rank)
+    ops = fd.NativeOps()
+    B, T, D = a.shape
+
+    def step():
+        h, saved = fd.seqpar_forward(a, b, None, ops)
+        return h, fd.seqpar_backward(a, h, g, saved, None, ops)
+
+    for _ in range(max(3, warmup)):
+        step()
+    hs.barrier()
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for e0, e1 in pairs:
         e0.record()
-        for s in range(args.steps):
-            fn(s)
+        step()
         e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / args.steps
+    hs.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) for e0, e1 in pairs], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = stats([float(x) for x in t.tolist()])
 
-    ms, ms_unfused = timed(fused), timed(unfused)
-    pkg.check_status()
-    peak, kind = peaks()
-    gbs = w.elems * 4 * esize / (ms * 1e-3) / 1e9
-    print(json.dumps({
-        "metric": "gated scan fwd elems/s", "value": w.elems / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
-        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-        "config": {"workload": f"{w.name}: gated forward scan, B{w.batch} T{w.seq} D{w.d_model}, r,i,x~N(0,1), "
-                               "lambda~U(-4.3,-0.5)",
-                   "l2": f"rotating {sets} disjoint buffer sets", "launch": "one C-ABI launch per step from Python"},
-        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
-                     "traffic": None, "peak_kind": f"of {kind}",
-                     "algorithmic_bytes": w.elems * 4 * esize, "per": "read r, i, x; write h"},
-        "unfused": {"ms_per_step": ms_unfused, "what": "torch gate formulas (fp32 math, rounded once) + plain forward scan",
-                    "speedup": ms_unfused / ms},
-        "gpu_launches": args.steps}), flush=True)
+    # phases (CUDA events on the compute stream, mean over a few steps, max over ranks)
+    names = []
+    acc = {}
+    for it in range(6):
+        marks = []
+        mark = lambda name: marks.append((name, _event(torch)))
+        mark("start")
+        h, saved = fd.seqpar_forward(a, b, None, ops, mark=mark)
+        fd.seqpar_backward(a, h, g, saved, None, ops, mark=mark)
+        torch.cuda.synchronize()
+        if it:
+            for (_, e0), (n1, e1) in zip(marks[:-1], marks[1:]):
+                acc[n1] = acc.get(n1, 0.0) + e0.elapsed_time(e1) / 5
+                if n1 not in names:
+                    names.append(n1)
+    all_names = ["fwd_local", "fwd_gather", "fwd_fixup", "bwd_local", "bwd_gather", "bwd_fixup"]
+    pt = torch.tensor([acc.get(n, 0.0) for n in all_names], device=dev, dtype=torch.float64)
+    dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+    phases = {n: float(v) for n, v in zip(all_names, pt.tolist())}
+
+    # one GPU's undivided scan of the same rows (no products, no exchange)
+    h1, da1, db1 = torch.empty_like(a), torch.empty_like(a), torch.empty_like(a)
+
+    def plain(i):
+        native.forward_into(a, b, h1)
+        native.backward_into(a, h1, g, da1, db1)
+
+    ms_plain = stats(hs.timed(plain, 5, 3, 5, 1, graphs=False))
+
+    # parity (untimed): a channel subset of the WHOLE sequence, gathered from all ranks, through the
+    # CPU checker; every rank checks all of its own rows
+    h, (da, db) = step()
+    torch.cuda.synchronize()
+    idx = torch.tensor([0, 1, 7, 8, 127, 128, 1023, 2047, 2048, 3000, 4094, 4095], device=dev)
+    sub = lambda x: x.index_select(2, idx).contiguous()
+    parts = {}
+    for name, x in (("a", a), ("b", b), ("g", g), ("h", h)):
+        mine = sub(x)
+        out = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(out, mine)
+        parts[name] = torch.cat(out, dim=1).cpu()
+    h_ref, _, _ = oracle.reference_values(parts["a"], parts["b"], None)
+    da_ref, db_ref = oracle.scan_backward_f32(parts["a"].float().numpy(), parts["h"].float().numpy(),
+                                              parts["g"].float().numpy())
+    rows = slice(rank * T, (rank + 1) * T)
+    ratios = [oracle.mixed_error_ratio(sub(h), h_ref[:, rows], 1e-2),
+              oracle.mixed_error_ratio(sub(da), torch.from_numpy(da_ref)[:, rows], 1e-2),
+              oracle.mixed_error_ratio(sub(db), torch.from_numpy(db_ref)[:, rows], 1e-2)]
+    ok = torch.tensor([1.0 if max(ratios) <= 1.0 else 0.0, max(ratios)], device=dev)
+    dist.all_reduce(ok[:1], op=dist.ReduceOp.MIN)
+    dist.all_reduce(ok[1:], op=dist.ReduceOp.MAX)
+    native_status_ok = True
+    try:
+        import fast_sequential_scan_b200 as pkg
+        pkg.check_status()
+    except RuntimeError:
+        native_status_ok = False
+    total = w.elems * world
+    gbs = w.elems * 16 / (ms["median"] * 1e-3) / 1e9
+    one_gpu_rate = w.elems / (ms_plain["median"] * 1e-3)
+    return {"workload": f"c5: ONE sequence, B1 T{T * world} D{D} bf16, {T} rows per GPU, a~U(0.9,0.9999)",
+            "parallelism": f"sequence split x{world}: local scan, NCCL all-gather of (product, carry), fix-up; mirrored backward",
+            "ms_per_step": ms["median"], "ms_per_step_min": ms["min"], "ms_per_step_max": ms["max"], "steps": steps,
+            "elems_per_s": total / (ms["median"] * 1e-3), "per_gpu_achieved_gbs": gbs, "per_gpu_frac": gbs / peak,
+            "phases_ms": phases,
+            "one_gpu_undivided": {"ms_per_step": ms_plain["median"], "elems_per_s": one_gpu_rate,
+                                  "what": "plain fwd+bwd scan of one rank's rows on one GPU (max over ranks)"},
+            "vs_one_gpu_undivided": (total / (ms["median"] * 1e-3)) / one_gpu_rate,
+            "parity_ok": bool(ok[0].item() == 1.0) and native_status_ok, "parity_max_ratio": float(ok[1].item()),
+            "parity_tol": 1e-2,
+            "parity": f"h, dalpha, dbeta on {len(idx)} channels, all rows of every rank, against the CPU checker's scan of the "
+                      "whole gathered sequence (gradients formed from the stored h)"}
+
+
+def _event(torch):
+    e = torch.cuda.Event(enable_timing=True)
+    e.record()
+    return e
 
 
 # ------------------------------------------------------------------ GPU arm
@@ -316,8 +621,8 @@ def main():
     import torch
     import torch.distributed as dist
     import fast_sequential_scan_b200 as pkg
-    from fast_sequential_scan_b200 import _lib, sequential_scan_cuda as native
-    from fast_sequential_scan_b200.workloads import CONFIGS, make_inputs
+    from fast_sequential_scan_b200 import _lib, distributed as fd, sequential_scan_cuda as native
+    from fast_sequential_scan_b200 import workloads as wl
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -326,15 +631,32 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    peak, peak_kind = peaks()
+    use_graphs = not args.no_graphs
+    hs = Harness(torch, dist, dev, world, use_graphs)
+
     if args.mode == "seqpar":
-        run_seqpar(args, world, rank, dev)
+        rec = seqpar_record(hs, native, fd, wl, dev, rank, world, peak, args.steps, args.warmup) if world > 1 else None
+        if world == 1:
+            raise SystemExit("--mode seqpar needs torchrun with at least 2 ranks")
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": rec["elems_per_s"], "unit": UNIT, "n_gpus": world,
+                              "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": rec["ms_per_step"],
+                              "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                              "data": "synthetic", "config": {"workload": rec["workload"]}, "seqpar": rec}), flush=True)
+        dist.destroy_process_group()
         return
     if args.mode == "gated":
         if rank == 0:
-            run_gated(args, dev)
+            rec = gated_record(hs, native, wl, dev, peak, args.steps, max(3, args.repeats // 10))
+            print(json.dumps({"metric": "gated scan fwd elems/s", "value": rec["elems_per_s"], "unit": UNIT, "n_gpus": 1,
+                              "steps": args.steps, "ms_per_step": rec["ms_per_launch"], "higher_is_better": True,
+                              "dtype": "bf16", "data": "synthetic", "config": {"workload": rec["workload"]},
+                              "roofline": {"bound": "hbm", "achieved": rec["achieved_gbs"], "peak": peak, "unit": "GB/s",
+                                           "frac": rec["frac"], "traffic": None}}), flush=True)
         return
 
-    w = CONFIGS[args.workload]
+    w = wl.CONFIGS[args.workload]
     if args.shape:
         import dataclasses
         bb, tt, dd = (int(x) for x in args.shape.split(","))
@@ -343,120 +665,49 @@ def main():
     dt = w.torch_dtype
     esize = 2 if w.dtype == "bf16" else 4
     tensor_bytes = w.elems * esize
-    # rotate enough disjoint buffer sets that no step finds its inputs in L2
-    sets = max(3, -(-3 * L2_BYTES // (6 * tensor_bytes)))
-    sets = min(sets, 16)
-    bufs = []
-    for s in range(sets):
-        a, b, g = make_inputs(w, dev, seed=1000 * rank + s)
-        bufs.append(dict(a=a, b=b, g=g, h=torch.empty_like(a), da=torch.empty_like(a), db=torch.empty_like(a)))
-
-    def fwd(s):
-        x = bufs[s % sets]
-        native.forward_into(x["a"], x["b"], x["h"], algo=algo)
-
-    def bwd(s):
-        x = bufs[s % sets]
-        native.backward_into(x["a"], x["h"], x["g"], x["da"], x["db"], algo=algo)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    side = torch.cuda.Stream(dev)
-
-    def capture(fn, first, count):
-        """CUDA graph of `count` consecutive steps starting at buffer set `first` (the launches
-        themselves are the library's own C-ABI calls, recorded on the capture stream)."""
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=side):
-            for i in range(count):
-                fn(first + i)
-        return g
-
-    def timed(fn, steps, warmup, graphs=True):
-        """Device time per step of exactly `steps` steps, max over ranks.  With graphs the steps
-        are replayed from CUDA graphs of `sets` steps each (plus one shorter graph for the
-        remainder) so that host launch cost does not gate a ~50 us step."""
-        with torch.cuda.stream(side):
-            for i in range(max(warmup, 3)):
-                fn(i)
-        side.synchronize()
-        if graphs:
-            full, rem = divmod(steps, sets)
-            g_full = capture(fn, 0, sets) if full else None
-            g_rem = capture(fn, 0, rem) if rem else None
-            with torch.cuda.stream(side):
-                for g in (g_full, g_rem):
-                    if g is not None:
-                        g.replay()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(side):
-            e0.record()
-            if graphs:
-                for _ in range(full):
-                    g_full.replay()
-                if rem:
-                    g_rem.replay()
-            else:
-                for i in range(steps):
-                    fn(warmup + i)
-            e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms / steps
+    bufs = make_sets(torch, w, wl.make_inputs, dev, 1000 * rank)
+    sets = len(bufs)
+    fwd, bwd = step_fns(native, bufs, algo)
 
     # which kernels a step launches (for gpu_launches): probe the algorithm actually taken
-    took_lookback = True
-    try:
-        native.forward_into(bufs[0]["a"], bufs[0]["b"], bufs[0]["h"], algo=_lib.ALGO_LOOKBACK)
-    except _lib.FssError:
-        took_lookback = False
-    if args.algo == "chunked":
-        took_lookback = False
+    took_lookback = args.algo != "chunked"
+    if took_lookback:
+        try:
+            native.forward_into(bufs[0]["a"], bufs[0]["b"], bufs[0]["h"], algo=_lib.ALGO_LOOKBACK)
+        except _lib.FssError:
+            took_lookback = False
     launches_per_step = 2 if took_lookback else 6
 
-    use_graphs = not args.no_graphs
     sampler = ClockSampler(local) if rank == 0 else None
-    t_begin = time.perf_counter()
-    ms_step = timed(lambda i: (fwd(i), bwd(i)), args.steps, args.warmup, use_graphs)
-    ms_fwd = timed(fwd, args.steps, max(3, args.warmup // 4), use_graphs)
-    ms_bwd = timed(bwd, args.steps, max(3, args.warmup // 4), use_graphs)
-    # keep the same step loop running until the clock sampler (100 ms period) has a few samples
-    # under load; these extra steps are not part of any reported time
-    soak_steps = 0
-    while not args.no_soak and time.perf_counter() - t_begin < 1.5:
-        with torch.cuda.stream(side):
-            for i in range(200):
-                fwd(i); bwd(i)
-        side.synchronize()
-        soak_steps += 200
+    R = max(1, args.repeats)
+    ms_step = stats(hs.timed(lambda i: (fwd(i), bwd(i)), args.steps, args.warmup, R, sets))
+    ms_fwd = stats(hs.timed(fwd, args.steps, 3, R, sets))
+    ms_bwd = stats(hs.timed(bwd, args.steps, 3, R, sets))
     clocks = sampler.stop() if sampler else None
     if clocks is not None:
-        clocks["window"] = f"warm-up + timed region + {soak_steps} further steps of the same loop"
+        clocks["window"] = (f"warm-up + {3 * R} timed replays of {args.steps} steps "
+                            f"(~{(ms_step['median'] + ms_fwd['median'] + ms_bwd['median']) * args.steps * R:.0f} ms of kernels)")
     pkg.check_status()
 
     total_elems = w.elems * world
-    value = total_elems / (ms_step * 1e-3)
-    peak, peak_kind = peaks()
+    value = total_elems / (ms_step["median"] * 1e-3)
     bwd_bytes = w.elems * w.bytes_per_elem(backward=True, forward=False)
     fwd_bytes = w.elems * w.bytes_per_elem(backward=False, forward=True)
-    ach_bwd = bwd_bytes / (ms_bwd * 1e-3) / 1e9
-    ach_fwd = fwd_bytes / (ms_fwd * 1e-3) / 1e9
-    ach_step = (bwd_bytes + fwd_bytes) / (ms_step * 1e-3) / 1e9
-    kernel_bwd = "fss::lookback::scan_kernel<bf16, backward> (single pass)" if took_lookback else "fss::chunked::chunk_scan_backward (+summary, compose)"
+    ach_bwd = bwd_bytes / (ms_bwd["median"] * 1e-3) / 1e9
+    ach_fwd = fwd_bytes / (ms_fwd["median"] * 1e-3) / 1e9
+    ach_step = (bwd_bytes + fwd_bytes) / (ms_step["median"] * 1e-3) / 1e9
+    fam = "lookback" if took_lookback else "chunked"
+    kernel_bwd = ("fss::lookback::scan_kernel<bf16, backward> (single pass)" if took_lookback
+                  else "fss::chunked::chunk_scan_backward (+summary, compose)")
+    wl_key = args.workload if not args.shape else ""
     roofline = {"bound": "hbm", "kernel": kernel_bwd, "achieved": ach_bwd, "peak": peak, "unit": "GB/s",
-                "frac": ach_bwd / peak,
-                "traffic": NCU_TRAFFIC.get((args.workload if not args.shape else "", "lookback" if took_lookback else "chunked")),
+                "frac": ach_bwd / peak, "traffic": captured_traffic(wl_key, fam + "_backward"),
                 "algorithmic_bytes": bwd_bytes, "peak_kind": f"of {peak_kind}",
-                "ms_per_launch": ms_bwd,
-                "forward": {"achieved": ach_fwd, "frac": ach_fwd / peak, "ms_per_launch": ms_fwd},
+                "ms_per_launch": ms_bwd["median"], "ms_per_launch_min": ms_bwd["min"], "ms_per_launch_max": ms_bwd["max"],
+                "kernel_revision": kernel_revision(),
+                "forward": {"achieved": ach_fwd, "frac": ach_fwd / peak, "ms_per_launch": ms_fwd["median"],
+                            "ms_per_launch_min": ms_fwd["min"], "ms_per_launch_max": ms_fwd["max"],
+                            "algorithmic_bytes": fwd_bytes, "traffic": captured_traffic(wl_key, fam + "_forward")},
                 "step": {"achieved": ach_step, "frac": ach_step / peak}}
 
     # ---- end to end through the public autograd API, from pinned host memory ----
@@ -508,33 +759,71 @@ def main():
             torch.cuda.current_stream().wait_event(left)
 
         e_steps = max(3, min(args.steps, 20))
-        ms_e2e = timed(e2e_step, e_steps, 3, graphs=False)
-        e2e = {"value": total_elems / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e, "steps": e_steps,
+        ms_e2e = stats(hs.timed(e2e_step, e_steps, 3, 3, 1, graphs=False))
+        sec = ms_e2e["median"] * 1e-3
+        e2e = {"value": total_elems / sec, "unit": UNIT, "ms_per_step": ms_e2e["median"],
+               "ms_per_step_min": ms_e2e["min"], "ms_per_step_max": ms_e2e["max"], "steps": e_steps, "repeats": 3,
                "h2d_bytes_per_step": 3 * tensor_bytes, "d2h_bytes_per_step": 3 * tensor_bytes,
+               "h2d_gbs": 3 * tensor_bytes / sec / 1e9, "d2h_gbs": 3 * tensor_bytes / sec / 1e9,
+               "aggregate_host_gbs_per_direction": world * 3 * tensor_bytes / sec / 1e9,
+               "bound": "host<->device copies (PCIe and host staging shared by all ranks of the box), not the kernels: "
+                        f"{(ms_step['median'] / ms_e2e['median']) * 100:.1f} % of an e2e step is kernel time",
                "api": "scan_cu(alpha, beta); h.backward(grad) on tensors copied from pinned host memory; "
                       "h, dalpha, dbeta copied back; copies of neighbouring steps overlap the compute "
                       "(3 streams, 2 device buffer sets)"}
         pkg.check_status()
+        del dsets
+
+    # ---- side records ----
+    api = workloads = gated = strong = seqpar = None
+    if not args.no_side:
+        if world == 1:
+            api = api_record(torch, pkg, w, bufs, ms_step["median"])
+            pkg.check_status()
+    del bufs
+    torch.cuda.empty_cache()
+    if not args.no_side:
+        if world == 1:
+            workloads = [side_workload(hs, native, wl.make_inputs, wl.CONFIGS[n], dev, algo, peak) for n in SIDE_WORKLOADS]
+            gated = gated_record(hs, native, wl, dev, peak)
+            pkg.check_status()
+        else:
+            sr = max(5, R // 5)
+            if w.d_model % world == 0:
+                strong = strong_record(hs, native, fd, wl, w, dev, rank, world, algo, peak, args.steps, sr)
+            torch.cuda.empty_cache()
+            seqpar = seqpar_record(hs, native, fd, wl, dev, rank, world, peak, max(10, args.steps), args.warmup)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        v, kind, cores, sample, _ = cpu_reference_leg(w, args.cpu_seconds, os.cpu_count() or 1)
+        v, kind, cores, sample, _ = cpu_reference_leg(w, wl.make_inputs, args.cpu_seconds, os.cpu_count() or 1)
         cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample,
                "host_cpus": os.cpu_count()}
+        try:
+            cpu["torch_ref"] = cpu_torch_loop_leg(wl.CONFIGS["c1"], wl.make_inputs)
+        except Exception as e:
+            cpu["torch_ref"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "repeats": R, "ms_per_step": ms_step["median"],
+            "ms_per_step_min": ms_step["min"], "ms_per_step_max": ms_step["max"],
+            "timed_region_ms": ms_step["median"] * args.steps * R,
+            "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
             "config": {"workload": f"{w.name}: fwd+bwd scan, B{w.batch} T{w.seq} D{w.d_model} per GPU, {w.gates} gates",
-                       "algo": "lookback" if took_lookback else "chunked",
+                       "algo": fam,
                        "parallelism": f"channel-sharded x{world} (d_model {w.d_model * world} total), no collective",
                        "launch": "CUDA-graph replay of the C-ABI launches" if use_graphs else "one C-ABI call per kernel from Python",
+                       "timing": f"median over {R} repeats of a {args.steps}-step replay, each repeat max over ranks",
                        "l2": f"rotating {sets} disjoint buffer sets ({sets * 6 * tensor_bytes / 1e6:.0f} MB > 126 MB L2)"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-            "gpu_launches": launches_per_step * args.steps,
+            "gpu_launches": launches_per_step * args.steps * R,
         }
+        for key, rec in (("api", api), ("workloads", workloads), ("gated", gated), ("strong", strong), ("seqpar", seqpar)):
+            if rec is not None:
+                line[key] = rec
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -16,7 +16,8 @@ namespace fss {
 
 thread_local std::string g_cuda_error;
 
-static int cuda_fail(cudaError_t e, const char *what, int code = FSS_E_LAUNCH) {
+// shared with the other translation units of the library (declared in fss_common.cuh)
+int cuda_fail(cudaError_t e, const char *what, int code) {
     g_cuda_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
     return code;
 }
@@ -24,7 +25,7 @@ static int cuda_fail(cudaError_t e, const char *what, int code = FSS_E_LAUNCH) {
 #define FSS_CUDA(call, what)                                      \
     do {                                                          \
         cudaError_t e_ = (call);                                  \
-        if (e_ != cudaSuccess) return cuda_fail(e_, what);        \
+        if (e_ != cudaSuccess) return cuda_fail(e_, what, FSS_E_LAUNCH); \
     } while (0)
 
 // Makes ctx->device current for the duration of a call and puts the previous one back.  The
@@ -59,16 +60,25 @@ static int check_ctx(const fss_scan_ctx *ctx) {
 }
 
 static int check_view(const fss_view *v, int64_t B, int64_t T, int64_t D) {
-    if (!v || !v->ptr) return FSS_E_NULL;
-    if (v->stride_t < D) return FSS_E_SHAPE;
-    if (B > 1 && v->stride_b < (T - 1) * v->stride_t + D) return FSS_E_SHAPE;
-    return FSS_OK;
+    return check_view_extents(v, B, T, D);
 }
+
+// Two views are "the same tensor" when they start at the same address.  Outputs that start where
+// an input starts are refused (the one sanctioned case, grad_beta over h, is handled by the
+// caller); partial overlaps of differently placed views are the caller's responsibility.
+static bool same_start(const fss_view *a, const fss_view *b) { return a->ptr == b->ptr; }
 
 static int check_shape(int dtype, int64_t B, int64_t T, int64_t D) {
     if (dtype != FSS_DTYPE_BF16 && dtype != FSS_DTYPE_F32) return FSS_E_DTYPE;
     if (B < 0 || T < 0 || D < 0) return FSS_E_SHAPE;
     return FSS_OK;
+}
+
+// A call that may end in the chunked kernels must fit their linear grid (checked for the
+// one-element-per-thread geometry, the largest grid the family launches).
+static int check_chunked_grid(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D) {
+    if (ctx->algo == FSS_ALGO_LOOKBACK) return FSS_OK;
+    return chunked::grid_fits(chunked::make_geometry(B, T, D, 1)) ? FSS_OK : FSS_E_SHAPE;
 }
 
 static int need_workspace(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t D, int dtype) {
@@ -79,7 +89,7 @@ static int need_workspace(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t
 
 static int launch_check(const char *what) {
     cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? FSS_OK : cuda_fail(e, what);
+    return e == cudaSuccess ? FSS_OK : cuda_fail(e, what, FSS_E_LAUNCH);
 }
 
 // ------------------------------------------------------------------ chunked path
@@ -93,6 +103,7 @@ static int chunked_forward(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64
     float *wsP = reinterpret_cast<float *>(plan_workspace(ctx->workspace, ctx->workspace_bytes).floats);
     float *wsC = reinterpret_cast<float *>((char *)wsP + align_up((size_t)(B * g.S * D) * sizeof(float), 256));
     const bool cont = ctx->flags & FSS_FLAG_CONTINUATION;
+    if (!chunked::grid_fits(g)) return FSS_E_SHAPE;
     const unsigned blocks = (unsigned)(g.vblocks * g.S * B);
     auto a = make_view<const T>(alpha);
     auto b = make_view<const T>(beta);
@@ -117,6 +128,7 @@ static int chunked_backward(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int6
     float *wsP = reinterpret_cast<float *>(plan_workspace(ctx->workspace, ctx->workspace_bytes).floats);
     float *wsC = reinterpret_cast<float *>((char *)wsP + align_up((size_t)(B * g.S * D) * sizeof(float), 256));
     const bool cont = ctx->flags & FSS_FLAG_CONTINUATION;
+    if (!chunked::grid_fits(g)) return FSS_E_SHAPE;
     const unsigned blocks = (unsigned)(g.vblocks * g.S * B);
     auto a = make_view<const T>(alpha);
     auto hh = make_view<const T>(h);
@@ -200,6 +212,7 @@ FSS_API const char *fss_strerror(int code) {
     case FSS_E_TENSORMAP: return "TMA descriptor rejected by the driver";
     case FSS_E_ARGS: return "struct_bytes does not match this library";
     case FSS_E_TOO_LARGE: return "problem larger than this entry point's fixed capacity";
+    case FSS_E_ALIAS: return "an output tensor starts at the address of an input (or of the other output)";
     }
     return "unknown error code";
 }
@@ -234,6 +247,8 @@ FSS_API int fss_scan_forward_ex(const fss_scan_ctx *ctx, int dtype, int64_t B, i
     if (B == 0 || T == 0 || D == 0) return FSS_OK;
     if ((rc = check_view(alpha, B, T, D)) || (rc = check_view(beta, B, T, D)) || (rc = check_view(h, B, T, D)))
         return rc;
+    if (same_start(h, alpha) || same_start(h, beta)) return FSS_E_ALIAS;
+    if ((rc = check_chunked_grid(ctx, B, T, D))) return rc;
     if ((rc = need_workspace(ctx, B, T, D, dtype))) return rc;
     DeviceGuard guard(ctx->device);
     if (guard.error) return guard.error;
@@ -252,6 +267,7 @@ FSS_API int fss_scan_forward_gated(const fss_scan_ctx *ctx, int dtype, int64_t B
     if (!lambda) return FSS_E_NULL;
     for (const fss_view *v : {r, i, x, h})
         if ((rc = check_view(v, B, T, D))) return rc;
+    if (same_start(h, r) || same_start(h, i) || same_start(h, x)) return FSS_E_ALIAS;
     if (state && (state->prod || state->block_prod || state->block_state)) return FSS_E_ARGS;
     if (ctx->algo == FSS_ALGO_CHUNKED) return FSS_E_LAYOUT;       // single-pass kernel only
     if ((rc = need_workspace(ctx, B, T, D, dtype))) return rc;
@@ -276,6 +292,11 @@ FSS_API int fss_scan_backward_ex(const fss_scan_ctx *ctx, int dtype, int64_t B, 
     if (B == 0 || T == 0 || D == 0) return FSS_OK;
     for (const fss_view *v : {alpha, h, grad_out, grad_alpha, grad_beta})
         if ((rc = check_view(v, B, T, D))) return rc;
+    // grad_beta may be h itself (checked in backward_typed); every other coincidence is refused
+    if (same_start(grad_alpha, alpha) || same_start(grad_alpha, h) || same_start(grad_alpha, grad_out) ||
+        same_start(grad_alpha, grad_beta) || same_start(grad_beta, alpha) || same_start(grad_beta, grad_out))
+        return FSS_E_ALIAS;
+    if ((rc = check_chunked_grid(ctx, B, T, D))) return rc;
     if ((rc = need_workspace(ctx, B, T, D, dtype))) return rc;
     DeviceGuard guard(ctx->device);
     if (guard.error) return guard.error;
@@ -411,13 +432,3 @@ FSS_API int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_
     return chunked::vector_ok<float>(D, {alpha, h, grad_out, grad_alpha, grad_beta}) ? FSS_FIXB(float, 4) : FSS_FIXB(float, 1);
 #undef FSS_FIXB
 }
-
-#ifdef FSS_TRACE
-// development builds only: install / remove the timeline buffer ([ctas][units][8] uint64)
-FSS_API int fss_debug_set_trace(void *buffer, int units) {
-    unsigned long long *ptr = static_cast<unsigned long long *>(buffer);
-    if (cudaMemcpyToSymbol(fss::lookback::g_trace, &ptr, sizeof(ptr)) != cudaSuccess) return FSS_E_LAUNCH;
-    if (cudaMemcpyToSymbol(fss::lookback::g_trace_units, &units, sizeof(units)) != cudaSuccess) return FSS_E_LAUNCH;
-    return FSS_OK;
-}
-#endif

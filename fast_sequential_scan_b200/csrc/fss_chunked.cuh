@@ -194,7 +194,6 @@ inline int64_t pick_chunk_rows(int64_t B, int64_t T, int64_t nvec) {
     int64_t L = ceil_div(T, S);
     if (L < 16) L = 16;
     if (L > 256) L = 256;
-    // keep the chunk count inside a 31-bit linear grid together with the other two axes
     return L;
 }
 
@@ -216,6 +215,15 @@ inline Geometry make_geometry(int64_t B, int64_t T, int64_t D, int V) {
     g.S = ceil_div(T, g.L);
     g.vblocks = ceil_div(g.nvec, kThreads);
     return g;
+}
+
+// The kernels run on a linear grid of (channel blocks x chunks x batch rows) CTAs, which has to
+// fit the 31 bits of gridDim.x; launchers refuse larger problems with FSS_E_SHAPE.
+inline bool grid_fits(const Geometry &g) {
+    if (g.vblocks <= 0 || g.S <= 0 || g.B <= 0) return false;
+    const int64_t lim = 0x7fffffffLL;
+    if (g.vblocks > lim || g.S > lim / g.vblocks) return false;
+    return g.B <= lim / (g.vblocks * g.S);
 }
 
 inline size_t workspace_bytes(int64_t B, int64_t T, int64_t D) {

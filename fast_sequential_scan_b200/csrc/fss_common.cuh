@@ -114,6 +114,23 @@ __device__ __forceinline__ void report_status(int32_t *status, int32_t code) {
 
 // ------------------------------------------------------------------ host helpers
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Records the text fss_last_cuda_error() returns for the calling thread and hands back `code`
+// (defined once, in fss_api.cu).
+int cuda_fail(cudaError_t e, const char *what, int code);
+
+// A view must span its extents without rows or batches overlapping, and its last element's
+// offset must be representable (the kernels index with 64-bit element offsets).
+inline int check_view_extents(const fss_view *v, int64_t B, int64_t T, int64_t D) {
+    if (!v || !v->ptr) return FSS_E_NULL;
+    if (v->stride_t < D) return FSS_E_SHAPE;
+    if (T > 1 && v->stride_t > (INT64_MAX / 8) / T) return FSS_E_SHAPE;
+    if (B > 1) {
+        if (v->stride_b < (T - 1) * v->stride_t + D) return FSS_E_SHAPE;
+        if (v->stride_b > (INT64_MAX / 8) / B) return FSS_E_SHAPE;
+    }
+    return FSS_OK;
+}
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -55,10 +55,7 @@ constexpr int kPass2Warp0 = kW;               // warps [0,kW) run pass 1, [kW,2k
 constexpr int kProducerWarp = 2 * kW;
 constexpr int kSummaryWarp = 2 * kW + 1;
 constexpr int kLookbackWarp0 = 2 * kW + 2;    // first of the look-back warps
-#ifndef FSS_LB_WARPS
-#define FSS_LB_WARPS 2
-#endif
-constexpr int kLookbackWarps = FSS_LB_WARPS;
+constexpr int kLookbackWarps = 2;             // three were measured slower on every workload
 constexpr int kGens = 4;                      // generations of summary buffers: pass 1 may run this far ahead of pass 2
 constexpr int kThreads = (2 * kW + 2 + kLookbackWarps) * 32;
 constexpr int kStagesFwd = 6;                 // 6 x 32 KiB
@@ -66,10 +63,7 @@ constexpr int kStagesBwd = 4;                 // 4 x 48 KiB
 constexpr uint32_t kMaxSpins = 1u << 21;      // per wait; ~a second before giving up
 
 constexpr uint32_t kStateAggregate = 1, kStateInclusive = 2;
-#ifndef FSS_WINDOW
-#define FSS_WINDOW 2
-#endif
-constexpr int kWindow = FSS_WINDOW;           // predecessors inspected per look-back round trip
+constexpr int kWindow = 2;                    // predecessors inspected per look-back round trip
 
 template <typename T> struct Cfg {
     static constexpr int V = kLaneBytes / (int)sizeof(T);   // channels per lane
@@ -111,35 +105,6 @@ struct Params {
     int32_t grid_q, grid_b, grid_cg;
 
 };
-
-// ------------------------------------------------------------------ optional timeline trace
-// Compiled in only with -DFSS_TRACE (development builds): every role stamps the global
-// nanosecond timer per work unit into a caller-provided buffer [cta][unit][event].
-#ifdef FSS_TRACE
-__device__ unsigned long long *g_trace = nullptr;
-__device__ int g_trace_units = 0;
-enum { kEvFull = 0, kEvP1 = 1, kEvSum = 2, kEvLbStart = 3, kEvLbDone = 4, kEvP2 = 5, kEvLbTop = 6, kEvRefill = 7,
-       kEvLbIssued = 8, kEvLbFound = 9, kEvCarrySeen = 10, kEvLbA = 11, kEvLbB = 12, kEvLbC = 13, kEvLbE = 14, kEvents = 16 };
-__device__ __forceinline__ void trace(int64_t unit, int ev) {
-    if (g_trace && unit < g_trace_units) {
-        const unsigned long long t = (unsigned long long)clock64();   // SM clock: comparable inside a CTA
-        g_trace[((int64_t)blockIdx.x * g_trace_units + unit) * kEvents + ev] = t;
-    }
-}
-#define FSS_TRACE_EV(unit, ev) do { if ((threadIdx.x & 31) == 0) trace(unit, ev); } while (0)
-// kernel life: slot 15 of units 0..4 = SM clock at entry / after set-up / at exit, global ns at entry / exit
-__device__ __forceinline__ void trace_life(int which, bool global_ns) {
-    if (g_trace && threadIdx.x == 0 && which < g_trace_units) {
-        unsigned long long t;
-        if (global_ns) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); else t = (unsigned long long)clock64();
-        g_trace[((int64_t)blockIdx.x * g_trace_units + which) * kEvents + 15] = t;
-    }
-}
-#define FSS_TRACE_LIFE(which, ns) trace_life(which, ns)
-#else
-#define FSS_TRACE_LIFE(which, ns) do { } while (0)
-#define FSS_TRACE_EV(unit, ev) do { } while (0)
-#endif
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -524,8 +489,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q = lane / LPG, cl = lane % LPG;
-    FSS_TRACE_LIFE(0, false);
-    FSS_TRACE_LIFE(3, true);
     const uint32_t first = blockIdx.x;
     const Unit u0 = unit_of_tile(p, first);
     // Programmatic dependent launch: let the next launch on the stream start its own set-up as SMs
@@ -541,7 +504,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         fence_proxy_async();
     }
     __syncthreads();
-    FSS_TRACE_LIFE(1, false);
     const Ctl ctl{p.hdr, p.status, cta_abort, p.max_spins};
     using Cursor = UnitCursor<kTickets, kStages>;
     // This launch's epoch (tags of its descriptors) is only needed by the summary and look-back
@@ -633,7 +595,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                     if (nu.k >= 0) tma_wait_read_all();   // the stage may be overwritten once the store has read it
                 }
                 post();
-                if (i >= 0) FSS_TRACE_EV(i, kEvRefill);
             }
             // leave nothing in flight: loads that were issued but never consumed, and all stores
             if (i < issued) {
@@ -667,7 +628,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             const bool last_block = u.s + 1 == (int32_t)p.S;
             const int32_t it_s = u.s;
             if (!ctl.wait(bar_agg(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
-            FSS_TRACE_EV(i, kEvLbA);
             // Lane (q, cl) owns the kW consecutive row groups q*kW .. q*kW+kW-1 (one per pass-1 warp):
             // it folds them in scan order, the kSp lane groups are combined with one shuffle scan,
             // and every slot then receives the map of all groups BEFORE it (its exclusive prefix).
@@ -736,7 +696,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             if (lane == 0) mbar_arrive(bar_sum(g));
             if (!last_block && q == 0 && !(p.mute_first_block && it_s == 0))
                 AggPk::store(p.packets + k * kTilePackets + cl, pc, tag_agg);
-            FSS_TRACE_EV(i, kEvSum);
         }
     } else if (warp >= kLookbackWarp0) {
         // ============================================================ look-back
@@ -796,7 +755,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 }
             }
             if (!ctl.wait(bar_sum(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
-            FSS_TRACE_EV(i, kEvLbStart);
             if (s > 0 && !hit) {       // one more look now that the summary is in
                 typename IncPk::Raw again;
                 IncPk::load_raw(inc_packets(k - p.ncols), again);
@@ -900,7 +858,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_carry(g));
-            FSS_TRACE_EV(i, kEvLbDone);
 
             // ---- publish the inclusive descriptor: state after this tile, product through it
             float out[NI];
@@ -967,7 +924,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 if (!ctl.wait(bar_done((int)(o % kStages)), (uint32_t)((o / kStages) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
             }
             if (!ctl.wait(bar_full(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
-            if (warp == 0) FSS_TRACE_EV(i, kEvFull);
             Raw *a_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + lane_off);
             Raw *x_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + kTileBytes + lane_off);
             // gated forward: the alpha slot arrives holding r, the third slot i; this pass turns them
@@ -1056,8 +1012,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             agg_at(g, warp, 1, lane) = vc;
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_agg(g));
-            if (warp == 0) FSS_TRACE_EV(i, kEvP1);
-            if (warp > 0) FSS_TRACE_EV(i, kEvLbA + warp);
         }
     } else {
         // ============================================================ pass 2
@@ -1086,7 +1040,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             Raw *h_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + 2 * kTileBytes + lane_off);
             // the carry barrier is reached through pass 1 of this unit, so the tile is resident
             if (!ctl.wait(bar_carry(g), (uint32_t)((i / kGens) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
-            if (w2 == 0) FSS_TRACE_EV(i, kEvCarrySeen);
             // state entering this warp's rows = (map of the warps before it)(state entering the tile)
             float stv[V];
             {
@@ -1169,14 +1122,11 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             fence_proxy_async();      // make the in-place results visible to the TMA store
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_done(st));
-            if (w2 == 0) FSS_TRACE_EV(i, kEvP2);
         }
     }
 
     // ---- leave: the last CTA advances the epoch, which invalidates every descriptor of this launch
     __syncthreads();
-    FSS_TRACE_LIFE(2, false);
-    FSS_TRACE_LIFE(4, true);
     if (threadIdx.x == 0) {
         __threadfence();
         const uint32_t prev = atomicAdd(&p.hdr->done, 1u);
@@ -1195,7 +1145,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
 // multiply the number of columns; with fewer columns than about two per SM several row blocks of
 // one column are in flight at once and the carry chain between them limits the speed.
 inline int choose_split(int dtype, int64_t B, int64_t T, int64_t D) {
-    if (const char *e = getenv("FSS_B200_SPLIT")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4) return v; }
+    static const int env = [] { const char *e = getenv("FSS_B200_SPLIT"); return e ? atoi(e) : 0; }();
+    if (env == 1 || env == 2 || env == 4) return env;
     const int64_t row_bytes = D * (dtype == FSS_DTYPE_BF16 ? 2 : 4);
     const int64_t cols = B * ceil_div(row_bytes, kRowBytes);
     int s = 1;
@@ -1291,6 +1242,43 @@ inline bool make_map(CUtensorMap *map, const fss_view *v, int64_t B, int64_t Tn,
     return true;
 }
 
+// Encoding a descriptor is a driver call; a training loop presents the same few tensors (same
+// address, shape and strides) launch after launch, so each host thread keeps the descriptors it
+// built last: 16 sets x 4 ways, keyed by everything the encoding depends on.  A descriptor holds
+// no reference to the memory it describes, so an entry stays valid when the buffer is freed and
+// the address is reused for a tensor of the same geometry.
+struct MapKey {
+    const void *ptr;
+    int64_t B, T, D, sb, st;
+    int32_t split, esize;
+    bool operator==(const MapKey &o) const {
+        return ptr == o.ptr && B == o.B && T == o.T && D == o.D && sb == o.sb && st == o.st && split == o.split &&
+               esize == o.esize;
+    }
+};
+struct MapCache {
+    static constexpr int kSets = 16, kWays = 4;
+    struct Slot { MapKey key; CUtensorMap map; bool valid; };
+    Slot slots[kSets][kWays] = {};
+    uint8_t next[kSets] = {};
+};
+template <typename T>
+inline const CUtensorMap *cached_map(const fss_view *v, int64_t B, int64_t Tn, int64_t D, int split, std::string *err) {
+    static thread_local MapCache cache;
+    const MapKey key{v->ptr, B, Tn, D, v->stride_b, v->stride_t, split, (int32_t)sizeof(T)};
+    const uintptr_t a = reinterpret_cast<uintptr_t>(v->ptr);
+    const int set = (int)(((a >> 9) ^ (a >> 21) ^ (uintptr_t)split) % MapCache::kSets);
+    for (auto &slot : cache.slots[set])
+        if (slot.valid && slot.key == key) return &slot.map;
+    auto &slot = cache.slots[set][cache.next[set]];
+    cache.next[set] = (uint8_t)((cache.next[set] + 1) % MapCache::kWays);
+    slot.valid = false;
+    if (!make_map<T>(&slot.map, v, B, Tn, D, split, err)) return nullptr;
+    slot.key = key;
+    slot.valid = true;
+    return &slot.map;
+}
+
 // CTAs that fit the device at once (one per SM with these shared-memory sizes), per device.
 template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets, bool kGate> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
     static std::mutex mu;
@@ -1323,15 +1311,18 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     constexpr int smem_bytes = Smem<kTensors, kStages>::kBytes;
     constexpr int Dc = Cfg<T>::Dc / kSp;
 
+    // copies: a later look-up may evict the slot an earlier pointer refers to
     CUtensorMap m_alpha, m_x, m_h, m_o0, m_o1;
-    if (!make_map<T>(&m_alpha, alpha, B, Tn, D, kSp, err_text) || !make_map<T>(&m_x, x, B, Tn, D, kSp, err_text) ||
-        !make_map<T>(&m_o0, out0, B, Tn, D, kSp, err_text))
-        return FSS_E_TENSORMAP;
+    auto fetch = [&](CUtensorMap *dst, const fss_view *v) {
+        const CUtensorMap *m = cached_map<T>(v, B, Tn, D, kSp, err_text);
+        if (m) *dst = *m;
+        return m != nullptr;
+    };
+    if (!fetch(&m_alpha, alpha) || !fetch(&m_x, x) || !fetch(&m_o0, out0)) return FSS_E_TENSORMAP;
     if (kBackward) {
-        if (!make_map<T>(&m_h, h, B, Tn, D, kSp, err_text) || !make_map<T>(&m_o1, out1, B, Tn, D, kSp, err_text))
-            return FSS_E_TENSORMAP;
+        if (!fetch(&m_h, h) || !fetch(&m_o1, out1)) return FSS_E_TENSORMAP;
     } else if (kGate) {
-        if (!make_map<T>(&m_h, h, B, Tn, D, kSp, err_text)) return FSS_E_TENSORMAP;      // the input gate
+        if (!fetch(&m_h, h)) return FSS_E_TENSORMAP;      // the input gate
         m_o1 = m_o0;
     } else {
         m_h = m_alpha; m_o1 = m_o0;

@@ -41,18 +41,12 @@ int scratch_address(int device, void **out) {
     if (!g_scratch_known[device]) {
         void *ptr = nullptr;
         const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-        if (e != cudaSuccess || ptr == nullptr) return FSS_E_DEVICE;
+        if (e != cudaSuccess) return fss::cuda_fail(e, "cudaGetSymbolAddress(no-alloc scratch)", FSS_E_DEVICE);
+        if (ptr == nullptr) return FSS_E_DEVICE;
         g_scratch_addr[device] = ptr;
         g_scratch_known[device] = true;
     }
     *out = g_scratch_addr[device];
-    return FSS_OK;
-}
-
-int check_view(const fss_view *v, int64_t B, int64_t T, int64_t D) {
-    if (!v || !v->ptr) return FSS_E_NULL;
-    if (v->stride_t < D) return FSS_E_SHAPE;
-    if (B > 1 && v->stride_b < (T - 1) * v->stride_t + D) return FSS_E_SHAPE;
     return FSS_OK;
 }
 
@@ -65,6 +59,7 @@ int run(cudaStream_t stream, float *scratch, int64_t B, int64_t Tn, int64_t D, c
     const size_t half = align_up((size_t)(B * g.S * D) * sizeof(float), 256);
     float *wsP = scratch;
     float *wsC = reinterpret_cast<float *>(reinterpret_cast<char *>(scratch) + half);
+    if (!grid_fits(g)) return FSS_E_SHAPE;
     const unsigned blocks = (unsigned)(g.vblocks * g.S * B);
     auto a = make_view<const T>(alpha);
     auto b = make_view<const T>(beta);
@@ -72,7 +67,8 @@ int run(cudaStream_t stream, float *scratch, int64_t B, int64_t Tn, int64_t D, c
     chunk_compose<false><<<(unsigned)ceil_div(B * D, 128), 128, 0, stream>>>(g, wsP, wsC, nullptr, nullptr,
                                                                            nullptr, nullptr, nullptr);
     chunk_scan_forward<T, V><<<blocks, kThreads, 0, stream>>>(g, a, b, make_view<T>(h), wsC, false);
-    return cudaGetLastError() == cudaSuccess ? FSS_OK : FSS_E_LAUNCH;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? FSS_OK : cuda_fail(e, "no-alloc forward launch", FSS_E_LAUNCH);
 }
 
 }  // namespace
@@ -85,15 +81,18 @@ int fss_scan_forward_noalloc(int dtype, int device, void *stream, int64_t B, int
     if (B < 0 || T < 0 || D < 0) return FSS_E_SHAPE;
     if (B == 0 || T == 0 || D == 0) return FSS_OK;
     int rc;
-    if ((rc = check_view(alpha, B, T, D)) || (rc = check_view(beta, B, T, D)) || (rc = check_view(h, B, T, D)))
+    if ((rc = check_view_extents(alpha, B, T, D)) || (rc = check_view_extents(beta, B, T, D)) ||
+        (rc = check_view_extents(h, B, T, D)))
         return rc;
     // the fixed scratch bounds the problem: two fp32 values per (batch, chunk, channel)
     if (chunked::workspace_bytes(B, T, D) > (size_t)FSS_NOALLOC_SCRATCH_BYTES) return FSS_E_TOO_LARGE;
 
     int prev = -1;
-    if (cudaGetDevice(&prev) != cudaSuccess) return FSS_E_DEVICE;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice", FSS_E_DEVICE);
     const int dev = device >= 0 ? device : prev;
-    if (cudaSetDevice(dev) != cudaSuccess) return FSS_E_DEVICE;      // the lookup needs `dev` current
+    e = cudaSetDevice(dev);                                          // the lookup needs `dev` current
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice", FSS_E_DEVICE);
     void *scratch = nullptr;
     rc = scratch_address(dev, &scratch);
     if (rc == FSS_OK) {

@@ -50,6 +50,8 @@ def _check_tensor(name: str, t: torch.Tensor, like: Optional[torch.Tensor], dtyp
 
 def _rowwise(t: torch.Tensor) -> torch.Tensor:
     """A tensor the kernels can address: unit channel stride, rows and batches not overlapping."""
+    if t.is_contiguous():
+        return t
     B, T, D = t.shape
     if t.numel() == 0:
         return t
@@ -60,15 +62,38 @@ def _rowwise(t: torch.Tensor) -> torch.Tensor:
 
 def _view(t: torch.Tensor) -> _lib.View:
     B, T, D = t.shape
+    if t.is_contiguous():
+        return _lib.View(t.data_ptr(), max(T * D, 1), D)
     st = t.stride(1) if T > 1 else D
     sb = t.stride(0) if B > 1 else max(st * T, 1)
     return _lib.View(t.data_ptr(), sb, st)
 
 
+_ws_bytes_cache: dict = {}
+
+
+def _workspace_for(t: torch.Tensor, dtype_id: int) -> workspace.Workspace:
+    """The calling stream's workspace on ``t``'s device, large enough for a scan of ``t``'s shape.
+    The size query is a native call; its answers are remembered per shape."""
+    key = (t.shape, dtype_id)
+    need = _ws_bytes_cache.get(key)
+    if need is None:
+        B, T, D = t.shape
+        need = _ws_bytes_cache[key] = _lib.lib().fss_workspace_bytes(B, T, D, dtype_id)
+    return workspace.get(t.device, need)
+
+
 def _ctx(device: torch.device, ws: workspace.Workspace, algo: Optional[int], flags: int = 0) -> _lib.ScanCtx:
-    return _lib.ScanCtx(ctypes.sizeof(_lib.ScanCtx), device.index, ws.stream_handle,
-                        ws.buf.data_ptr(), ws.buf.numel(), ws.status.data_ptr(),
-                        default_algo() if algo is None else algo, flags)
+    """The per-call context; the struct lives with the workspace and only algo / flags change per call.
+    ``device`` goes to the library, which makes it current for the launch, so no torch device
+    context is entered here."""
+    ctx = ws.ctx
+    if ctx is None or ctx.workspace != ws.buf.data_ptr():
+        ctx = ws.ctx = _lib.ScanCtx(ctypes.sizeof(_lib.ScanCtx), device.index if device.index is not None else -1,
+                                    ws.stream_handle, ws.buf.data_ptr(), ws.buf.numel(), ws.status.data_ptr(), 0, 0)
+    ctx.algo = default_algo() if algo is None else algo
+    ctx.flags = flags
+    return ctx
 
 
 def _vec(t: Optional[torch.Tensor], B: int, D: int, name: str) -> Optional[int]:
@@ -87,6 +112,32 @@ def _blocks(t: Optional[torch.Tensor], name: str) -> Optional[int]:
     return t.data_ptr()
 
 
+def _launch_forward(a, b, h, dtype_id: int, algo, flags: int, state) -> None:
+    """One checked call of ``fss_scan_forward_ex`` on tensors that were validated by the caller."""
+    B, T, D = a.shape
+    ws = _workspace_for(a, dtype_id)
+    ctx = _ctx(a.device, ws, algo, flags)
+    va, vb, vh = _view(a), _view(b), _view(h)
+    rc = _lib.lib().fss_scan_forward_ex(ctypes.byref(ctx), dtype_id, B, T, D, ctypes.byref(va), ctypes.byref(vb),
+                                        ctypes.byref(vh), ctypes.byref(state) if state is not None else None)
+    workspace.launched(ws)
+    if rc:
+        _lib.check(rc, "fss_scan_forward_ex")
+
+
+def _launch_backward(a, hh, g, grad_alpha, grad_beta, dtype_id: int, algo, flags: int, state) -> None:
+    B, T, D = a.shape
+    ws = _workspace_for(a, dtype_id)
+    ctx = _ctx(a.device, ws, algo, flags)
+    v0, v1, v2, v3, v4 = _view(a), _view(hh), _view(g), _view(grad_alpha), _view(grad_beta)
+    rc = _lib.lib().fss_scan_backward_ex(ctypes.byref(ctx), dtype_id, B, T, D, ctypes.byref(v0), ctypes.byref(v1),
+                                         ctypes.byref(v2), ctypes.byref(v3), ctypes.byref(v4),
+                                         ctypes.byref(state) if state is not None else None)
+    workspace.launched(ws)
+    if rc:
+        _lib.check(rc, "fss_scan_backward_ex")
+
+
 def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_last=None,
                  prod=None, block_prod=None, block_state=None, _extra_flags: int = 0) -> None:
     """h <- scan(alpha, beta) into a caller-owned tensor, with the optional boundary state."""
@@ -102,20 +153,12 @@ def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_
     a, b = _rowwise(alpha), _rowwise(beta)
     if _rowwise(h) is not h:
         raise RuntimeError("h: output must have unit channel stride and non-overlapping rows")
-    L = _lib.lib()
-    with torch.cuda.device(alpha.device):
-        ws = workspace.get(alpha.device, L.fss_workspace_bytes(B, T, D, _DTYPES[dtype]))
-        ctx = _ctx(alpha.device, ws, algo, (_lib.FLAG_CONTINUATION if continuation else 0) | _extra_flags)
-        state = None
-        if any(x is not None for x in (h_in, h_last, prod, block_prod, block_state)):
-            state = _lib.ForwardState(_vec(h_in, B, D, "h_in"), _vec(h_last, B, D, "h_last"),
-                                      _vec(prod, B, D, "prod"), _blocks(block_prod, "block_prod"),
-                                      _blocks(block_state, "block_state"))
-        va, vb, vh = _view(a), _view(b), _view(h)
-        rc = L.fss_scan_forward_ex(ctypes.byref(ctx), _DTYPES[dtype], B, T, D, ctypes.byref(va),
-                                   ctypes.byref(vb), ctypes.byref(vh),
-                                   ctypes.byref(state) if state is not None else None)
-    _lib.check(rc, "fss_scan_forward_ex")
+    state = None
+    if not (h_in is None and h_last is None and prod is None and block_prod is None and block_state is None):
+        state = _lib.ForwardState(_vec(h_in, B, D, "h_in"), _vec(h_last, B, D, "h_last"),
+                                  _vec(prod, B, D, "prod"), _blocks(block_prod, "block_prod"),
+                                  _blocks(block_state, "block_state"))
+    _launch_forward(a, b, h, _DTYPES[dtype], algo, (_lib.FLAG_CONTINUATION if continuation else 0) | _extra_flags, state)
 
 
 def gates_reference(r, i, x, lam):
@@ -147,17 +190,16 @@ def forward_gated_into(r, i, x, lam, h, *, continuation=False, h_in=None, h_last
     rr, ii, xx = _rowwise(r), _rowwise(i), _rowwise(x)
     if _rowwise(h) is not h:
         raise RuntimeError("h: output must have unit channel stride and non-overlapping rows")
-    L = _lib.lib()
-    with torch.cuda.device(r.device):
-        ws = workspace.get(r.device, L.fss_workspace_bytes(B, T, D, _DTYPES[dtype]))
-        ctx = _ctx(r.device, ws, None, _lib.FLAG_CONTINUATION if continuation else 0)
-        state = None
-        if h_in is not None or h_last is not None:
-            state = _lib.ForwardState(_vec(h_in, B, D, "h_in"), _vec(h_last, B, D, "h_last"), None, None, None)
-        views = [_view(t) for t in (rr, ii, xx, h)]
-        rc = L.fss_scan_forward_gated(ctypes.byref(ctx), _DTYPES[dtype], B, T, D, ctypes.byref(views[0]),
-                                      ctypes.byref(views[1]), ctypes.byref(views[2]), lam.data_ptr(),
-                                      ctypes.byref(views[3]), ctypes.byref(state) if state is not None else None)
+    ws = _workspace_for(r, _DTYPES[dtype])
+    ctx = _ctx(r.device, ws, None, _lib.FLAG_CONTINUATION if continuation else 0)
+    state = None
+    if h_in is not None or h_last is not None:
+        state = _lib.ForwardState(_vec(h_in, B, D, "h_in"), _vec(h_last, B, D, "h_last"), None, None, None)
+    views = [_view(t) for t in (rr, ii, xx, h)]
+    rc = _lib.lib().fss_scan_forward_gated(ctypes.byref(ctx), _DTYPES[dtype], B, T, D, ctypes.byref(views[0]),
+                                           ctypes.byref(views[1]), ctypes.byref(views[2]), lam.data_ptr(),
+                                           ctypes.byref(views[3]), ctypes.byref(state) if state is not None else None)
+    workspace.launched(ws)
     _lib.check(rc, "fss_scan_forward_gated")
 
 
@@ -192,45 +234,44 @@ def backward_into(alpha, h, grad_out, grad_alpha, grad_beta, *, algo=None, conti
     for name, t in (("grad_alpha", grad_alpha), ("grad_beta", grad_beta)):
         if _rowwise(t) is not t:
             raise RuntimeError(f"{name}: output must have unit channel stride and non-overlapping rows")
-    L = _lib.lib()
-    with torch.cuda.device(alpha.device):
-        ws = workspace.get(alpha.device, L.fss_workspace_bytes(B, T, D, _DTYPES[dtype]))
-        ctx = _ctx(alpha.device, ws, algo, _lib.FLAG_CONTINUATION if continuation else 0)
-        state = None
-        if any(x is not None for x in (u_in, h_prev, u_out, block_prod, block_state)):
-            state = _lib.BackwardState(_vec(u_in, B, D, "u_in"), _vec(h_prev, B, D, "h_prev"),
-                                       _vec(u_out, B, D, "u_out"), _blocks(block_prod, "block_prod"),
-                                       _blocks(block_state, "block_state"))
-        views = [_view(t) for t in (a, hh, g, grad_alpha, grad_beta)]
-        rc = L.fss_scan_backward_ex(ctypes.byref(ctx), _DTYPES[dtype], B, T, D,
-                                    *[ctypes.byref(v) for v in views],
-                                    ctypes.byref(state) if state is not None else None)
-    _lib.check(rc, "fss_scan_backward_ex")
+    state = None
+    if not (u_in is None and h_prev is None and u_out is None and block_prod is None and block_state is None):
+        state = _lib.BackwardState(_vec(u_in, B, D, "u_in"), _vec(h_prev, B, D, "h_prev"),
+                                   _vec(u_out, B, D, "u_out"), _blocks(block_prod, "block_prod"),
+                                   _blocks(block_state, "block_state"))
+    _launch_backward(a, hh, g, grad_alpha, grad_beta, _DTYPES[dtype], algo,
+                     _lib.FLAG_CONTINUATION if continuation else 0, state)
 
 
 def _forward(alpha: torch.Tensor, beta: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     _check_tensor("alpha", alpha, None, dtype)
     _check_tensor("beta", beta, alpha, dtype)
     h = torch.empty(alpha.shape, dtype=dtype, device=alpha.device)
-    forward_into(alpha, beta, h)
+    if h.numel():
+        _launch_forward(_rowwise(alpha), _rowwise(beta), h, _DTYPES[dtype], None, 0, None)
     return h
 
 
 def _backward(alpha_saved, h_saved, grad_out, dtype, inplace_grad_beta: bool = False) -> List[torch.Tensor]:
     _check_tensor("alpha_saved", alpha_saved, None, dtype)
+    _check_tensor("h_saved", h_saved, alpha_saved, dtype)
+    _check_tensor("grad_out", grad_out, alpha_saved, dtype)
     grad_alpha = torch.empty(alpha_saved.shape, dtype=dtype, device=alpha_saved.device)
+    if grad_alpha.numel() == 0:
+        return [grad_alpha, torch.empty_like(grad_alpha)]
+    a, g = _rowwise(alpha_saved), _rowwise(grad_out)
     if inplace_grad_beta and h_saved.is_contiguous():
         # grad_beta overwrites h_saved (reference: csrc/sequential_scan_kernel.cu:197 does this
         # unconditionally for bf16).  Only the single-pass kernel can; if the layout sends the
         # call to the chunked kernels the library refuses and a separate buffer is used instead.
         try:
-            backward_into(alpha_saved, h_saved, grad_out, grad_alpha, h_saved)
+            _launch_backward(a, h_saved, g, grad_alpha, h_saved, _DTYPES[dtype], None, 0, None)
             return [grad_alpha, h_saved]
         except _lib.FssError as e:
             if e.code != _lib.E_LAYOUT:
                 raise
     grad_beta = torch.empty(alpha_saved.shape, dtype=dtype, device=alpha_saved.device)
-    backward_into(alpha_saved, h_saved, grad_out, grad_alpha, grad_beta)
+    _launch_backward(a, _rowwise(h_saved), g, grad_alpha, grad_beta, _DTYPES[dtype], None, 0, None)
     return [grad_alpha, grad_beta]
 
 

@@ -58,6 +58,7 @@ extern "C" {
 #define FSS_E_TENSORMAP (-9)  /* the driver refused a TMA descriptor                          */
 #define FSS_E_ARGS (-10)      /* struct_bytes does not match this header                      */
 #define FSS_E_TOO_LARGE (-11) /* problem exceeds a fixed-capacity entry point                 */
+#define FSS_E_ALIAS (-12)     /* an output starts at the address of an input / the other output */
 
 /* values the kernels write to the status word (0 = nothing to report) */
 #define FSS_STATUS_OK 0

@@ -8,7 +8,9 @@ It wraps two native libraries built by ``oracle/build_oracle.py``:
 * ``libfss_oracle.so`` -- the C restatement in ``scan_oracle.c`` of the reference's sequential
   scan (sequential_scan/common.py:46-59) and of its backward
   (csrc/include/sequential_scan_cpu.hpp:36-115);
-* ``_ref/libfss_ref.so`` -- the reference's own C++ loop compiled from its header (optional).
+* ``_ref/libfss_ref.so`` -- the reference's own C++ loop compiled from its header (optional);
+* ``_ref/libfss_refgpu.so`` -- the reference's own CUDA kernels compiled from its headers behind a
+  C ABI (optional; :class:`RefGpu`).
 
 and adds :func:`torch_loop_scan`, the same recurrence written with torch ops so that autograd
 can differentiate it (the way the reference's tests obtain their gradients,
@@ -165,6 +167,46 @@ def reference_values(alpha, beta, grad=None):
     return torch.from_numpy(h), torch.from_numpy(da), torch.from_numpy(db)
 
 
+def reference_values_with_state(alpha, beta, grad=None, h0=None, grad_last=None, h_saved=None):
+    """The fp32 oracle for a scan that starts from the state ``h0`` ([B, D], fp32) instead of from
+    nothing, i.e. the reference's sequential loop (sequential_scan/common.py:51-57) with its carry
+    initialised to ``h0``: ``h_0 = alpha_0*h0 + beta_0``.  Evaluated with the unchanged C oracle on
+    the sequence extended by one leading row ``(alpha=1, beta=h0)``, whose row 0 is ``h0`` itself.
+
+    ``grad_last`` ([B, D]) is an extra gradient for the state after the last row; ``h_saved`` is the
+    stored (possibly rounded) output the gradients should be formed from, as the kernels do
+    (``dalpha_t = dh_t * h_{t-1}`` uses the saved ``h``); default: the oracle's own fp32 ``h``.
+
+    Returns fp32 torch tensors ``(h, h_last, dalpha, dbeta, dh0)``; entries that do not apply are None.
+    """
+    import torch
+    widen = lambda t: (lambda x, is16: widen_bf16(x) if is16 else x)(*_np_of(t))
+    a, b = widen(alpha), widen(beta)
+    B, T, D = a.shape
+    s0 = None if h0 is None else _f32(h0.detach().cpu().float().numpy()).reshape(B, 1, D)
+    if s0 is None:
+        h = scan_forward_f32(a, b)
+    else:
+        a2 = np.concatenate([np.ones((B, 1, D), np.float32), a], axis=1)
+        b2 = np.concatenate([s0, b], axis=1)
+        h = scan_forward_f32(a2, b2)[:, 1:]
+    h = np.ascontiguousarray(h)
+    to_t = lambda x: None if x is None else torch.from_numpy(np.ascontiguousarray(x))
+    if grad is None:
+        return to_t(h), to_t(h[:, -1]), None, None, None
+    g = widen(grad).copy()
+    if grad_last is not None:
+        g[:, -1] += _f32(grad_last.detach().cpu().float().numpy())
+    hs = h if h_saved is None else widen(h_saved)
+    if s0 is None:
+        da, db = scan_backward_f32(a, hs, g)
+        return to_t(h), to_t(h[:, -1]), to_t(da), to_t(db), None
+    hs2 = np.concatenate([s0, hs], axis=1)
+    g2 = np.concatenate([np.zeros((B, 1, D), np.float32), g], axis=1)
+    da2, db2 = scan_backward_f32(a2, hs2, g2)
+    return to_t(h), to_t(h[:, -1]), to_t(da2[:, 1:]), to_t(db2[:, 1:]), to_t(db2[:, 0])
+
+
 def bf16_storage_values(alpha, beta, grad=None, fused: bool = True):
     """What an exact kernel with bf16 storage / fp32 state returns, as bf16 torch tensors."""
     import torch
@@ -295,3 +337,61 @@ class _RefJob:
 
     def __del__(self):
         self.close()
+
+
+class RefGpu:
+    """The reference's own CUDA kernels (``oracle/_ref/libfss_refgpu.so``; launch geometry of
+    csrc/sequential_scan_kernel.cu:7-268) on torch CUDA tensors.  fp32 or bf16, contiguous
+    ``[batch, seq, d_model]`` with d_model in {512, 768, 1024, 1536, 2048}, seq >= 3."""
+
+    WIDTHS = (512, 768, 1024, 1536, 2048)
+
+    def __init__(self):
+        path = _build.build_ref_gpu()
+        if path is None or not Path(path).is_file():
+            raise FileNotFoundError("oracle/_ref/libfss_refgpu.so has not been built")
+        L = ctypes.CDLL(str(path))
+        P = ctypes.c_void_p
+        for name, n in (("fss_refgpu_forward", 3), ("fss_refgpu_backward", 5),
+                        ("fss_refgpu_forward_half", 3), ("fss_refgpu_backward_half", 5)):
+            fn = getattr(L, name)
+            fn.argtypes = [P] * n + [_I, _I, _I, P]
+            fn.restype = ctypes.c_int
+        self.L = L
+
+    @staticmethod
+    def available() -> bool:
+        try:
+            p = _build.build_ref_gpu()
+        except Exception:
+            return False
+        return p is not None and Path(p).is_file()
+
+    @staticmethod
+    def _stream(t):
+        import torch
+        return torch.cuda.current_stream(t.device).cuda_stream
+
+    def forward(self, alpha, beta, out=None):
+        import torch
+        assert alpha.is_cuda and alpha.is_contiguous() and beta.is_contiguous() and alpha.shape == beta.shape
+        out = torch.empty_like(alpha) if out is None else out
+        fn = self.L.fss_refgpu_forward_half if alpha.dtype == torch.bfloat16 else self.L.fss_refgpu_forward
+        rc = fn(alpha.data_ptr(), beta.data_ptr(), out.data_ptr(), *alpha.shape, self._stream(alpha))
+        if rc:
+            raise RuntimeError(f"reference forward kernel refused the call (code {rc}) for shape {tuple(alpha.shape)}")
+        return out
+
+    def backward(self, alpha, h, grad, dalpha=None, dbeta=None):
+        """``(dalpha, dbeta)``; pass ``dbeta=h`` for the reference's own aliasing
+        (csrc/sequential_scan_kernel.cu:197)."""
+        import torch
+        assert alpha.is_cuda and all(t.is_contiguous() and t.shape == alpha.shape for t in (alpha, h, grad))
+        dalpha = torch.empty_like(alpha) if dalpha is None else dalpha
+        dbeta = torch.empty_like(alpha) if dbeta is None else dbeta
+        fn = self.L.fss_refgpu_backward_half if alpha.dtype == torch.bfloat16 else self.L.fss_refgpu_backward
+        rc = fn(alpha.data_ptr(), h.data_ptr(), grad.data_ptr(), dalpha.data_ptr(), dbeta.data_ptr(), *alpha.shape,
+                self._stream(alpha))
+        if rc:
+            raise RuntimeError(f"reference backward kernel refused the call (code {rc}) for shape {tuple(alpha.shape)}")
+        return dalpha, dbeta

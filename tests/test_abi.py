@@ -37,7 +37,7 @@ def test_error_strings_and_argument_checks_need_no_device():
     from fast_sequential_scan_b200 import _lib
     L = _lib.lib()
     assert L.fss_strerror(0) == b"ok"
-    for code in range(-11, 0):
+    for code in range(-12, 0):
         assert L.fss_strerror(code) != b"unknown error code"
     v = _lib.View(0, 0, 0)
     ctx = _lib.ScanCtx(ctypes.sizeof(_lib.ScanCtx), -1, None, None, 0, None, 0, 0)
@@ -53,8 +53,19 @@ def test_error_strings_and_argument_checks_need_no_device():
     buf = (ctypes.c_uint16 * 64)()
     p = _lib.View(ctypes.addressof(buf), 32, 4)                    # row stride 4 < D = 8
     assert call(ctx, 2, 4, 8, p, p, p) == -2
-    ok = _lib.View(ctypes.addressof(buf), 32, 8)
-    assert call(ctx, 2, 4, 8, ok, ok, ok) == -4                    # no workspace
+    ok = [_lib.View(ctypes.addressof(buf) + 128 * k, 32, 8) for k in range(3)]
+    assert call(ctx, 2, 4, 8, *ok) == -4                           # no workspace
+    assert call(ctx, 2, 4, 8, ok[0], ok[1], ok[0]) == -12          # h starts where alpha starts
+    assert call(ctx, 2, 4, 8, ok[0], ok[1], ok[1]) == -12          # ... or where beta starts
+    # the chunked kernels run on a linear grid of (channel blocks x chunks x batch) CTAs; a problem
+    # whose grid would not fit 31 bits is refused instead of being launched with a truncated grid
+    T, D = 1 << 34, 1 << 14
+    huge = [_lib.View(ctypes.addressof(buf) + 128 * k, T * D, D) for k in range(3)]
+    ctx.algo = _lib.ALGO_CHUNKED
+    assert call(ctx, 64, T, D, *huge) == -2
+    ctx.algo = 0
+    wide = _lib.View(ctypes.addressof(buf), 1 << 62, 8)            # batch stride whose extent overflows
+    assert call(ctx, 16, 4, 8, wide, ok[1], ok[2]) == -2
     assert L.fss_workspace_bytes(8, 2048, 1024, 0) > 256
     assert L.fss_workspace_bytes(0, 0, 0, 0) >= 256
     assert L.fss_block_rows(0, 1, 65536, 4096, 1) >= 1

@@ -1,8 +1,10 @@
 """Two-GPU (NCCL) run of the sequence-parallel scan; skipped on boxes with fewer than 2 GPUs.
 
-Each rank holds half of the rows, runs ``seqpar_scan`` (local zero-state scan, all-gather of the
-carries over NCCL, re-scan of the blocks the carry reaches) forward and backward; rank 0 also
-computes the undivided scan on its own GPU, and both are compared with the bf16 parity bound.
+Each rank holds its share of the rows and runs ``seqpar_scan`` (local zero-state scan, all-gather
+of the carries over NCCL, re-scan of the blocks the carry reaches) forward and backward.  Every
+rank then checks its rows of h, dalpha and dbeta against the CPU checker's undivided scan of the
+whole sequence at the bf16 parity bound |x - ref| <= 1e-2 + 1e-2*|ref| (gradients formed from the
+h the ranks stored, as the kernels do).
 """
 import os
 import socket
@@ -37,15 +39,17 @@ def _worker(rank, world, port, out_dir):
         h = fd.seqpar_scan(al, bl)
         h.backward(g[:, rows].cuda())
         pkg.check_status()
-        # the undivided scan on this rank's own GPU
-        af = a.cuda().requires_grad_(True)
-        bf = b.cuda().requires_grad_(True)
-        hf = pkg.scan_cu(af, bf)
-        hf.backward(g.cuda())
+        # the CPU checker on the whole, undivided sequence (every rank computes it for itself)
+        from oracle import oracle
+        h_ref, _, _ = oracle.reference_values(a, b, None)
+        h_all = [torch.empty_like(h) for _ in range(world)]
+        dist.all_gather(h_all, h.detach().contiguous())
+        h_saved = torch.cat(h_all, dim=1).cpu()
+        da_ref, db_ref = (torch.from_numpy(x) for x in oracle.scan_backward_f32(
+            a.float().numpy(), h_saved.float().numpy(), g.float().numpy()))
         ok = True
-        for got, ref in ((h, hf[:, rows]), (al.grad, af.grad[:, rows]), (bl.grad, bf.grad[:, rows])):
-            err = (got.float() - ref.float()).abs()
-            ok = ok and bool((err <= 2e-2 + 2e-2 * ref.float().abs()).all())   # two bf16 results compared
+        for got, ref in ((h, h_ref[:, rows]), (al.grad, da_ref[:, rows]), (bl.grad, db_ref[:, rows])):
+            ok = ok and oracle.mixed_error_ratio(got, ref, 1e-2) <= 1.0
         Path(out_dir, f"rank{rank}.{'ok' if ok else 'bad'}").write_text("x")
     finally:
         dist.destroy_process_group()

@@ -55,6 +55,20 @@ def assert_parity(got, ref, tol, what):
     assert r <= 1.0, f"{what}: max |x-ref|/(tol+tol|ref|) = {r:.3f} at tol {tol}"
 
 
+def assert_same_up_to_association(x, y, what):
+    """Two launches of the single-pass kernels on the same values may resolve a tile's entering state
+    from its predecessor's inclusive state or from a fold of aggregates, whichever is published
+    first; the two associate differently, so the fp32 state can differ in its last bits.  Results of
+    separate launches are therefore compared as: a few ulp of the I/O type, and (rare) differing
+    elements only.  Bit equality is asserted nowhere across launches."""
+    assert x.shape == y.shape and x.dtype == y.dtype, what
+    xf, yf = x.detach().float(), y.detach().float()
+    eps = 2.0 ** -7 if x.dtype == torch.bfloat16 else 2.0 ** -22          # 2 ulp (bf16) / 4 ulp (fp32)
+    bound = eps * torch.maximum(xf.abs(), yf.abs()) + (1e-30 if x.dtype == torch.bfloat16 else 1e-7)
+    bad = (xf - yf).abs() > bound
+    assert not bool(bad.any()), f"{what}: {int(bad.sum())} elements differ by more than the association bound"
+
+
 @pytest.mark.parametrize("algo", ALGOS)
 @pytest.mark.parametrize("name", golden_cases())
 def test_golden_vectors(name, algo):
@@ -114,16 +128,33 @@ def test_strided_views_channel_shards(algo):
     b = torch.randn(full, generator=gen).bfloat16().cuda()
     g = torch.randn(full, generator=gen).bfloat16().cuda()
     h_full, da_full, db_full = run_native(a, b, g, algo)
+    h_ref, _, _ = oracle.reference_values(a, b, None)
+    da_ref, db_ref = (torch.from_numpy(x) for x in oracle.scan_backward_f32(
+        a.float().cpu().numpy(), h_full.float().cpu().numpy(), g.float().cpu().numpy()))
     for lo, hi in [(0, 128), (128, 256), (64, 72)]:
         h, da, db = run_native(a[..., lo:hi], b[..., lo:hi], g[..., lo:hi], algo)
-        assert torch.equal(h, h_full[..., lo:hi])
-        assert torch.equal(da, da_full[..., lo:hi]) and torch.equal(db, db_full[..., lo:hi])
+        # every shard against the oracle on its own channels (channels are independent) ...
+        assert_parity(h, h_ref[..., lo:hi], BF16_TOL, f"h[{lo}:{hi}]")
+        assert_parity(db, db_ref[..., lo:hi], BF16_TOL, f"dbeta[{lo}:{hi}]")
+        assert_parity(da, da_ref[..., lo:hi], BF16_TOL, f"dalpha[{lo}:{hi}]")
+        # ... and against the unsharded launch (other tile geometry, so not bit for bit)
+        assert_same_up_to_association(h, h_full[..., lo:hi].contiguous(), "shard h")
+        assert_same_up_to_association(db, db_full[..., lo:hi].contiguous(), "shard dbeta")
 
 
 # ---- the reference's own test grid and metric (sequential_scan/test_scan_cuda.py:27-124) ----
-@pytest.mark.parametrize("bs", [2, 9])
-@pytest.mark.parametrize("sq", [128, 1024])
-@pytest.mark.parametrize("d", [512, 768, 1024])
+# fp32: bs {9, 10, 12, 2} x sq {128, 256, 512, 1024} x d {512, 768, 1024} (test_scan_cuda.py:27-29, 44-46);
+# bf16: five batch sizes drawn from [1, 16) x the same sq x d (:80-82, 97-99).  The reference draws them
+# from an unseeded NumPy generator; here the draw is seeded so that the cases are the same in every run.
+REF_BS_SINGLE = [9, 10, 12, 2]
+REF_BS_HALF = sorted(set(int(x) for x in np.random.RandomState(0).randint(1, 16, size=5)))
+REF_SQ = [128, 256, 512, 1024]
+REF_D = [512, 768, 1024]
+
+
+@pytest.mark.parametrize("bs", REF_BS_SINGLE)
+@pytest.mark.parametrize("sq", REF_SQ)
+@pytest.mark.parametrize("d", REF_D)
 def test_reference_grid_single(bs, sq, d):
     pkg, _, _ = _mods()
     torch.manual_seed(0)
@@ -138,9 +169,9 @@ def test_reference_grid_single(bs, sq, d):
         assert oracle.digits(err) >= 7, (what, err)      # SINGLE_TOL = 7 digits
 
 
-@pytest.mark.parametrize("bs", [1, 7, 15])
-@pytest.mark.parametrize("sq", [128, 512])
-@pytest.mark.parametrize("d", [512, 768, 1024])
+@pytest.mark.parametrize("bs", REF_BS_HALF)
+@pytest.mark.parametrize("sq", REF_SQ)
+@pytest.mark.parametrize("d", REF_D)
 def test_reference_grid_half(bs, sq, d):
     pkg, _, _ = _mods()
     torch.manual_seed(0)
@@ -181,6 +212,13 @@ def test_benchmark_configurations(cfg, algo):
     from fast_sequential_scan_b200.workloads import CONFIGS, make_inputs
     w = CONFIGS[cfg]
     a, b, g = make_inputs(w, device="cuda", seed=0)
+    if algo == "auto":
+        # "auto" falls back to the chunked kernels on a layout the single-pass kernels cannot take;
+        # every benchmark configuration must be eligible, so ask for them explicitly (this raises
+        # FssError(FSS_E_LAYOUT) instead of falling back)
+        _, native, _lib = _mods()
+        assert native.tma_eligible(a, b, g)
+        algo = "lookback"
     h, da, db = run_native(a, b, g, algo)
     tol = BF16_TOL if w.dtype == "bf16" else F32_TOL
     _subset_check(w, a, b, g, h, da, db, tol)
@@ -281,12 +319,22 @@ def test_memory_saving_backward_modes(shape, fp32, mode):
     assert torch.equal(h_ref, h_ref_keep)                   # default mode leaves the output alone
     h, h_keep, da, db = run(mode)
     pkg.check_status()
-    assert torch.equal(h_keep, h_ref_keep)
-    assert torch.equal(da, da_ref) and torch.equal(db, db_ref)
+    # both modes against the oracle (gradients formed from the h each run saved) ...
+    tol = F32_TOL if fp32 else BF16_TOL
+    o_h, _, _ = oracle.reference_values(a0, b0, None)
+    assert_parity(h_keep, o_h, tol, f"{mode} h")
+    o_da, o_db = (torch.from_numpy(x) for x in oracle.scan_backward_f32(
+        a0.float().cpu().numpy(), h_keep.float().cpu().numpy(), g.float().cpu().numpy()))
+    assert_parity(da, o_da, tol, f"{mode} dalpha")
+    assert_parity(db, o_db, tol, f"{mode} dbeta")
+    # ... and against the default mode: the same kernels on the same values, equal up to the
+    # association of the look-back (separate launches are never compared bit for bit)
+    assert_same_up_to_association(h_keep, h_ref_keep, "h")
+    assert_same_up_to_association(db, db_ref, "dbeta")
     if mode == "inplace" and native.tma_eligible(a0, b0, g):
-        assert torch.equal(h.detach(), db_ref)              # h's storage now holds grad_beta
+        assert h.detach().data_ptr() == db.data_ptr()       # h's storage now holds grad_beta
     if mode == "recompute":
-        assert torch.equal(h.detach(), h_ref_keep)          # the returned output was never touched
+        assert torch.equal(h.detach(), h_keep)              # the returned output was never touched
 
 
 def test_inplace_grad_beta_through_the_c_abi():
@@ -307,9 +355,21 @@ def test_inplace_grad_beta_through_the_c_abi():
         native.backward_into(a, h2, g, da, h2, algo=_algo_id("chunked"))
     assert err.value.code == _lib.E_LAYOUT and torch.equal(h2, h)
     native.backward_into(a, h2, g, da, h2, algo=_algo_id("lookback"))
-    assert torch.equal(da, da_ref) and torch.equal(h2, db_ref)
+    o_da, o_db = (torch.from_numpy(x) for x in oracle.scan_backward_f32(
+        a.float().cpu().numpy(), h.float().cpu().numpy(), g.float().cpu().numpy()))
+    assert_parity(da, o_da, BF16_TOL, "dalpha, grad_beta written over h")
+    assert_parity(h2, o_db, BF16_TOL, "dbeta written over h")
+    assert_same_up_to_association(h2, db_ref, "dbeta over h vs separate buffer")
     got = native.scan_backward_half(a, h.clone(), g, inplace_grad_beta=True)
-    assert torch.equal(got[0], da_ref) and torch.equal(got[1], db_ref)
+    assert_parity(got[0], o_da, BF16_TOL, "dalpha (tensor-level entry)")
+    assert_parity(got[1], o_db, BF16_TOL, "dbeta (tensor-level entry)")
+    # aliasing the library does not accept: an output that starts where an input starts
+    with pytest.raises(_lib.FssError) as err:
+        native.forward_into(a, b, a)
+    assert err.value.code == -12
+    with pytest.raises(_lib.FssError) as err:
+        native.backward_into(a, h, g, a, db_ref)
+    assert err.value.code == -12
 
 
 @pytest.mark.parametrize("fp32", [False, True])
@@ -354,9 +414,16 @@ def test_gated_scan_gradients_and_state():
     pkg.scan_cu_single(a, b).backward(g)
     for got, ref, name in zip(leaves, ref_leaves, "r i x lam".split()):
         assert_parity(got.grad.cpu(), ref.grad.cpu(), 1e-4, f"d{name}")
-    # two halves with h_last -> h_in equal one pass
-    h_full = torch.empty_like(r)
-    native.forward_gated_into(r, i, x, lam, h_full)
+    # boundary state of the gated entry point against the oracle: the float64 gate formulas rounded
+    # once, scanned by the oracle from a non-zero h0; and two halves chained through h_last -> h_in
+    a_ref, b_ref = oracle.gated_alpha_beta(r.cpu(), i.cpu(), x.cpu(), lam.cpu())
+    h0 = torch.randn(r.shape[0], r.shape[2], generator=torch.Generator().manual_seed(2)).cuda()
+    h_c = torch.empty_like(r)
+    last_c = torch.empty_like(h0)
+    native.forward_gated_into(r, i, x, lam, h_c, continuation=True, h_in=h0, h_last=last_c)
+    o_h, o_last, _, _, _ = oracle.reference_values_with_state(a_ref, b_ref, None, h0)
+    assert_parity(h_c.cpu(), o_h, 1e-4, "gated scan from h0")
+    assert_parity(last_c.cpu(), o_last, 1e-4, "gated scan: state after the last row")
     half = r.shape[1] // 2
     h_a, h_b = torch.empty_like(r[:, :half]), torch.empty_like(r[:, half:])
     last = torch.empty(r.shape[0], r.shape[2], device="cuda")
@@ -364,7 +431,8 @@ def test_gated_scan_gradients_and_state():
     native.forward_gated_into(r[:, half:].contiguous(), i[:, half:].contiguous(), x[:, half:].contiguous(), lam, h_b,
                               continuation=True, h_in=last)
     pkg.check_status()
-    assert_parity(torch.cat([h_a, h_b], 1).cpu(), h_full.cpu(), 1e-5, "continued gated scan")
+    o_full, _, _ = oracle.reference_values(a_ref, b_ref, None)
+    assert_parity(torch.cat([h_a, h_b], 1).cpu(), o_full, 1e-4, "continued gated scan")
 
 
 @pytest.mark.parametrize("shape", [(4, 4096, 2048), (2, 8192, 1024), (1, 16384, 512)])
@@ -380,8 +448,7 @@ def test_lookback_descriptors_survive_reuse_with_different_data(shape):
     for _ in range(3):
         a = (0.5 + 0.499 * torch.rand(shape, generator=gen, device="cuda")).bfloat16()
         b = (torch.randn(shape, generator=gen, device="cuda") * 3).bfloat16()
-        ref = torch.empty_like(a)
-        native.forward_into(a, b, ref, algo=_lib.ALGO_CHUNKED)
+        ref, _, _ = oracle.reference_values(a, b, None)          # the CPU checker, not another kernel
         sets.append((a, b, ref))
     h = torch.empty_like(sets[0][0])
     for it in range(24):
@@ -445,21 +512,158 @@ def test_sequence_parallel_pieces_on_one_gpu(dtype, algo):
     pkg.check_status()
 
 
-def test_boundary_state_vectors_continue_a_scan():
-    """h_in / h_last / u_in / u_out: scanning two halves with the state handed over equals one scan."""
+@pytest.mark.parametrize("algo", ["chunked", "lookback"])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("shape", [(2, 1000, 128), (3, 257, 264), (2, 70, 7)])
+def test_boundary_state_vectors_against_the_oracle(shape, dtype, algo):
+    """h_in / h_last (forward) and u_in / h_prev / u_out (backward) through the C ABI against the
+    oracle started from the same state (sequential_scan/common.py:51-57 with its carry initialised
+    to h_in), on layouts both kernel families take and on one only the chunked kernels take."""
     _, native, _lib = _mods()
-    gen = torch.Generator(device="cuda").manual_seed(5)
-    B, T, D = 2, 1000, 128
-    a = torch.rand(B, T, D, generator=gen, device="cuda") * 0.5 + 0.5
-    b = torch.randn(B, T, D, generator=gen, device="cuda")
-    for algo in ("chunked", "auto"):
-        full = torch.empty_like(a)
-        native.forward_into(a, b, full, algo=_algo_id(algo))
-        h1, h2 = torch.empty_like(a[:, :400]), torch.empty_like(a[:, 400:])
-        last = torch.empty(B, D, device="cuda")
-        native.forward_into(a[:, :400], b[:, :400], h1, algo=_algo_id(algo), h_last=last)
-        native.forward_into(a[:, 400:], b[:, 400:], h2, algo=_algo_id(algo), continuation=True, h_in=last)
-        assert torch.allclose(torch.cat([h1, h2], 1), full, rtol=1e-5, atol=1e-5), algo
+    dt = torch.bfloat16 if dtype == "bf16" else torch.float32
+    tol = BF16_TOL if dtype == "bf16" else F32_TOL
+    B, T, D = shape
+    gen = torch.Generator().manual_seed(5)
+    a = (torch.rand(shape, generator=gen) * 0.5 + 0.5).to(dt).cuda()
+    b = torch.randn(shape, generator=gen).to(dt).cuda()
+    g = torch.randn(shape, generator=gen).to(dt).cuda()
+    h0 = torch.randn(B, D, generator=gen).cuda()
+    g_last = torch.randn(B, D, generator=gen).cuda()
+    if algo == "lookback" and not native.tma_eligible(a, b, g):
+        pytest.skip("layout not eligible for the single-pass kernels")
+    h = torch.empty_like(a)
+    h_last = torch.empty(B, D, device="cuda")
+    native.forward_into(a, b, h, algo=_algo_id(algo), continuation=True, h_in=h0, h_last=h_last)
+    da, db = torch.empty_like(a), torch.empty_like(a)
+    u_out = torch.empty(B, D, device="cuda")
+    native.backward_into(a, h, g, da, db, algo=_algo_id(algo), continuation=True, u_in=g_last, h_prev=h0, u_out=u_out)
+    import fast_sequential_scan_b200 as pkg
+    pkg.check_status()
+    o_h, o_last, o_da, o_db, o_dh0 = oracle.reference_values_with_state(a, b, g, h0, g_last, h_saved=h)
+    assert_parity(h, o_h, tol, "h from h_in")
+    assert_parity(h_last, o_last, tol, "h_last")
+    assert_parity(db, o_db, tol, "dbeta with u_in")
+    assert_parity(da, o_da, tol, "dalpha with h_prev")
+    assert_parity(u_out, o_dh0, tol, "u_out")
+    # two pieces chained through the state vectors equal the undivided scan of the oracle
+    cut = T // 3 + 1
+    h1, h2 = torch.empty_like(a[:, :cut]), torch.empty_like(a[:, cut:])
+    mid = torch.empty(B, D, device="cuda")
+    native.forward_into(a[:, :cut], b[:, :cut], h1, algo=_algo_id(algo), h_last=mid)
+    native.forward_into(a[:, cut:], b[:, cut:], h2, algo=_algo_id(algo), continuation=True, h_in=mid)
+    o_plain, _, _ = oracle.reference_values(a, b, None)
+    assert_parity(torch.cat([h1, h2], 1), o_plain, tol, "two chained pieces")
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("reverse", [False, True])
+def test_initial_and_final_state_on_the_autograd_api(dtype, reverse):
+    """scan_cu(alpha, beta, h0=..., return_final_state=True, reverse=...): values and all four
+    gradients (alpha, beta, h0, through h and through the returned final state) against the oracle."""
+    pkg, _, _ = _mods()
+    fn = pkg.scan_cu if dtype == "bf16" else pkg.scan_cu_single
+    dt = torch.bfloat16 if dtype == "bf16" else torch.float32
+    tol = BF16_TOL if dtype == "bf16" else F32_TOL
+    B, T, D = 3, 777, 256
+    gen = torch.Generator().manual_seed(17)
+    a = (torch.rand(B, T, D, generator=gen) * 0.6 + 0.4).to(dt).cuda().requires_grad_()
+    b = torch.randn(B, T, D, generator=gen).to(dt).cuda().requires_grad_()
+    g = torch.randn(B, T, D, generator=gen).to(dt).cuda()
+    h0 = torch.randn(B, D, generator=gen).cuda().requires_grad_()
+    g_last = torch.randn(B, D, generator=gen).cuda()
+    h, h_last = fn(a, b, h0=h0, return_final_state=True, reverse=reverse)
+    assert h.dtype == dt and h_last.dtype == torch.float32 and h_last.shape == (B, D)
+    torch.autograd.backward((h, h_last), (g, g_last))
+    pkg.check_status()
+    flip = (lambda t: t.flip(1)) if reverse else (lambda t: t)
+    o = oracle.reference_values_with_state(flip(a.detach()), flip(b.detach()), flip(g), h0.detach(), g_last,
+                                           h_saved=flip(h.detach()))
+    o_h, o_last, o_da, o_db, o_dh0 = o
+    assert_parity(flip(h.detach()), o_h, tol, "h")
+    assert_parity(h_last, o_last, tol, "final state")
+    assert_parity(flip(b.grad), o_db, tol, "dbeta")
+    assert_parity(flip(a.grad), o_da, tol, "dalpha")
+    assert_parity(h0.grad, o_dh0, tol, "dh0")
+    # only the final state requested, no h0: the plain first-row rule
+    h2, last2 = fn(a.detach(), b.detach(), return_final_state=True, reverse=reverse)
+    o2, o2_last, _, _, _ = oracle.reference_values_with_state(flip(a.detach()), flip(b.detach()))
+    assert_parity(flip(h2), o2, tol, "h (no h0)")
+    assert_parity(last2, o2_last, tol, "final state (no h0)")
+
+
+@pytest.mark.parametrize("algo", ["chunked", "lookback"])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("shape", [(2, 100, 72), (2, 333, 264), (1, 65, 520), (3, 50, 7)])
+def test_outputs_stay_inside_their_views(shape, dtype, algo):
+    """Output canaries: h, grad_alpha and grad_beta are strided views inside sentinel-filled buffers
+    (extra rows before and after, extra channels on both sides; d_model not a multiple of the tile
+    width, seq not a multiple of the tile height, odd d_model for the chunked family).  After forward
+    and backward every sentinel byte must be untouched and the views must hold the oracle's values."""
+    _, native, _lib = _mods()
+    dt = torch.bfloat16 if dtype == "bf16" else torch.float32
+    tol = BF16_TOL if dtype == "bf16" else F32_TOL
+    B, T, D = shape
+    pad_c = 8 if D % 8 == 0 else 3            # keeps 16-byte alignment when D allows the TMA path
+    gen = torch.Generator().manual_seed(23)
+    a = torch.sigmoid(torch.randn(shape, generator=gen)).to(dt).cuda()
+    b = torch.randn(shape, generator=gen).to(dt).cuda()
+    g = torch.randn(shape, generator=gen).to(dt).cuda()
+    sentinel = -12345.0 if dtype == "f32" else -12352.0      # exactly representable in bf16
+
+    def framed():
+        buf = torch.full((B, T + 4, D + 2 * pad_c), sentinel, dtype=dt, device="cuda")
+        return buf, buf[:, 2:T + 2, pad_c:pad_c + D]
+
+    (hb, h), (dab, da), (dbb, db) = framed(), framed(), framed()
+    if algo == "lookback" and not native.tma_eligible(a, b, g, h):
+        pytest.skip("layout not eligible for the single-pass kernels")
+    native.forward_into(a, b, h, algo=_algo_id(algo))
+    native.backward_into(a, h, g, da, db, algo=_algo_id(algo))
+    import fast_sequential_scan_b200 as pkg
+    pkg.check_status()
+    for name, buf, view in (("h", hb, h), ("grad_alpha", dab, da), ("grad_beta", dbb, db)):
+        frame = torch.ones_like(buf, dtype=torch.bool)
+        frame[:, 2:T + 2, pad_c:pad_c + D] = False
+        assert bool((buf[frame] == sentinel).all()), f"{name}: a kernel wrote outside its view"
+        assert not bool((view == sentinel).any()), f"{name}: part of the view was never written"
+    o_h, _, _ = oracle.reference_values(a, b, None)
+    assert_parity(h, o_h, tol, "h")
+    o_da, o_db = (torch.from_numpy(x) for x in oracle.scan_backward_f32(
+        a.float().cpu().numpy(), h.float().cpu().numpy(), g.float().cpu().numpy()))
+    assert_parity(db, o_db, tol, "dbeta")
+    assert_parity(da, o_da, tol, "dalpha")
+
+
+def test_launches_on_two_streams_are_ordered_and_correct():
+    """A single-pass launch needs all its CTAs resident at once, so two of them must not be placed
+    on the device at the same time.  The host layer orders launches that go to different streams of
+    one device (each stream has its own workspace); here two streams alternate without any
+    synchronisation by the caller, and every result is checked against the oracle."""
+    pkg, native, _lib = _mods()
+    gen = torch.Generator().manual_seed(41)
+    shape = (4, 4096, 1024)
+    sets = []
+    for k in range(2):
+        a = (0.5 + 0.499 * torch.rand(shape, generator=gen)).bfloat16().cuda()
+        b = torch.randn(shape, generator=gen).bfloat16().cuda()
+        g = torch.randn(shape, generator=gen).bfloat16().cuda()
+        sets.append(dict(a=a, b=b, g=g, h=torch.empty_like(a), da=torch.empty_like(a), db=torch.empty_like(a)))
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for it in range(6):
+        for k in (0, 1):
+            x = sets[k]
+            with torch.cuda.stream(streams[k]):
+                native.forward_into(x["a"], x["b"], x["h"], algo=_lib.ALGO_LOOKBACK)
+                native.backward_into(x["a"], x["h"], x["g"], x["da"], x["db"], algo=_lib.ALGO_LOOKBACK)
+    pkg.check_status()                 # synchronises the device; raises if any bounded wait ran out
+    for k, x in enumerate(sets):
+        o_h, _, _ = oracle.reference_values(x["a"], x["b"], None)
+        assert_parity(x["h"], o_h, BF16_TOL, f"stream {k}: h")
+        o_da, o_db = (torch.from_numpy(v) for v in oracle.scan_backward_f32(
+            x["a"].float().cpu().numpy(), x["h"].float().cpu().numpy(), x["g"].float().cpu().numpy()))
+        assert_parity(x["db"], o_db, BF16_TOL, f"stream {k}: dbeta")
+        assert_parity(x["da"], o_da, BF16_TOL, f"stream {k}: dalpha")
 
 
 def test_bounded_waits_give_up_report_and_recover():

@@ -16,6 +16,7 @@ LIB_PATH = PKG / "libfss_b200.so"
 DTYPE_BF16, DTYPE_F32 = 0, 1
 ALGO_AUTO, ALGO_CHUNKED, ALGO_LOOKBACK = 0, 1, 2
 FLAG_CONTINUATION = 1
+FLAG_DETERMINISTIC = 2
 E_LAYOUT = -5      # FSS_E_LAYOUT
 FLAG_TEST_SHORT_WAITS, FLAG_TEST_MUTE_FIRST_BLOCK = 0x100, 0x200
 
@@ -66,6 +67,10 @@ SIGNATURES = {
                              + [_P(BackwardState)]),
     "fss_scan_forward_gated": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View),
                                        c_void_p, _P(View), _P(ForwardState)]),
+    "fss_gates_forward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View),
+                                  c_void_p, _P(View), _P(View)]),
+    "fss_gates_backward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View),
+                                   c_void_p] + [_P(View)] * 5 + [c_void_p]),
     "fss_block_rows": (c_int64, [c_int, c_int64, c_int64, c_int64, c_int]),
     "fss_seqpar_compose": (c_int, [_P(ScanCtx), c_int, c_int, c_int, c_int64, c_void_p, c_void_p]),
     "fss_seqpar_fixup_forward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View),

@@ -7,6 +7,7 @@
 
 #include "fss_chunked.cuh"
 #include "fss_common.cuh"
+#include "fss_gates.cuh"
 #include "fss_lookback.cuh"
 #include "fss_seqpar.cuh"
 
@@ -150,7 +151,8 @@ static int forward_typed(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t 
                          const fss_forward_state *st) {
     int algo = ctx->algo;
     if (algo != FSS_ALGO_CHUNKED) {
-        const bool ok = lookback::layout_ok<T>(B, Tn, D, {alpha, beta, h});
+        const bool ok = lookback::layout_ok<T>(B, Tn, D, {alpha, beta, h}) &&
+                        (!st || lookback::state_aligned({st->h_in, st->h_last, st->prod, st->block_prod, st->block_state}));
         if (!ok && algo == FSS_ALGO_LOOKBACK) return FSS_E_LAYOUT;
         algo = ok ? FSS_ALGO_LOOKBACK : FSS_ALGO_CHUNKED;
     }
@@ -176,7 +178,8 @@ static int backward_typed(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t
     const bool inplace = dbeta->ptr == h->ptr;
     if (inplace && (dbeta->stride_b != h->stride_b || dbeta->stride_t != h->stride_t)) return FSS_E_LAYOUT;
     if (algo != FSS_ALGO_CHUNKED) {
-        const bool ok = lookback::layout_ok<T>(B, Tn, D, {alpha, h, grad, dalpha, dbeta});
+        const bool ok = lookback::layout_ok<T>(B, Tn, D, {alpha, h, grad, dalpha, dbeta}) &&
+                        (!st || lookback::state_aligned({st->u_in, st->h_prev, st->u_out, st->block_prod, st->block_state}));
         if (!ok && algo == FSS_ALGO_LOOKBACK) return FSS_E_LAYOUT;
         algo = ok ? FSS_ALGO_LOOKBACK : FSS_ALGO_CHUNKED;
     }
@@ -223,7 +226,9 @@ FSS_API size_t fss_workspace_bytes(int64_t B, int64_t T, int64_t D, int dtype) {
     if (B <= 0 || T <= 0 || D <= 0) return workspace_total(0);
     size_t a = chunked::workspace_bytes(B, T, D);
     size_t b = lookback::workspace_bytes(B, T, D, dtype);
-    return workspace_total(a > b ? a : b);
+    size_t c = lookback::float_scratch_bytes(B, T, D);
+    if (b > a) a = b;
+    return workspace_total(a > c ? a : c);
 }
 
 FSS_API int fss_workspace_init(void *workspace, size_t bytes, void *stream) {
@@ -270,6 +275,7 @@ FSS_API int fss_scan_forward_gated(const fss_scan_ctx *ctx, int dtype, int64_t B
     if (same_start(h, r) || same_start(h, i) || same_start(h, x)) return FSS_E_ALIAS;
     if (state && (state->prod || state->block_prod || state->block_state)) return FSS_E_ARGS;
     if (ctx->algo == FSS_ALGO_CHUNKED) return FSS_E_LAYOUT;       // single-pass kernel only
+    if (state && !lookback::state_aligned({state->h_in, state->h_last})) return FSS_E_LAYOUT;
     if ((rc = need_workspace(ctx, B, T, D, dtype))) return rc;
     DeviceGuard guard(ctx->device);
     if (guard.error) return guard.error;
@@ -343,15 +349,6 @@ FSS_API int fss_seqpar_compose(const fss_scan_ctx *ctx, int backward, int world,
 }
 
 namespace fss {
-static seqpar::Geometry fixup_geometry(int64_t B, int64_t T, int64_t D, int64_t R, int V) {
-    seqpar::Geometry g;
-    g.B = B; g.T = T; g.D = D; g.R = R;
-    g.NB = ceil_div(T, R);
-    g.nvec = D / V;
-    g.vblocks = ceil_div(g.nvec, 32);
-    return g;
-}
-
 // multiprocessors of the current device (cached per device; 148 if the query fails)
 static int sm_count() {
     static int cached[64] = {0};
@@ -364,12 +361,25 @@ static int sm_count() {
     return cached[dev];
 }
 
+static seqpar::Geometry fixup_geometry(int64_t B, int64_t T, int64_t D, int64_t R, int V) {
+    seqpar::Geometry g;
+    g.B = B; g.T = T; g.D = D; g.R = R;
+    g.NB = ceil_div(T, R);
+    g.nvec = D / V;
+    g.vblocks = ceil_div(g.nvec, 32);
+    g.slots = seqpar::choose_slots(g.NB, g.vblocks, B, sm_count());
+    return g;
+}
+static bool fixup_grid_ok(const seqpar::Geometry &g) { return g.vblocks <= 65535 && g.B <= 65535; }
+
 template <typename T, int V>
 static int fixup_forward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *alpha,
                                 const fss_view *beta, const fss_view *h, const float *carry_in, const float *bp,
                                 const float *bs, int64_t R) {
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
-    seqpar::fixup_forward<T, V><<<seqpar::fixup_grid(g, sm_count()), seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
+    if (!fixup_grid_ok(g)) return FSS_E_SHAPE;
+    const dim3 grid((unsigned)g.slots, (unsigned)g.vblocks, (unsigned)B);
+    seqpar::fixup_forward<T, V><<<grid, seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
         g, make_view<const T>(alpha), make_view<const T>(beta), make_view<T>(h), carry_in, bp, bs);
     return launch_check("seqpar forward fix-up launch");
 }
@@ -379,7 +389,9 @@ static int fixup_backward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn,
                                  const fss_view *h, const fss_view *grad, const fss_view *da, const fss_view *db,
                                  const float *u_in, const float *h_prev, const float *bp, const float *bs, int64_t R) {
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
-    seqpar::fixup_backward<T, V><<<seqpar::fixup_grid(g, sm_count()), seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
+    if (!fixup_grid_ok(g)) return FSS_E_SHAPE;
+    const dim3 grid((unsigned)g.slots, (unsigned)g.vblocks, (unsigned)B);
+    seqpar::fixup_backward<T, V><<<grid, seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
         g, make_view<const T>(alpha), make_view<const T>(h), make_view<const T>(grad), make_view<T>(da),
         make_view<T>(db), u_in, h_prev, bp, bs, (ctx->flags & FSS_FLAG_CONTINUATION) != 0);
     return launch_check("seqpar backward fix-up launch");
@@ -431,4 +443,73 @@ FSS_API int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_
         return chunked::vector_ok<bf16>(D, {alpha, h, grad_out, grad_alpha, grad_beta}) ? FSS_FIXB(bf16, 8) : FSS_FIXB(bf16, 1);
     return chunked::vector_ok<float>(D, {alpha, h, grad_out, grad_alpha, grad_beta}) ? FSS_FIXB(float, 4) : FSS_FIXB(float, 1);
 #undef FSS_FIXB
+}
+
+// ---------------------------------------------------------------------- gates outside the scan
+namespace fss {
+template <typename T, int V>
+static int gates_forward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *r,
+                                const fss_view *i, const fss_view *x, const float *lambda, const fss_view *alpha,
+                                const fss_view *beta) {
+    const dim3 grid((unsigned)ceil_div(D / V, gates::kThreads), (unsigned)ceil_div(Tn, gates::kRowsPerCta), (unsigned)B);
+    const fss_view *bv = beta ? beta : alpha;
+    gates::materialize<T, V><<<grid, gates::kThreads, 0, (cudaStream_t)ctx->stream>>>(
+        B, Tn, D, make_view<const T>(r), make_view<const T>(i ? i : r), make_view<const T>(x ? x : r), lambda,
+        make_view<T>(alpha), make_view<T>(bv), beta != nullptr);
+    return launch_check("gate launch");
+}
+template <typename T, int V>
+static int gates_backward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *r,
+                                 const fss_view *i, const fss_view *x, const float *lambda, const fss_view *da,
+                                 const fss_view *db, const fss_view *dr, const fss_view *di, const fss_view *dx,
+                                 float *dlambda) {
+    const dim3 grid((unsigned)ceil_div(D / V, gates::kThreads), (unsigned)ceil_div(Tn, gates::kRowsPerCta), (unsigned)B);
+    gates::backward<T, V><<<grid, gates::kThreads, 0, (cudaStream_t)ctx->stream>>>(
+        B, Tn, D, make_view<const T>(r), make_view<const T>(i), make_view<const T>(x), lambda, make_view<const T>(da),
+        make_view<const T>(db), make_view<T>(dr), make_view<T>(di), make_view<T>(dx), dlambda);
+    return launch_check("gate backward launch");
+}
+static bool gate_grid_ok(int64_t B, int64_t Tn) { return B <= 65535 && ceil_div(Tn, gates::kRowsPerCta) <= 65535; }
+}  // namespace fss
+
+FSS_API int fss_gates_forward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                              const fss_view *r, const fss_view *i, const fss_view *x, const float *lambda,
+                              const fss_view *alpha, const fss_view *beta) {
+    int rc;
+    if ((rc = check_ctx(ctx))) return rc;
+    if ((rc = check_shape(dtype, B, T, D))) return rc;
+    if (B == 0 || T == 0 || D == 0) return FSS_OK;
+    if (!lambda) return FSS_E_NULL;
+    if ((rc = check_view(r, B, T, D)) || (rc = check_view(alpha, B, T, D))) return rc;
+    if (beta && ((rc = check_view(i, B, T, D)) || (rc = check_view(x, B, T, D)) || (rc = check_view(beta, B, T, D))))
+        return rc;
+    if (!gate_grid_ok(B, T)) return FSS_E_SHAPE;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+#define FSS_GF(TT, VV) gates_forward_launch<TT, VV>(ctx, B, T, D, r, i, x, lambda, alpha, beta)
+    if (dtype == FSS_DTYPE_BF16)
+        return chunked::vector_ok<bf16>(D, {r, beta ? i : r, beta ? x : r, alpha, beta}) ? FSS_GF(bf16, 8) : FSS_GF(bf16, 1);
+    return chunked::vector_ok<float>(D, {r, beta ? i : r, beta ? x : r, alpha, beta}) ? FSS_GF(float, 4) : FSS_GF(float, 1);
+#undef FSS_GF
+}
+
+FSS_API int fss_gates_backward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                               const fss_view *r, const fss_view *i, const fss_view *x, const float *lambda,
+                               const fss_view *grad_alpha, const fss_view *grad_beta, const fss_view *grad_r,
+                               const fss_view *grad_i, const fss_view *grad_x, float *grad_lambda) {
+    int rc;
+    if ((rc = check_ctx(ctx))) return rc;
+    if ((rc = check_shape(dtype, B, T, D))) return rc;
+    if (B == 0 || T == 0 || D == 0) return FSS_OK;
+    if (!lambda || !grad_lambda) return FSS_E_NULL;
+    for (const fss_view *v : {r, i, x, grad_alpha, grad_beta, grad_r, grad_i, grad_x})
+        if ((rc = check_view(v, B, T, D))) return rc;
+    if (!gate_grid_ok(B, T)) return FSS_E_SHAPE;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+#define FSS_GB(TT, VV) gates_backward_launch<TT, VV>(ctx, B, T, D, r, i, x, lambda, grad_alpha, grad_beta, grad_r, grad_i, grad_x, grad_lambda)
+    if (dtype == FSS_DTYPE_BF16)
+        return chunked::vector_ok<bf16>(D, {r, i, x, grad_alpha, grad_beta, grad_r, grad_i, grad_x}) ? FSS_GB(bf16, 8) : FSS_GB(bf16, 1);
+    return chunked::vector_ok<float>(D, {r, i, x, grad_alpha, grad_beta, grad_r, grad_i, grad_x}) ? FSS_GB(float, 4) : FSS_GB(float, 1);
+#undef FSS_GB
 }

@@ -85,7 +85,8 @@ chunk_summary(Geometry g, View<const T> alpha, View<const T> other /* beta | gra
 
 // ---------------------------------------------------------------- 2. composition
 // In place: wsC[chunk] becomes the state entering that chunk, wsP[chunk] the product of alpha
-// from the scan's starting end through that chunk.
+// from the scan's starting end through that chunk.  block_prod receives each chunk's own product,
+// block_state the state leaving it.
 template <bool kBackward>
 __global__ void chunk_compose(Geometry g, float *__restrict__ wsP, float *__restrict__ wsC,
                               const float *__restrict__ state_in, float *__restrict__ state_out,
@@ -105,7 +106,7 @@ __global__ void chunk_compose(Geometry g, float *__restrict__ wsP, float *__rest
         carry = (carry == 0.0f) ? c : fmaf(p, carry, c);   // 0 absorbs an overflowed product
         run *= p;
         wsP[o] = run;
-        if (block_prod) block_prod[o] = run;
+        if (block_prod) block_prod[o] = p;
         if (block_state) block_state[o] = carry;
     }
     if (state_out) state_out[idx] = carry;

@@ -28,8 +28,9 @@ template <typename T> inline View<T> make_view(const fss_view *v) {
 template <typename T, int V> struct Frag;
 
 template <> struct Frag<bf16, 8> {
-    static __device__ __forceinline__ void load(const bf16 *p, float (&x)[8]) {
-        const uint4 r = __ldg(reinterpret_cast<const uint4 *>(p));
+    using Raw = uint4;      // the fragment as it travels: unpacked only when used, to keep loads in flight cheap
+    static __device__ __forceinline__ Raw load_raw(const bf16 *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+    static __device__ __forceinline__ void unpack(const Raw &r, float (&x)[8]) {
         const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -37,6 +38,7 @@ template <> struct Frag<bf16, 8> {
             x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
         }
     }
+    static __device__ __forceinline__ void load(const bf16 *p, float (&x)[8]) { unpack(load_raw(p), x); }
     static __device__ __forceinline__ void store(bf16 *p, const float (&x)[8]) {
         uint32_t w[4];
 #pragma unroll
@@ -49,6 +51,9 @@ template <> struct Frag<bf16, 8> {
 };
 
 template <> struct Frag<bf16, 1> {
+    using Raw = bf16;
+    static __device__ __forceinline__ Raw load_raw(const bf16 *p) { return *p; }
+    static __device__ __forceinline__ void unpack(const Raw &r, float (&x)[1]) { x[0] = __bfloat162float(r); }
     static __device__ __forceinline__ void load(const bf16 *p, float (&x)[1]) {
         x[0] = __bfloat162float(*p);
     }
@@ -58,16 +63,19 @@ template <> struct Frag<bf16, 1> {
 };
 
 template <> struct Frag<float, 4> {
-    static __device__ __forceinline__ void load(const float *p, float (&x)[4]) {
-        const float4 r = __ldg(reinterpret_cast<const float4 *>(p));
-        x[0] = r.x; x[1] = r.y; x[2] = r.z; x[3] = r.w;
-    }
+    using Raw = float4;
+    static __device__ __forceinline__ Raw load_raw(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+    static __device__ __forceinline__ void unpack(const Raw &r, float (&x)[4]) { x[0] = r.x; x[1] = r.y; x[2] = r.z; x[3] = r.w; }
+    static __device__ __forceinline__ void load(const float *p, float (&x)[4]) { unpack(load_raw(p), x); }
     static __device__ __forceinline__ void store(float *p, const float (&x)[4]) {
         *reinterpret_cast<float4 *>(p) = make_float4(x[0], x[1], x[2], x[3]);
     }
 };
 
 template <> struct Frag<float, 1> {
+    using Raw = float;
+    static __device__ __forceinline__ Raw load_raw(const float *p) { return __ldg(p); }
+    static __device__ __forceinline__ void unpack(const Raw &r, float (&x)[1]) { x[0] = r; }
     static __device__ __forceinline__ void load(const float *p, float (&x)[1]) { x[0] = __ldg(p); }
     static __device__ __forceinline__ void store(float *p, const float (&x)[1]) { *p = x[0]; }
 };

@@ -40,6 +40,7 @@
 #include <string>
 
 #include "fss_common.cuh"
+#include "fss_gates.cuh"
 
 namespace fss {
 namespace lookback {
@@ -88,22 +89,24 @@ struct Params {
     int32_t *status;
     const float *state_in;   // forward h_in / backward u_in, [B, D] or null
     float *state_out;        // forward h_last / backward u_out
-    float *prod_out;         // forward prod
-    float *block_prod;       // [B, S, D]
-    float *block_state;      // [B, S, D]
+    float *block_prod;       // [B, S, D]: product of alpha over the rows of each row block
+    float *block_state;      // [B, S, D]: state leaving each row block
     const float *h_prev;     // backward only
     const float *lambda;     // gated forward only: [D]
     int continuation;
     int32_t tile_rows;       // rows per tile: 64 * split
     uint32_t max_spins;      // iterations a wait may take before it gives up
     int mute_first_block;    // test hook: row block 0 publishes no descriptors (its successors' waits run out)
+    int deterministic;       // a tile only ever starts from its predecessor's inclusive state
     int64_t grid;            // CTAs of the launch
     // fixed tile order (CTA x takes tiles x, x+G, ...): ntiles = units_q * grid + units_r, so CTA x
     // owns units_q + (x < units_r) tiles; one grid stride = grid_q row blocks + grid_b batch rows +
     // grid_cg channel groups
     int32_t units_q, units_r;
     int32_t grid_q, grid_b, grid_cg;
-
+    // ticket order: the first n_fixed units of every CTA are the fixed ones (tiles x, x+G, ...),
+    // all tiles from n_fixed * G on are handed out by the counter
+    int32_t n_fixed;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -323,18 +326,19 @@ __device__ __forceinline__ Unit unit_of_tile(const Params &p, int64_t tile) {
 
 // How a role learns which tile its next unit is.
 //   fixed order (kTickets = false): arithmetic only -- CTA x works on tiles x, x+G, x+2G, ...
-//   tickets (kTickets = true): the producer describes every unit in a shared-memory slot per stage
-//     (see the producer) and arrives on info[stage]; a role reads the descriptor of its next unit
-//     while it still waits for the data of the current one, and only blocks if that was too early.
+//   tickets (kTickets = true): the first p.n_fixed units of a CTA are still the fixed ones; every
+//     later unit is described by the producer in a shared-memory slot per stage (see the producer),
+//     which then arrives on info[stage]; a role reads the descriptor of its next unit while it still
+//     waits for the data of the current one, and only blocks if that was too early.
 template <bool kTickets, int kStages> struct UnitCursor {
     const Params &p;
     const Ctl &ctl;
     const Unit *units;
     uint32_t bar_info0;
     int stride;          // units between two of this role's units (look-back warps: their number)
-    Unit cur, nxt;       // fixed order: unit i / i + stride.  tickets: nxt valid when `have`
+    Unit cur, nxt;       // unit i / i + stride; nxt valid when `have`
     bool have;
-    int n_my;
+    int n_arith;         // units of this CTA that follow from arithmetic
 
     __device__ __forceinline__ UnitCursor(const Params &p_, const Ctl &ctl_, const Unit *units_, uint32_t bar_info0_)
         : p(p_), ctl(ctl_), units(units_), bar_info0(bar_info0_) {}
@@ -349,9 +353,13 @@ template <bool kTickets, int kStages> struct UnitCursor {
             if (u.b >= (int32_t)p.B) { u.b -= (int32_t)p.B; u.s += 1; }
         }
     }
+    // phase of info[j % kStages] that unit j >= n_fixed completes: units n_fixed, n_fixed + 1, ... arrive in turn
+    __device__ __forceinline__ uint32_t info_parity(int j) const {
+        return (uint32_t)(((j - p.n_fixed) / kStages) & 1);
+    }
     __device__ __forceinline__ bool try_read(int j, Unit &out) const {   // warp-uniform
         const int sj = j % kStages;
-        if (!__all_sync(0xffffffffu, mbar_test_wait(bar_info0 + 8u * sj, (uint32_t)((j / kStages) & 1)))) return false;
+        if (!__all_sync(0xffffffffu, mbar_test_wait(bar_info0 + 8u * sj, info_parity(j)))) return false;
         out = units[sj];
         return true;
     }
@@ -359,31 +367,27 @@ template <bool kTickets, int kStages> struct UnitCursor {
     // u0: the CTA's first unit (tile blockIdx.x), worked out once per thread before the roles part
     __device__ __forceinline__ void init(const Unit &u0, int first_unit, int stride_) {
         stride = stride_;
-        have = false;
-        if (!kTickets) {
-            n_my = p.units_q + ((int32_t)blockIdx.x < p.units_r ? 1 : 0);
-            nxt = u0;
-            step(nxt, first_unit);
-            have = first_unit < n_my;
-        } else {
-            have = try_read(first_unit, nxt);
-        }
+        n_arith = kTickets ? p.n_fixed : p.units_q + ((int32_t)blockIdx.x < p.units_r ? 1 : 0);
+        nxt = u0;
+        have = first_unit < n_arith;
+        if (have) step(nxt, first_unit);
+        else if (kTickets) have = try_read(first_unit, nxt);
     }
     // Unit i into `cur`; false = no more units (or the wait was abandoned).  Then looks ahead to unit
     // i + stride: next_known() says whether `nxt` already describes a real unit.
     __device__ __forceinline__ bool advance(int i) {
-        if (!kTickets) {
-            if (i >= n_my) return false;
+        if (i < n_arith) {
             cur = nxt;
-            step(nxt, stride);
-            have = i + stride < n_my;
+            if (i + stride < n_arith) step(nxt, stride);      // have stays true
+            else have = kTickets ? try_read(i + stride, nxt) : false;
             return true;
         }
+        if (!kTickets) return false;
         if (have) {
             cur = nxt;
         } else {
             const int si = i % kStages;
-            if (!ctl.wait(bar_info0 + 8u * si, (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) return false;
+            if (!ctl.wait(bar_info0 + 8u * si, info_parity(i), FSS_STATUS_TMA_TIMEOUT)) return false;
             cur = units[si];
         }
         if (cur.k < 0) return false;
@@ -393,67 +397,17 @@ template <bool kTickets, int kStages> struct UnitCursor {
     __device__ __forceinline__ bool next_known() const { return have && nxt.k >= 0; }
 };
 
-// ------------------------------------------------------------------ gate front-end
-// RG-LRU gates evaluated in the kernel (gated forward):  a = exp(c * sigmoid(r)) with
-// c = -8 * softplus(lambda) per channel, b = sqrt(1 - a^2) * sigmoid(i) * x.  bf16 I/O rounds a and
-// b to 8 mantissa bits anyway, so it takes the 1-MUFU forms (tanh.approx, ex2.approx, sqrt.approx:
-// 4 special-function operations per element); fp32 I/O uses the fp32 ex2 / rcp / sqrt approximations (5 per element).  Measured on B200 the bf16 kernel is bound by the
-// special-function unit at about half of the HBM rate.
-template <typename T> struct Gate;
-template <> struct Gate<bf16> {
-    static __device__ __forceinline__ float sigmoid(float z) {
-        float t;
-        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * z));
-        return fmaf(0.5f, t, 0.5f);
-    }
-    static __device__ __forceinline__ float prescale(float c) { return c * 1.4426950408889634f; }   // exp(z) = 2^(z log2 e)
-    static __device__ __forceinline__ float exp_scaled(float z) {
-        float r;
-        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(z));
-        return r;
-    }
-    static __device__ __forceinline__ float root(float z) {
-        float r;
-        asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(z));
-        return r;
-    }
-};
-template <> struct Gate<float> {
-    // ex2 / rcp / sqrt of the special-function unit on fp32 operands: each within about 2^-22
-    // relative, far inside what the recurrence amplifies anyway (tanh.approx, good to 2^-11, is not)
-    static __device__ __forceinline__ float sigmoid(float z) {
-        float e, r;
-        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * z));
-        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-        return r;
-    }
-    static __device__ __forceinline__ float prescale(float c) { return c * 1.4426950408889634f; }
-    static __device__ __forceinline__ float exp_scaled(float z) {
-        float r;
-        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(z));
-        return r;
-    }
-    static __device__ __forceinline__ float root(float z) {
-        float r;
-        asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(z));
-        return r;
-    }
-};
-__device__ __forceinline__ float gate_scale(float lambda) {      // -8 * softplus(lambda)
-    return -8.0f * (lambda > 20.0f ? lambda : log1pf(expf(lambda)));
-}
-
 // ------------------------------------------------------------------ the kernel
 // Forward: tiles of (alpha, beta) are loaded, h is stored from beta's stage slot.
 // Backward: (alpha, grad, h shifted one row down) are loaded; dbeta is stored from grad's slot,
 // dalpha from h's slot.  Results are written in place in shared memory and leave through TMA
 // stores issued by the producer, so the consumer warps never stall on the global write path.
-template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets, bool kGate = false>
+template <typename T, bool kBackward, int kSp, bool kTickets, bool kGate = false>
 __global__ void __launch_bounds__(kThreads, 1)
 scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant__ CUtensorMap map_x,
             const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_out0,
             const __grid_constant__ CUtensorMap map_out1, const Params p) {
-    static_assert(!(kGate && (kBackward || kProd || kTickets)), "the gate front-end exists for the plain forward only");
+    static_assert(!(kGate && (kBackward || kTickets)), "the gate front-end exists for the plain forward only");
     constexpr bool kThree = kBackward || kGate;      // tensors loaded per unit: 3, else 2
     constexpr int kTensors = kThree ? 3 : 2;
     constexpr int kStages = kThree ? kStagesBwd : kStagesFwd;
@@ -495,6 +449,14 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     // become free, and do everything that touches no global memory before waiting for the previous
     // launch to finish (both instructions do nothing for an ordinary launch).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == kProducerWarp * 32) {
+        // the descriptors are kernel parameters, not data of the previous launch: fetch them now
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_alpha) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        if (kThree) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_h) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out0) : "memory");
+        if (kBackward) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out1) : "memory");
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_done(s), kW); mbar_init(bar_info(s), 1); }
         for (int g = 0; g < kGens; ++g) { mbar_init(bar_agg(g), kW); mbar_init(bar_carry(g), 1); mbar_init(bar_sum(g), 1); }
@@ -515,14 +477,10 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     if (warp == kProducerWarp) {
         // ============================================================ producer
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_alpha) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-            if (kThree) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_h) : "memory");
             // Which tile a unit is.  Fixed order: CTA x takes tiles x, x+G, x+2G, ...  Tickets: the same
-            // for the first kStages units, after that every refill takes the next tile from a global
+            // for the first n_fixed units, after that every refill takes the next tile from a global
             // counter, so an SM that the memory system serves faster takes more tiles and all CTAs
-            // finish together (worth it for long, HBM-bound launches; the descriptors cost a little
-            // on short ones).  Tickets are handed out in increasing order and each CTA works through
+            // finish together.  Tickets are handed out in increasing order and each CTA works through
             // its own in order, so a tile still only depends on tiles some resident CTA has taken.
             const int64_t G = p.grid;
             uint32_t hand = 0;            // ticket requested one refill ahead (hides the atomic's latency)
@@ -535,34 +493,33 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             // markers keep being posted as stages free up, because the look-back warps take units
             // alternately and each has to meet one.  prepare() runs while the stage is still busy, so
             // its arithmetic and the ticket's round trip stay off the refill path.
-            Cursor fixed(p, ctl, units, bar_info(0));
-            if (!kTickets) fixed.init(u0, 0, 1);
+            // (this thread runs alone: it only uses the cursor's arithmetic, never its warp-wide reads)
+            const Cursor arith(p, ctl, units, bar_info(0));
+            const int n_arith = kTickets ? p.n_fixed : p.units_q + ((int32_t)first < p.units_r ? 1 : 0);
+            Unit walk = u0;               // the unit slot `next` holds while next < n_arith
             auto prepare = [&]() {
-                if (!kTickets) {
-                    ended = !fixed.advance(next);
-                    nu = fixed.cur;
-                    if (ended) nu.k = -1;
+                if (next < n_arith) {
+                    nu = walk;
+                    arith.step(walk, 1);
+                    if (kTickets && next == n_arith - 1) hand = atomicAdd(&p.hdr->ticket, 1u);
                     return;
                 }
-                int64_t tile = 0;
+                if (!kTickets) { ended = true; nu.k = -1; return; }
                 if (!ended) {
-                    if (issued < kStages) {
-                        tile = (int64_t)first + (int64_t)issued * G;
-                        if (issued == kStages - 1) hand = atomicAdd(&p.hdr->ticket, 1u);
-                    } else {
-                        tile = G * kStages + hand;
-                        hand = atomicAdd(&p.hdr->ticket, 1u);
-                    }
+                    const int64_t tile = (int64_t)p.n_fixed * G + hand;
                     ended = tile >= p.ntiles;
+                    if (!ended) {
+                        hand = atomicAdd(&p.hdr->ticket, 1u);
+                        nu = unit_of_tile(p, tile);
+                    }
                 }
                 if (ended) { nu.k = -1; nu.s = nu.b = nu.cg = 0; }
-                else nu = unit_of_tile(p, tile);
             };
             auto post = [&]() {
                 const int st = next % kStages;
                 ++next;
                 units[st] = nu;           // the producer itself reads it back when it stores the unit
-                if (kTickets) mbar_arrive(bar_info(st));
+                if (kTickets && next > p.n_fixed) mbar_arrive(bar_info(st));   // the other roles compute the first n_fixed
                 if (nu.k < 0) return;
                 const uint32_t base = smem_base + st * SM::kStageBytes;
                 const int32_t c0 = nu.cg * Dc, c1 = nu.template row0<kBackward>(p), c2 = nu.b;
@@ -615,7 +572,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         // at once: successors of this tile can then fold it without waiting for the tile's own
         // carry resolution.  This warp never waits on anything outside its CTA.
         using AggPk = PacketGroup<2 * V, LPG>;
-        constexpr int kTilePackets = (AggPk::kPackets + PacketGroup<(kProd ? 2 : 1) * V>::kPackets) * LPG;
+        constexpr int kTilePackets = (AggPk::kPackets + PacketGroup<V>::kPackets) * LPG;
         const uint32_t tag_agg = (epoch << 2) | kStateAggregate;
         Cursor cursor(p, ctl, units, bar_info(0));
         cursor.init(u0, 0, 1);
@@ -696,12 +653,20 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             if (lane == 0) mbar_arrive(bar_sum(g));
             if (!last_block && q == 0 && !(p.mute_first_block && it_s == 0))
                 AggPk::store(p.packets + k * kTilePackets + cl, pc, tag_agg);
+            // the row block's own product of alpha, for callers that stitch scans together
+            if (p.block_prod && q == 0) {
+                const int64_t dch = (int64_t)u.cg * Dc + cl * V;
+                if (dch < p.D) {
+                    const int64_t blk = kBackward ? (p.S - 1 - it_s) : it_s;
+                    *reinterpret_cast<VecF *>(p.block_prod + ((int64_t)u.b * p.S + blk) * p.D + dch) = sp;
+                }
+            }
         }
     } else if (warp >= kLookbackWarp0) {
         // ============================================================ look-back
         // kLookbackWarps warps share the work units round-robin, so several carry resolutions
         // (each a few L2 round trips) are in flight per CTA.
-        constexpr int NI = kProd ? 2 * V : V;          // floats of an inclusive descriptor
+        constexpr int NI = V;                          // floats of an inclusive descriptor
         constexpr int kWin = kWindow;
         using AggPk = PacketGroup<2 * V, LPG>;         // (P, C) of the tile scanned from zero
         using IncPk = PacketGroup<NI, LPG>;                 // state after the tile (and product up to it)
@@ -769,18 +734,18 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 for (int v = 0; v < V; ++v) { Pt[v] = vec_get(sp, v); Ct[v] = vec_get(sc, v); }
             }
 
-            // ---- the state entering this tile (cin) and the product of alpha before it (pin)
-            float cin[V], pin[V];
+            // ---- the state entering this tile
+            float cin[V];
             bool ok = true;
             auto state0 = [&](int v) {
                 return (p.state_in && ch_ok) ? p.state_in[(int64_t)b * p.D + dch + v] : 0.0f;
             };
             if (s == 0) {
 #pragma unroll
-                for (int v = 0; v < V; ++v) { cin[v] = state0(v); pin[v] = 1.0f; }
+                for (int v = 0; v < V; ++v) cin[v] = state0(v);
             } else if (hit) {
 #pragma unroll
-                for (int v = 0; v < V; ++v) { cin[v] = cur[v]; pin[v] = kProd ? cur[kProd ? V + v : v] : 1.0f; }
+                for (int v = 0; v < V; ++v) cin[v] = cur[v];
             } else {
                 float Pa[V], Ca[V];          // map of the tiles between the predecessor at q and this one
 #pragma unroll
@@ -812,12 +777,9 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                             stop = true;
                         } else if (__all_sync(0xffffffffu, inc_ok[j])) {
 #pragma unroll
-                            for (int v = 0; v < V; ++v) {
-                                cin[v] = fmaf(Pa[v], inc[j][v], Ca[v]);
-                                pin[v] = kProd ? Pa[v] * inc[j][kProd ? V + v : v] : 1.0f;
-                            }
+                            for (int v = 0; v < V; ++v) cin[v] = fmaf(Pa[v], inc[j][v], Ca[v]);
                             found = true;
-                        } else if (__all_sync(0xffffffffu, ag_ok[j])) {
+                        } else if (!p.deterministic && __all_sync(0xffffffffu, ag_ok[j])) {
 #pragma unroll
                             for (int v = 0; v < V; ++v) {
                                 Ca[v] = fmaf(Pa[v], ag[j][V + v], Ca[v]);
@@ -826,7 +788,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                             adv = j + 1;
                             if (qj - p.ncols < 0) {      // folded everything down to row block 0
 #pragma unroll
-                                for (int v = 0; v < V; ++v) { cin[v] = fmaf(Pa[v], state0(v), Ca[v]); pin[v] = Pa[v]; }
+                                for (int v = 0; v < V; ++v) cin[v] = fmaf(Pa[v], state0(v), Ca[v]);
                                 found = true;
                             }
                         } else {
@@ -859,34 +821,22 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_carry(g));
 
-            // ---- publish the inclusive descriptor: state after this tile, product through it
+            // ---- publish the inclusive descriptor: the state after this tile
             float out[NI];
 #pragma unroll
-            for (int v = 0; v < V; ++v) {
-                out[v] = fmaf(Pt[v], cin[v], Ct[v]);
-                if (kProd) out[kProd ? V + v : v] = Pt[v] * pin[v];
-            }
+            for (int v = 0; v < V; ++v) out[v] = fmaf(Pt[v], cin[v], Ct[v]);
             if (s + 1 < (int32_t)p.S && q == 0 && !(p.mute_first_block && s == 0)) IncPk::store(inc_packets(k), out, tag_inc);
 
             if (ch_ok && q == 0) {
-                if (kProd && p.block_prod) {
+                VecF vo;
+#pragma unroll
+                for (int v = 0; v < V; ++v) vec_set(vo, v, out[v]);
+                if (p.block_state) {
                     const int64_t blk = kBackward ? (p.S - 1 - s) : s;
-                    float *bp = p.block_prod + ((int64_t)b * p.S + blk) * p.D + dch;
-#pragma unroll
-                    for (int v = 0; v < V; ++v) bp[v] = out[kProd ? V + v : v];
-                    if (p.block_state) {
-                        float *bs = p.block_state + ((int64_t)b * p.S + blk) * p.D + dch;
-#pragma unroll
-                        for (int v = 0; v < V; ++v) bs[v] = out[v];
-                    }
+                    *reinterpret_cast<VecF *>(p.block_state + ((int64_t)b * p.S + blk) * p.D + dch) = vo;
                 }
-                if (s + 1 == (int32_t)p.S) {
-#pragma unroll
-                    for (int v = 0; v < V; ++v) {
-                        if (p.state_out) p.state_out[(int64_t)b * p.D + dch + v] = out[v];
-                        if (kProd && p.prod_out) p.prod_out[(int64_t)b * p.D + dch + v] = out[kProd ? V + v : v];
-                    }
-                }
+                if (s + 1 == (int32_t)p.S && p.state_out)
+                    *reinterpret_cast<VecF *>(p.state_out + (int64_t)b * p.D + dch) = vo;
             }
         }
     } else if (warp < kPass2Warp0) {
@@ -1153,27 +1103,36 @@ inline int choose_split(int dtype, int64_t B, int64_t T, int64_t D) {
     while (s < 4 && cols * s < 2 * 148 && row_bytes >= kRowBytes / s && T >= 2 * kTc * s * 2) s *= 2;
     return s;
 }
-// Tile order: tickets (tiles handed out by a global counter, see the producer) once a tensor is
-// larger than the L2 can hold between the forward and the backward launch -- such launches are
-// HBM-bound from end to end and gain 1-5 % from the balancing; shorter ones lose 2-4 % to the
-// unit descriptors, so they keep the fixed order.  FSS_B200_TICKETS=0 / 1 forces the choice.
-inline bool choose_tickets(int dtype, int64_t B, int64_t T, int64_t D) {
-    static const int env = [] { const char *e = getenv("FSS_B200_TICKETS"); return !e ? -1 : (e[0] == '1' ? 1 : 0); }();
-    if (env >= 0) return env == 1;
-    return B * T * D * (dtype == FSS_DTYPE_BF16 ? 2 : 4) >= (int64_t)96 << 20;
+// Tile order.  Returns how many units at the END of a CTA's share are handed out by the global
+// counter instead of by arithmetic (see the producer): 0 = fixed order throughout, a large value =
+// everything after the first ring of stages.  Measured on B200: SMs are not served equally by the
+// memory system, so with a fixed order the first CTA finishes several microseconds before the
+// last; tiles taken by ticket let the fast SMs take more.  The descriptors that ticketed units
+// travel in cost a little per unit, which is why short launches only ticket their tail.
+// The forward kernel (six stages in flight) lost 2-15 % with any number of ticketed units on every
+// workload measured, so it keeps the fixed order.  FSS_B200_TAIL=<n> forces n for both directions
+// (0 = fixed order); FSS_B200_TICKETS=0 / 1 forces none / all for the backward kernel.
+constexpr int kAllTickets = 1 << 30;
+inline int choose_tail(int dtype, bool backward, int64_t B, int64_t T, int64_t D) {
+    static const int env_tail = [] { const char *e = getenv("FSS_B200_TAIL"); return e ? atoi(e) : -1; }();
+    static const int env_all = [] { const char *e = getenv("FSS_B200_TICKETS"); return !e ? -1 : (e[0] == '1' ? 1 : 0); }();
+    if (env_tail >= 0) return env_tail;
+    if (!backward) return 0;
+    if (env_all >= 0) return env_all ? kAllTickets : 0;
+    const int64_t bytes = B * T * D * (dtype == FSS_DTYPE_BF16 ? 2 : 4);
+    return bytes >= ((int64_t)96 << 20) ? kAllTickets : 0;
 }
 inline int64_t block_rows(int dtype, int64_t B, int64_t T, int64_t D) { return (int64_t)kTc * choose_split(dtype, B, T, D); }
 
 template <typename T> inline int64_t channel_groups(int64_t D) { return ceil_div(D, Cfg<T>::Dc); }
 
-// bytes of descriptor packets for a problem (worst case: with products)
-template <typename T> constexpr int packets_per_tile(bool prod) {
-    return (PacketGroup<2 * Cfg<T>::V>::kPackets +
-            (prod ? PacketGroup<2 * Cfg<T>::V>::kPackets : PacketGroup<Cfg<T>::V>::kPackets)) * 32;
+// descriptor packets per tile: the aggregate (P, C) and the inclusive state
+template <typename T> constexpr int packets_per_tile() {
+    return (PacketGroup<2 * Cfg<T>::V>::kPackets + PacketGroup<Cfg<T>::V>::kPackets) * 32;
 }
 inline size_t workspace_bytes(int64_t B, int64_t T, int64_t D, int dtype) {
     const int Dc = dtype == FSS_DTYPE_BF16 ? Cfg<bf16>::Dc : Cfg<float>::Dc;
-    const int per_tile = dtype == FSS_DTYPE_BF16 ? packets_per_tile<bf16>(true) : packets_per_tile<float>(true);
+    const int per_tile = dtype == FSS_DTYPE_BF16 ? packets_per_tile<bf16>() : packets_per_tile<float>();
     size_t worst = 0;
     for (int s = 1; s <= 4; s *= 2) {       // any tile shape the launcher may pick
         const int64_t ntiles = B * ceil_div(D, Dc / s) * ceil_div(T, (int64_t)kTc * s);
@@ -1181,6 +1140,11 @@ inline size_t workspace_bytes(int64_t B, int64_t T, int64_t D, int dtype) {
         if (need > worst) worst = need;
     }
     return worst;
+}
+// float scratch a launch may use: per-block products when the caller asks for the total product
+// without providing a block array
+inline size_t float_scratch_bytes(int64_t B, int64_t T, int64_t D) {
+    return (size_t)(B * ceil_div(T, (int64_t)kTc) * D) * sizeof(float);
 }
 
 // What TMA needs: 16-byte aligned bases and strides, extents that fit its 32-bit coordinates.
@@ -1280,14 +1244,14 @@ inline const CUtensorMap *cached_map(const fss_view *v, int64_t B, int64_t Tn, i
 }
 
 // CTAs that fit the device at once (one per SM with these shared-memory sizes), per device.
-template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets, bool kGate> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
+template <typename T, bool kBackward, int kSp, bool kTickets, bool kGate> inline int resident_ctas(int device, int smem_bytes, cudaError_t *err) {
     static std::mutex mu;
     static int cached[64];
     static bool have[64];
     std::lock_guard<std::mutex> lock(mu);
     if (device < 0 || device >= 64) { *err = cudaErrorInvalidDevice; return 0; }
     if (!have[device]) {
-        auto kern = scan_kernel<T, kBackward, kProd, kSp, kTickets, kGate>;
+        auto kern = scan_kernel<T, kBackward, kSp, kTickets, kGate>;
         *err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (*err != cudaSuccess) return 0;
         int per_sm = 0, sms = 0;
@@ -1302,10 +1266,10 @@ template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets, bool k
     return cached[device];
 }
 
-template <typename T, bool kBackward, bool kProd, int kSp, bool kTickets, bool kGate = false>
+template <typename T, bool kBackward, int kSp, bool kTickets, bool kGate = false>
 inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t Tn, int64_t D,
                   const fss_view *alpha, const fss_view *x, const fss_view *h, const fss_view *out0,
-                  const fss_view *out1, Params p, std::string *err_text) {
+                  const fss_view *out1, Params p, int tail, std::string *err_text) {
     constexpr int kTensors = (kBackward || kGate) ? 3 : 2;
     constexpr int kStages = (kBackward || kGate) ? kStagesBwd : kStagesFwd;
     constexpr int smem_bytes = Smem<kTensors, kStages>::kBytes;
@@ -1331,7 +1295,7 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) { *err_text = cudaGetErrorString(e); return FSS_E_DEVICE; }
-    const int resident = resident_ctas<T, kBackward, kProd, kSp, kTickets, kGate>(device, smem_bytes, &e);
+    const int resident = resident_ctas<T, kBackward, kSp, kTickets, kGate>(device, smem_bytes, &e);
     if (e != cudaSuccess || resident < 1) { *err_text = cudaGetErrorString(e); return FSS_E_LAUNCH; }
 
     p.B = B; p.T = Tn; p.D = D;
@@ -1341,13 +1305,14 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     p.tile_rows = kTc * kSp;
     p.ntiles = p.ncols * p.S;
     if (p.ntiles > 0x7fffffffLL) return FSS_E_SHAPE;      // tile numbers travel as 32-bit values
-    if ((size_t)p.ntiles * (packets_per_tile<T>(kProd) / kSp) * 16 > ws.packet_bytes) return FSS_E_WORKSPACE;
+    if ((size_t)p.ntiles * (packets_per_tile<T>() / kSp) * 16 > ws.packet_bytes) return FSS_E_WORKSPACE;
     p.hdr = reinterpret_cast<Header *>(ws.hdr);
     p.packets = reinterpret_cast<uint4 *>(ws.packets);
     p.status = ctx->status;
     p.continuation = (ctx->flags & FSS_FLAG_CONTINUATION) ? 1 : 0;
     p.max_spins = (ctx->flags & FSS_FLAG_TEST_SHORT_WAITS) ? 4096u : kMaxSpins;
     p.mute_first_block = (ctx->flags & FSS_FLAG_TEST_MUTE_FIRST_BLOCK) ? 1 : 0;
+    p.deterministic = (ctx->flags & FSS_FLAG_DETERMINISTIC) ? 1 : 0;
 
     const unsigned grid = (unsigned)(p.ntiles < resident ? p.ntiles : resident);
     p.grid = grid;
@@ -1356,6 +1321,14 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     p.grid_q = (int32_t)(grid / p.ncols);
     p.grid_b = (int32_t)((grid % p.ncols) / p.ncg);
     p.grid_cg = (int32_t)((grid % p.ncols) % p.ncg);
+    // every CTA owns at least units_q tiles in the fixed order; the last `tail` of those, and
+    // everything after them, go by ticket (at least the first ring stays fixed: its loads start
+    // before anything else is known)
+    {
+        const int32_t ring = p.units_q < kStages ? p.units_q : kStages;
+        const int64_t keep = (int64_t)p.units_q - tail;
+        p.n_fixed = kTickets ? (int32_t)(keep > ring ? keep : ring) : p.units_q + 1;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);
@@ -1375,21 +1348,21 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     const bool use_pdl = pdl_env >= 0 ? pdl_env == 1 : (!kBackward || p.ntiles <= kPdlMaxUnits * (int64_t)grid);
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, scan_kernel<T, kBackward, kProd, kSp, kTickets, kGate>, m_alpha, m_x, m_h, m_o0, m_o1, p);
+    e = cudaLaunchKernelEx(&cfg, scan_kernel<T, kBackward, kSp, kTickets, kGate>, m_alpha, m_x, m_h, m_o0, m_o1, p);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { *err_text = std::string("look-back launch: ") + cudaGetErrorString(e); return FSS_E_LAUNCH; }
     return FSS_OK;
 }
 
-template <typename T, bool kBackward, bool kProd>
+template <typename T, bool kBackward>
 inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t Tn, int64_t D,
                   const fss_view *alpha, const fss_view *x, const fss_view *h, const fss_view *out0,
                   const fss_view *out1, Params p, std::string *err_text) {
     const int dtype = sizeof(T) == 2 ? FSS_DTYPE_BF16 : FSS_DTYPE_F32;
-    const bool tickets = kBackward && choose_tickets(dtype, B, Tn, D);    // measured: the forward never gains
+    const int tail = choose_tail(dtype, kBackward, B, Tn, D);
 #define FSS_LAUNCH_SPLIT(SP)                                                                                       \
-    return tickets ? launch_split<T, kBackward, kProd, SP, true>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, err_text) \
-                   : launch_split<T, kBackward, kProd, SP, false>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, err_text)
+    return tail > 0 ? launch_split<T, kBackward, SP, true>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, tail, err_text) \
+                    : launch_split<T, kBackward, SP, false>(ctx, ws, B, Tn, D, alpha, x, h, out0, out1, p, 0, err_text)
     switch (choose_split(dtype, B, Tn, D)) {
     case 4: FSS_LAUNCH_SPLIT(4);
     case 2: FSS_LAUNCH_SPLIT(2);
@@ -1398,22 +1371,88 @@ inline int launch(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t 
 #undef FSS_LAUNCH_SPLIT
 }
 
+// prod[b, d] = product over the row blocks of block_prod[b, :, d].  A CTA owns 8 channel vectors
+// (float4) of one batch row; its 64 thread rows split the blocks, so that every thread has only a
+// handful of independent loads, and combine through shared memory.
+constexpr int kProdSlices = 64, kProdVecs = 8;
+__global__ void __launch_bounds__(kProdSlices * kProdVecs)
+column_product(const float *__restrict__ block_prod, float *__restrict__ prod, int64_t S, int64_t D) {
+    __shared__ float4 part[kProdSlices][kProdVecs];
+    const int vec = threadIdx.x % kProdVecs, slice = threadIdx.x / kProdVecs;
+    const int64_t b = blockIdx.y;
+    const int64_t d0 = ((int64_t)blockIdx.x * kProdVecs + vec) * 4;
+    float4 acc = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    if (d0 < D) {
+        const float *base = block_prod + b * S * D + d0;
+        const bool vec_ok = d0 + 4 <= D && (D % 4 == 0) && (reinterpret_cast<uintptr_t>(base) & 15u) == 0;
+#pragma unroll 4
+        for (int64_t s = slice; s < S; s += kProdSlices) {
+            float4 v;
+            if (vec_ok) {
+                v = *reinterpret_cast<const float4 *>(base + s * D);
+            } else {
+                v.x = base[s * D];
+                v.y = d0 + 1 < D ? base[s * D + 1] : 1.0f;
+                v.z = d0 + 2 < D ? base[s * D + 2] : 1.0f;
+                v.w = d0 + 3 < D ? base[s * D + 3] : 1.0f;
+            }
+            acc.x *= v.x; acc.y *= v.y; acc.z *= v.z; acc.w *= v.w;
+        }
+    }
+    part[slice][vec] = acc;
+    __syncthreads();
+    // tree over the slices (the order of the factors is fixed, so the result is reproducible)
+    for (int half = kProdSlices / 2; half > 0; half /= 2) {
+        if (slice < half) {
+            const float4 o = part[slice + half][vec];
+            float4 m = part[slice][vec];
+            m.x *= o.x; m.y *= o.y; m.z *= o.z; m.w *= o.w;
+            part[slice][vec] = m;
+        }
+        __syncthreads();
+    }
+    if (slice == 0 && d0 < D) {
+        const float4 r = part[0][vec];
+        float *out = prod + b * D + d0;
+        out[0] = r.x;
+        if (d0 + 1 < D) out[1] = r.y;
+        if (d0 + 2 < D) out[2] = r.z;
+        if (d0 + 3 < D) out[3] = r.w;
+    }
+}
+inline int launch_column_product(const float *block_prod, float *prod, int64_t B, int64_t S, int64_t D, cudaStream_t stream,
+                                 std::string *err_text) {
+    if (B > 65535) { *err_text = "product of alpha: more than 65535 batch rows"; return FSS_E_SHAPE; }
+    const dim3 grid((unsigned)ceil_div(D, 4 * kProdVecs), (unsigned)B);
+    column_product<<<grid, kProdSlices * kProdVecs, 0, stream>>>(block_prod, prod, S, D);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { *err_text = std::string("product launch: ") + cudaGetErrorString(e); return FSS_E_LAUNCH; }
+    return FSS_OK;
+}
+
 template <typename T>
 inline int forward(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_t Tn, int64_t D,
                    const fss_view *alpha, const fss_view *beta, const fss_view *h,
                    const fss_forward_state *st, std::string *err_text) {
     Params p{};
     const bool cont = ctx->flags & FSS_FLAG_CONTINUATION;
+    float *prod = nullptr;
     if (st) {
         p.state_in = cont ? st->h_in : nullptr;
         p.state_out = st->h_last;
-        p.prod_out = st->prod;
         p.block_prod = st->block_prod;
         p.block_state = st->block_state;
+        prod = st->prod;
     }
-    if (p.prod_out || p.block_prod)
-        return launch<T, false, true>(ctx, ws, B, Tn, D, alpha, beta, nullptr, h, nullptr, p, err_text);
-    return launch<T, false, false>(ctx, ws, B, Tn, D, alpha, beta, nullptr, h, nullptr, p, err_text);
+    if (prod && !p.block_prod) {      // the total product is folded from the per-block products: keep them in scratch
+        if (float_scratch_bytes(B, Tn, D) > ws.float_bytes) return FSS_E_WORKSPACE;
+        p.block_prod = reinterpret_cast<float *>(ws.floats);
+    }
+    const int rc = launch<T, false>(ctx, ws, B, Tn, D, alpha, beta, nullptr, h, nullptr, p, err_text);
+    if (rc != FSS_OK || !prod) return rc;
+    const int dtype = sizeof(T) == 2 ? FSS_DTYPE_BF16 : FSS_DTYPE_F32;
+    const int64_t S = ceil_div(Tn, block_rows(dtype, B, Tn, D));
+    return launch_column_product(p.block_prod, prod, B, S, D, (cudaStream_t)ctx->stream, err_text);
 }
 
 // Forward scan whose alpha and beta are computed in the kernel from the recurrence gate r, the input
@@ -1431,9 +1470,9 @@ inline int forward_gated(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, i
     p.lambda = lambda;
     const int dtype = sizeof(T) == 2 ? FSS_DTYPE_BF16 : FSS_DTYPE_F32;
     switch (choose_split(dtype, B, Tn, D)) {
-    case 4: return launch_split<T, false, false, 4, false, true>(ctx, ws, B, Tn, D, r, x, i, h, nullptr, p, err_text);
-    case 2: return launch_split<T, false, false, 2, false, true>(ctx, ws, B, Tn, D, r, x, i, h, nullptr, p, err_text);
-    default: return launch_split<T, false, false, 1, false, true>(ctx, ws, B, Tn, D, r, x, i, h, nullptr, p, err_text);
+    case 4: return launch_split<T, false, 4, false, true>(ctx, ws, B, Tn, D, r, x, i, h, nullptr, p, 0, err_text);
+    case 2: return launch_split<T, false, 2, false, true>(ctx, ws, B, Tn, D, r, x, i, h, nullptr, p, 0, err_text);
+    default: return launch_split<T, false, 1, false, true>(ctx, ws, B, Tn, D, r, x, i, h, nullptr, p, 0, err_text);
     }
 }
 
@@ -1450,9 +1489,14 @@ inline int backward(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, int64_
         p.block_state = st->block_state;
         p.h_prev = cont ? st->h_prev : nullptr;
     }
-    if (p.block_prod)
-        return launch<T, true, true>(ctx, ws, B, Tn, D, alpha, grad, h, dalpha, dbeta, p, err_text);
-    return launch<T, true, false>(ctx, ws, B, Tn, D, alpha, grad, h, dalpha, dbeta, p, err_text);
+    return launch<T, true>(ctx, ws, B, Tn, D, alpha, grad, h, dalpha, dbeta, p, err_text);
+}
+
+// fp32 state vectors are moved as 8- or 16-byte words by the single-pass kernels
+inline bool state_aligned(std::initializer_list<const void *> ptrs) {
+    for (const void *q : ptrs)
+        if (q && !aligned16(q)) return false;
+    return true;
 }
 
 }  // namespace lookback

@@ -1,7 +1,8 @@
 // Sequence-parallel pieces: every rank scans its rows from a zero state, the per-rank
-// (product, state) vectors are gathered by the host (NCCL), and these kernels fold them and add
-// the missing term to the rows already written.  The reference never splits the sequence; this
-// follows the chunk algebra of fss_chunked.cuh one level up.
+// (product, state) vectors are gathered by the host (NCCL), and these kernels fold them and
+// re-scan the rows that the state arriving from the neighbouring rank still reaches.  The
+// reference never splits the sequence; this follows the chunk algebra of fss_chunked.cuh one
+// level up.
 #pragma once
 
 #include "fss_common.cuh"
@@ -32,25 +33,33 @@ __global__ void compose(int backward, int world, int rank, int64_t n,
     carry_in[i] = carry;
 }
 
-// Fix-up geometry: one CTA per (block of R rows, group of 32 channel vectors, batch row); its
-// kWarps warps split the block's rows, lane = channel vector.
-constexpr int kWarps = 8;
-constexpr int kFixThreads = kWarps * 32;
+// ------------------------------------------------------------------ fix-up
+// The zero-state scan left, per block of R rows, the block's own product of alpha (block_prod) and
+// the state leaving the block (block_state).  With the state `carry` that really enters the rows,
+// block j starts from   block_state[j-1] + (product of the blocks before j) * carry   (forward;
+// the backward mirrors it from the last block down).  A block whose correction term is exactly
+// zero for all its channels already holds the exact result; because the running product only
+// shrinks for gates in [0, 1] -- and, once it has underflowed, stays zero in the sequential scan
+// too -- the first such block ends the work of its column.
+//
+// Grid: (slots, channel blocks, batch rows).  The CTA in slot k handles blocks k, k + slots, ... of
+// its column until it meets a dead one, so the cost follows the rows that are still reached, plus
+// one cheap look per CTA.  Inside a live block the CTA's warps split the rows: each first reduces
+// its rows to (P, C), then re-scans them from (map of the warps before it)(entering state).
+constexpr int kFixWarps = 16;
+constexpr int kFixThreads = kFixWarps * 32;
+constexpr int kFixRowBatch = 4;      // rows whose loads are in flight together (two tensors)
+constexpr int kFixRowBatch3 = 4;     // the same where three tensors are read per row
 
 struct Geometry {
     int64_t B, T, D;
     int64_t R;        // rows per block (the block_prod granularity)
     int64_t NB;       // blocks per column
     int64_t nvec, vblocks;   // channel vectors per row, CTAs along the channel axis (32 vectors each)
+    int slots;        // CTAs along the block axis
 };
 
-__device__ __forceinline__ void decode_block(const Geometry &g, int64_t id, int64_t &vb, int64_t &j, int64_t &b) {
-    vb = id % g.vblocks; id /= g.vblocks;
-    j = id % g.NB;
-    b = id / g.NB;
-}
-// V consecutive floats, as 16-byte loads when the address allows it (one sector per 8 floats
-// instead of one per float: the liveness check below is all loads)
+// V consecutive floats, as 16-byte loads when the address allows it
 template <int V> __device__ __forceinline__ void load_floats(const float *__restrict__ p, float (&out)[V]) {
     if (V % 4 == 0 && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
 #pragma unroll
@@ -63,186 +72,272 @@ template <int V> __device__ __forceinline__ void load_floats(const float *__rest
         for (int i = 0; i < V; ++i) out[i] = p[i];
     }
 }
-// The grid is at most a few CTAs per SM and every CTA walks the (block, channel group, batch row)
-// candidates with a grid stride: almost all candidates are dead (their check costs one round of
-// loads), and launching a CTA per candidate cost more than checking them.
-inline unsigned fixup_grid(const Geometry &g, int sms) {
-    const int64_t total = g.vblocks * g.NB * g.B;
-    const int64_t cap = (int64_t)sms * (2048 / kFixThreads);
-    return (unsigned)(total < cap ? total : cap);
+
+inline int choose_slots(int64_t NB, int64_t vblocks, int64_t B, int sms) {
+    // one CTA per SM in total (a CTA takes a whole SM's registers); a column whose carry reaches
+    // further than the slots is walked in strides
+    int64_t s = (int64_t)sms / (vblocks * B > 0 ? vblocks * B : 1);
+    if (s < 1) s = 1;
+    if (s > NB) s = NB;
+    return (int)s;
 }
 
-// Re-scan of the blocks that the entering state still reaches (forward).  A block is live when
-// (product of alpha before it) * carry_in is non-zero for some channel; a dead block already holds
-// the exact result.  Inside a live block the warps first summarise their rows (P, C), then each
-// re-scans its rows from  (map of the warps before it)(true state entering the block).
+// Product over blocks [lo, hi) of block_prod for this lane's channels, all warps of the CTA
+// together; every thread returns the full product.  `scratch` is [kFixWarps][32][V] floats.
+template <int V>
+__device__ __forceinline__ void block_range_product(const float *__restrict__ bp_col, int64_t D, int64_t lo, int64_t hi,
+                                                    bool has, float *scratch, float (&out)[V]) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 1.0f;
+    if (has) {
+        for (int64_t s = lo + warp; s < hi; s += kFixWarps) {
+            float v[V];
+            load_floats<V>(bp_col + s * D, v);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] *= v[i];
+        }
+    }
+    __syncthreads();      // the scratch may still be read from the previous use
+#pragma unroll
+    for (int i = 0; i < V; ++i) scratch[(warp * 32 + lane) * V + i] = acc[i];
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < V; ++i) out[i] = 1.0f;
+    for (int w = 0; w < kFixWarps; ++w) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) out[i] *= scratch[(w * 32 + lane) * V + i];
+    }
+}
+
 template <typename T, int V>
 __global__ void __launch_bounds__(kFixThreads)
 fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, const float *__restrict__ carry_in,
               const float *__restrict__ block_prod, const float *__restrict__ block_state) {
-    __shared__ float sP[kWarps][32][V], sC[kWarps][32][V];
+    __shared__ float sP[kFixWarps * 32 * V], sC[kFixWarps * 32 * V];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t total = g.vblocks * g.NB * g.B;
-    for (int64_t id = blockIdx.x; id < total; id += gridDim.x) {
-    int64_t vb, j, b;
-    decode_block(g, id, vb, j, b);
-    const int64_t v = vb * 32 + lane;
+    const int64_t b = blockIdx.z;
+    const int64_t v = (int64_t)blockIdx.y * 32 + lane;
     const bool has = v < g.nvec;
     const int64_t d0 = v * V;
-    float st[V];         // what the entering state adds to this block: (product before it) * carry
-    bool live = false;
+    const float *bp_col = block_prod + b * g.NB * g.D + d0;
+    const float *bs_col = block_state + b * g.NB * g.D + d0;
+    float carry[V], run[V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) st[i] = 0.0f;
-    const int64_t o = (b * g.NB + j - 1) * g.D + d0;
-    if (has) {
-        float pr[V];
-        load_floats<V>(carry_in + b * g.D + d0, st);
-        if (j > 0) {
-            load_floats<V>(block_prod + o, pr);
+    for (int i = 0; i < V; ++i) { carry[i] = 0.0f; run[i] = 1.0f; }
+    if (has) load_floats<V>(carry_in + b * g.D + d0, carry);
+
+    int64_t done = 0;      // blocks whose product is already in `run`
+    for (int64_t j = blockIdx.x; j < g.NB; j += g.slots) {
+        // running product of the blocks before j
+        float more[V];
+        block_range_product<V>(bp_col, g.D, done, j, has, sP, more);
+        done = j;
+        float st[V];
+        bool live = false;
 #pragma unroll
-            for (int i = 0; i < V; ++i) st[i] *= pr[i];
+        for (int i = 0; i < V; ++i) {
+            run[i] *= more[i];
+            st[i] = run[i] * carry[i];
+            live |= has && (st[i] != 0.0f);
         }
+        if (!__syncthreads_or(live)) break;      // this block and all later ones already hold the exact result
+        if (has && j > 0) {
+            float bs[V];
+            load_floats<V>(bs_col + (j - 1) * g.D, bs);
 #pragma unroll
-        for (int i = 0; i < V; ++i) live |= (st[i] != 0.0f);
-    }
-    if (!__syncthreads_or(live)) continue;   // the zero-state result of this block is already exact
-    if (has && j > 0) {
-        float bs[V];
-        load_floats<V>(block_state + o, bs);
-#pragma unroll
-        for (int i = 0; i < V; ++i) st[i] += bs[i];
-    }
-    const int64_t r0 = j * g.R, r1 = min(g.T, r0 + g.R);
-    const int64_t per = (g.R + kWarps - 1) / kWarps;
-    const int64_t w0 = min(r1, r0 + warp * per), w1 = min(r1, w0 + per);
-    float P[V], C[V];
-#pragma unroll
-    for (int i = 0; i < V; ++i) { P[i] = 1.0f; C[i] = 0.0f; }
-    if (has) {
-#pragma unroll 4
-        for (int64_t t = w0; t < w1; ++t) {
-            float a[V], x[V];
-            Frag<T, V>::load(alpha.row(b, t) + d0, a);
-            Frag<T, V>::load(beta.row(b, t) + d0, x);
-#pragma unroll
-            for (int i = 0; i < V; ++i) { C[i] = fmaf(a[i], C[i], x[i]); P[i] *= a[i]; }
+            for (int i = 0; i < V; ++i) st[i] += bs[i];
         }
-    }
+        const int64_t r0 = j * g.R, r1 = min(g.T, r0 + g.R);
+        const int64_t per = (g.R + kFixWarps - 1) / kFixWarps;
+        const int64_t w0 = min(r1, r0 + warp * per), w1 = min(r1, w0 + per);
+        float P[V], C[V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) { sP[warp][lane][i] = P[i]; sC[warp][lane][i] = C[i]; }
-    __syncthreads();
-    if (has) {
-        for (int w = 0; w < warp; ++w) {
+        for (int i = 0; i < V; ++i) { P[i] = 1.0f; C[i] = 0.0f; }
+        if (has) {
+#pragma unroll 1
+            for (int64_t t0 = w0; t0 < w1; t0 += kFixRowBatch) {
+                typename Frag<T, V>::Raw ra[kFixRowBatch], rx[kFixRowBatch];
 #pragma unroll
-            for (int i = 0; i < V; ++i) st[i] = fmaf(sP[w][lane][i], st[i], sC[w][lane][i]);
+                for (int r = 0; r < kFixRowBatch; ++r) {
+                    if (t0 + r < w1) {
+                        ra[r] = Frag<T, V>::load_raw(alpha.row(b, t0 + r) + d0);
+                        rx[r] = Frag<T, V>::load_raw(beta.row(b, t0 + r) + d0);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < kFixRowBatch; ++r) {
+                    if (t0 + r < w1) {
+                        float a[V], x[V];
+                        Frag<T, V>::unpack(ra[r], a);
+                        Frag<T, V>::unpack(rx[r], x);
+#pragma unroll
+                        for (int i = 0; i < V; ++i) { C[i] = fmaf(a[i], C[i], x[i]); P[i] *= a[i]; }
+                    }
+                }
+            }
         }
-#pragma unroll 4
-        for (int64_t t = w0; t < w1; ++t) {
-            float a[V], x[V];
-            Frag<T, V>::load(alpha.row(b, t) + d0, a);
-            Frag<T, V>::load(beta.row(b, t) + d0, x);
+        __syncthreads();
 #pragma unroll
-            for (int i = 0; i < V; ++i) st[i] = fmaf(a[i], st[i], x[i]);
-            Frag<T, V>::store(h.row(b, t) + d0, st);
+        for (int i = 0; i < V; ++i) { sP[(warp * 32 + lane) * V + i] = P[i]; sC[(warp * 32 + lane) * V + i] = C[i]; }
+        __syncthreads();
+        if (has) {
+            for (int w = 0; w < warp; ++w) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) st[i] = fmaf(sP[(w * 32 + lane) * V + i], st[i], sC[(w * 32 + lane) * V + i]);
+            }
+#pragma unroll 1
+            for (int64_t t0 = w0; t0 < w1; t0 += kFixRowBatch) {
+                typename Frag<T, V>::Raw ra[kFixRowBatch], rx[kFixRowBatch];
+#pragma unroll
+                for (int r = 0; r < kFixRowBatch; ++r) {
+                    if (t0 + r < w1) {
+                        ra[r] = Frag<T, V>::load_raw(alpha.row(b, t0 + r) + d0);
+                        rx[r] = Frag<T, V>::load_raw(beta.row(b, t0 + r) + d0);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < kFixRowBatch; ++r) {
+                    if (t0 + r < w1) {
+                        float a[V], x[V];
+                        Frag<T, V>::unpack(ra[r], a);
+                        Frag<T, V>::unpack(rx[r], x);
+#pragma unroll
+                        for (int i = 0; i < V; ++i) st[i] = fmaf(a[i], st[i], x[i]);
+                        Frag<T, V>::store(h.row(b, t0 + r) + d0, st);
+                    }
+                }
+            }
         }
-    }
-    __syncthreads();      // the summaries are read above; the next candidate may overwrite them
     }
 }
 
-// Re-scan of the blocks that the arriving u still reaches (backward); same structure, rows taken
-// from the end of the block.
+// The same for the backward scan: u arrives after the last row, blocks are walked from the end.
 template <typename T, int V>
 __global__ void __launch_bounds__(kFixThreads)
 fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> grad, View<T> dalpha,
                View<T> dbeta, const float *__restrict__ u_in, const float *__restrict__ h_prev,
                const float *__restrict__ block_prod, const float *__restrict__ block_state, bool continuation) {
-    __shared__ float sP[kWarps][32][V], sC[kWarps][32][V];
+    __shared__ float sP[kFixWarps * 32 * V], sC[kFixWarps * 32 * V];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t total = g.vblocks * g.NB * g.B;
-    for (int64_t id = blockIdx.x; id < total; id += gridDim.x) {
-    int64_t vb, j, b;
-    decode_block(g, id, vb, j, b);
-    const int64_t v = vb * 32 + lane;
+    const int64_t b = blockIdx.z;
+    const int64_t v = (int64_t)blockIdx.y * 32 + lane;
     const bool has = v < g.nvec;
     const int64_t d0 = v * V;
-    float u[V];
-    bool live = false;
+    const float *bp_col = block_prod + b * g.NB * g.D + d0;
+    const float *bs_col = block_state + b * g.NB * g.D + d0;
+    float carry[V], run[V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) u[i] = 0.0f;
-    const bool lastb = j == g.NB - 1;
-    const int64_t o = (b * g.NB + j + 1) * g.D + d0;
-    if (has) {
-        float pr[V];
-        load_floats<V>(u_in + b * g.D + d0, u);
-        if (!lastb) {
-            load_floats<V>(block_prod + o, pr);
-#pragma unroll
-            for (int i = 0; i < V; ++i) u[i] *= pr[i];
-        }
-#pragma unroll
-        for (int i = 0; i < V; ++i) live |= (u[i] != 0.0f);
-    }
-    if (!__syncthreads_or(live)) continue;
-    if (has && !lastb) {
-        float bs[V];
-        load_floats<V>(block_state + o, bs);
-#pragma unroll
-        for (int i = 0; i < V; ++i) u[i] += bs[i];
-    }
-    const int64_t r0 = j * g.R, r1 = min(g.T, r0 + g.R);
-    const int64_t per = (g.R + kWarps - 1) / kWarps;
-    // warp 0 takes the last rows of the block, warp 1 the rows before them, ...
-    const int64_t w1 = max(r0, r1 - warp * per), w0 = max(r0, w1 - per);
-    float P[V], C[V];
-#pragma unroll
-    for (int i = 0; i < V; ++i) { P[i] = 1.0f; C[i] = 0.0f; }
-    if (has) {
-#pragma unroll 4
-        for (int64_t t = w1 - 1; t >= w0; --t) {
-            float a[V], x[V];
-            Frag<T, V>::load(alpha.row(b, t) + d0, a);
-            Frag<T, V>::load(grad.row(b, t) + d0, x);
-            const bool head = (t == 0) && !continuation;
-#pragma unroll
-            for (int i = 0; i < V; ++i) {
-                const float av = head ? 0.0f : a[i];
-                C[i] = av * (x[i] + C[i]);
-                P[i] *= av;
-            }
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < V; ++i) { sP[warp][lane][i] = P[i]; sC[warp][lane][i] = C[i]; }
-    __syncthreads();
-    if (has) {
-    for (int w = 0; w < warp; ++w) {
-#pragma unroll
-        for (int i = 0; i < V; ++i) u[i] = fmaf(sP[w][lane][i], u[i], sC[w][lane][i]);
-    }
-#pragma unroll 4
-    for (int64_t t = w1 - 1; t >= w0; --t) {
-        float a[V], gr[V], hp[V], da[V], dh[V];
-        Frag<T, V>::load(alpha.row(b, t) + d0, a);
-        Frag<T, V>::load(grad.row(b, t) + d0, gr);
-        if (t > 0) {
-            Frag<T, V>::load(h.row(b, t - 1) + d0, hp);
-        } else {
-#pragma unroll
-            for (int i = 0; i < V; ++i) hp[i] = (continuation && h_prev) ? h_prev[b * g.D + d0 + i] : 0.0f;
-        }
-        const bool head = (t == 0) && !continuation;
+    for (int i = 0; i < V; ++i) { carry[i] = 0.0f; run[i] = 1.0f; }
+    if (has) load_floats<V>(u_in + b * g.D + d0, carry);
+
+    int64_t done = g.NB;      // blocks [done, NB) are already in `run`
+    for (int64_t k = blockIdx.x; k < g.NB; k += g.slots) {
+        const int64_t j = g.NB - 1 - k;
+        float more[V];
+        block_range_product<V>(bp_col, g.D, j + 1, done, has, sP, more);
+        done = j + 1;
+        float u[V];
+        bool live = false;
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            dh[i] = gr[i] + u[i];
-            da[i] = head ? 0.0f : dh[i] * hp[i];
-            u[i] = (head ? 0.0f : a[i]) * dh[i];
+            run[i] *= more[i];
+            u[i] = run[i] * carry[i];
+            live |= has && (u[i] != 0.0f);
         }
-        Frag<T, V>::store(dbeta.row(b, t) + d0, dh);
-        Frag<T, V>::store(dalpha.row(b, t) + d0, da);
-    }
-    }
-    __syncthreads();      // the summaries are read above; the next candidate may overwrite them
+        if (!__syncthreads_or(live)) break;
+        if (has && j + 1 < g.NB) {
+            float bs[V];
+            load_floats<V>(bs_col + (j + 1) * g.D, bs);
+#pragma unroll
+            for (int i = 0; i < V; ++i) u[i] += bs[i];
+        }
+        const int64_t r0 = j * g.R, r1 = min(g.T, r0 + g.R);
+        const int64_t per = (g.R + kFixWarps - 1) / kFixWarps;
+        // warp 0 takes the last rows of the block, warp 1 the rows before them, ...
+        const int64_t w1 = max(r0, r1 - warp * per), w0 = max(r0, w1 - per);
+        float P[V], C[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) { P[i] = 1.0f; C[i] = 0.0f; }
+        if (has) {
+#pragma unroll 1
+            for (int64_t t1 = w1; t1 > w0; t1 -= kFixRowBatch) {
+                typename Frag<T, V>::Raw ra[kFixRowBatch], rx[kFixRowBatch];
+#pragma unroll
+                for (int r = 0; r < kFixRowBatch; ++r) {
+                    const int64_t t = t1 - 1 - r;
+                    if (t >= w0) {
+                        ra[r] = Frag<T, V>::load_raw(alpha.row(b, t) + d0);
+                        rx[r] = Frag<T, V>::load_raw(grad.row(b, t) + d0);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < kFixRowBatch; ++r) {
+                    const int64_t t = t1 - 1 - r;
+                    if (t >= w0) {
+                        const bool head = (t == 0) && !continuation;
+                        float a[V], x[V];
+                        Frag<T, V>::unpack(ra[r], a);
+                        Frag<T, V>::unpack(rx[r], x);
+#pragma unroll
+                        for (int i = 0; i < V; ++i) {
+                            const float av = head ? 0.0f : a[i];
+                            C[i] = av * (x[i] + C[i]);
+                            P[i] *= av;
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < V; ++i) { sP[(warp * 32 + lane) * V + i] = P[i]; sC[(warp * 32 + lane) * V + i] = C[i]; }
+        __syncthreads();
+        if (has) {
+            for (int w = 0; w < warp; ++w) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) u[i] = fmaf(sP[(w * 32 + lane) * V + i], u[i], sC[(w * 32 + lane) * V + i]);
+            }
+#pragma unroll 1
+            for (int64_t t1 = w1; t1 > w0; t1 -= kFixRowBatch3) {
+                typename Frag<T, V>::Raw ra[kFixRowBatch3], rg[kFixRowBatch3], rh[kFixRowBatch3];
+#pragma unroll
+                for (int r = 0; r < kFixRowBatch3; ++r) {
+                    const int64_t t = t1 - 1 - r;
+                    if (t >= w0) {
+                        ra[r] = Frag<T, V>::load_raw(alpha.row(b, t) + d0);
+                        rg[r] = Frag<T, V>::load_raw(grad.row(b, t) + d0);
+                        if (t > 0) rh[r] = Frag<T, V>::load_raw(h.row(b, t - 1) + d0);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < kFixRowBatch3; ++r) {
+                    const int64_t t = t1 - 1 - r;
+                    if (t >= w0) {
+                        const bool head = (t == 0) && !continuation;
+                        float a[V], gr[V], hp[V], da[V], dh[V];
+                        Frag<T, V>::unpack(ra[r], a);
+                        Frag<T, V>::unpack(rg[r], gr);
+                        if (t > 0) {
+                            Frag<T, V>::unpack(rh[r], hp);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < V; ++i)
+                                hp[i] = (continuation && h_prev) ? h_prev[b * g.D + d0 + i] : 0.0f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < V; ++i) {
+                            dh[i] = gr[i] + u[i];
+                            da[i] = head ? 0.0f : dh[i] * hp[i];
+                            u[i] = (head ? 0.0f : a[i]) * dh[i];
+                        }
+                        Frag<T, V>::store(dbeta.row(b, t) + d0, dh);
+                        Frag<T, V>::store(dalpha.row(b, t) + d0, da);
+                    }
+                }
+            }
+        }
     }
 }
 

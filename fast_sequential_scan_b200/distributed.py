@@ -6,12 +6,14 @@ Two partitionings, neither of which exists in the reference (it is a single-GPU 
   simply scans its slice; :func:`shard_channels` returns the slice as a view and nothing is
   exchanged.
 * **sequence-parallel** -- rank ``r`` holds rows ``[r*T/G, (r+1)*T/G)``.  :func:`seqpar_scan`
-  1. scans the local rows from a zero state, keeping the running product of ``alpha``;
+  1. scans the local rows from a zero state; the kernel also leaves, per block of rows, the block's
+     product of ``alpha`` and the state leaving it, and a small kernel folds the block products into
+     the product over all local rows;
   2. all-gathers the per-rank ``(product, last state)`` vectors (``2*B*D`` fp32 per rank);
   3. folds the maps of the ranks before it into the state entering its rows;
-  4. re-scans, from its corrected entering state, every block of rows that the carry still
-     reaches -- a block whose entering product times the carry is exactly zero already holds the
-     exact result and is skipped (for decaying gates: all but the first few thousand rows).
+  4. re-scans, from its corrected entering state, the blocks of rows that the carry still reaches:
+     block after block until (product of the blocks so far) x carry is exactly zero -- from there
+     on the zero-state result is already exact (for decaying gates: after a few thousand rows).
   The backward mirrors this with ``u_t = alpha_t * dh_t`` flowing from the later ranks.
 
 The numeric work is done by an ``ops`` object; :class:`NativeOps` (the product) calls the CUDA
@@ -35,10 +37,14 @@ def shard_channels(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
 
 
 class NativeOps:
-    """Local pieces on the GPU through the C ABI."""
+    """Local pieces on the GPU through the C ABI.  The small fp32 vectors and block tables of a step
+    live in buffers that are kept between calls (one set per shape): a training loop calls this
+    with the same shapes every step, and the kernels write the (product, state) pair straight into
+    the buffer that is handed to the all-gather."""
 
     def __init__(self, algo: Optional[int] = None):
         self.algo = algo
+        self._bufs: dict = {}
 
     def _algo_for(self, *tensors):
         """The kernel family that will really run: block sizes of the two families differ, so a
@@ -51,33 +57,52 @@ class NativeOps:
             return _lib.ALGO_CHUNKED
         return algo
 
+    def _buffers(self, which: str, alpha, algo):
+        """(send [2, B*D], block_prod [B, nb, D], block_state [B, nb, D], rows per block) for one direction."""
+        from . import sequential_scan_cuda as native
+        B, T, D = alpha.shape
+        key = (which, alpha.device, alpha.dtype, B, T, D, algo)
+        got = self._bufs.get(key)
+        if got is None:
+            R = native.block_rows(alpha.dtype, B, T, D, algo)
+            nb = -(-T // R)
+            f32 = dict(dtype=torch.float32, device=alpha.device)
+            got = self._bufs[key] = (torch.empty(2, B * D, **f32), torch.empty(B, nb, D, **f32),
+                                     torch.empty(B, nb, D, **f32), R)
+        return got
+
     def local_forward(self, alpha, beta, continuation: bool):
+        """Zero-state scan of this rank's rows.  Returns ``(h, send, blocks)``: ``send[0]`` is the product
+        of alpha over the rows, ``send[1]`` the state after the last row; ``blocks`` = per-block products,
+        per-block leaving states, rows per block."""
         from . import sequential_scan_cuda as native
         B, T, D = alpha.shape
         algo = self._algo_for(alpha, beta)
-        R = native.block_rows(alpha.dtype, B, T, D, algo)
-        nb = -(-T // R)
-        f32 = dict(dtype=torch.float32, device=alpha.device)
+        send, bp, bs, R = self._buffers("fwd", alpha, algo)
         h = torch.empty_like(alpha)
-        h_last, prod = torch.empty(B, D, **f32), torch.empty(B, D, **f32)
-        blocks = (torch.empty(B, nb, D, **f32), torch.empty(B, nb, D, **f32), R)     # products, states, rows
-        native.forward_into(alpha, beta, h, algo=algo, continuation=continuation, h_last=h_last, prod=prod,
-                            block_prod=blocks[0], block_state=blocks[1])
-        return h, h_last, prod, blocks
+        native.forward_into(alpha, beta, h, algo=algo, continuation=continuation, h_last=send[1].view(B, D),
+                            prod=send[0].view(B, D), block_prod=bp, block_state=bs)
+        return h, send, (bp, bs, R)
 
-    def local_backward(self, alpha, h, grad, continuation: bool, h_prev):
+    def local_backward(self, alpha, h, grad, continuation: bool, h_prev, prod):
+        """Zero-state reverse scan.  Returns ``(dalpha, dbeta, send, blocks)`` with ``send[0]`` the product of
+        alpha over the rows (the forward's, copied) and ``send[1]`` what row 0 hands to the rows before it."""
         from . import sequential_scan_cuda as native
         B, T, D = alpha.shape
         algo = self._algo_for(alpha, h, grad)
-        R = native.block_rows(alpha.dtype, B, T, D, algo)
-        nb = -(-T // R)
-        f32 = dict(dtype=torch.float32, device=alpha.device)
+        send, bp, bs, R = self._buffers("bwd", alpha, algo)
         da, db = torch.empty_like(alpha), torch.empty_like(alpha)
-        u_out = torch.empty(B, D, **f32)
-        blocks = (torch.empty(B, nb, D, **f32), torch.empty(B, nb, D, **f32), R)
+        send[0].copy_(prod.reshape(-1))
         native.backward_into(alpha, h, grad, da, db, algo=algo, continuation=continuation, h_prev=h_prev,
-                             u_out=u_out, block_prod=blocks[0], block_state=blocks[1])
-        return da, db, u_out, blocks
+                             u_out=send[1].view(B, D), block_prod=bp, block_state=bs)
+        return da, db, send, (bp, bs, R)
+
+    def gather_buffer(self, which: str, send, world: int):
+        key = ("gather", which, send.device, send.shape, world)
+        got = self._bufs.get(key)
+        if got is None:
+            got = self._bufs[key] = torch.empty(world, 2, send.shape[1], dtype=send.dtype, device=send.device)
+        return got
 
     def compose(self, pc, rank: int, backward: bool):
         from . import sequential_scan_cuda as native
@@ -101,43 +126,55 @@ def _world(group) -> int:
     return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
 
 
-def _gather(vec_a: torch.Tensor, vec_b: torch.Tensor, group) -> torch.Tensor:
-    """All-gather of this rank's two [B, D] fp32 vectors -> [world, 2, B*D]."""
-    mine = torch.stack([vec_a.reshape(-1), vec_b.reshape(-1)]).contiguous()
+def _gather(send: torch.Tensor, group, ops, which: str) -> torch.Tensor:
+    """All-gather of this rank's [2, B*D] fp32 (product, state) pair -> [world, 2, B*D]."""
     world = _world(group)
     if world == 1:
-        return mine.view(1, 2, mine.shape[1])
-    out = torch.empty((world * 2, mine.shape[1]), dtype=mine.dtype, device=mine.device)   # ranks concatenated
-    dist.all_gather_into_tensor(out, mine, group=group)
-    return out.view(world, 2, mine.shape[1])
+        return send.view(1, 2, send.shape[1])
+    make = getattr(ops, "gather_buffer", None)
+    out = make(which, send, world) if make else torch.empty((world, 2, send.shape[1]), dtype=send.dtype,
+                                                            device=send.device)
+    dist.all_gather_into_tensor(out.view(world * 2, send.shape[1]), send, group=group)
+    return out
 
 
-def seqpar_forward(alpha, beta, group=None, ops=None):
+def _no_mark(_name: str) -> None:
+    pass
+
+
+def seqpar_forward(alpha, beta, group=None, ops=None, mark=_no_mark):
     """Forward of the sequence-parallel scan on this rank's rows.  Returns ``(h, saved)`` where
-    ``saved`` carries what the backward needs (state entering the rows, local product)."""
+    ``saved`` carries what the backward needs (state entering the rows, local product).  ``mark``
+    is called with a phase name after each phase has been enqueued (for timing with events)."""
     ops = ops or NativeOps()
     rank, world = _rank(group), _world(group)
     B, T, D = alpha.shape
-    h, h_last, prod, blocks = ops.local_forward(alpha, beta, continuation=rank > 0)
-    pc = _gather(prod, h_last, group)
+    h, send, blocks = ops.local_forward(alpha, beta, continuation=rank > 0)
+    mark("fwd_local")
+    pc = _gather(send, group, ops, "fwd")
+    mark("fwd_gather")
     carry_in = None
     if rank > 0:
         carry_in = ops.compose(pc, rank, backward=False).reshape(B, D)
         ops.fixup_forward(alpha, beta, h, carry_in, blocks)
-    return h, dict(carry_in=carry_in, prod=prod)
+    mark("fwd_fixup")
+    return h, dict(carry_in=carry_in, prod=send[0].clone())
 
 
-def seqpar_backward(alpha, h, grad, saved, group=None, ops=None):
+def seqpar_backward(alpha, h, grad, saved, group=None, ops=None, mark=_no_mark):
     """Backward on this rank's rows: ``(dalpha, dbeta)`` for the local slices."""
     ops = ops or NativeOps()
     rank, world = _rank(group), _world(group)
     B, T, D = alpha.shape
     h_prev = saved["carry_in"]
-    da, db, u_out, blocks = ops.local_backward(alpha, h, grad, continuation=rank > 0, h_prev=h_prev)
-    pc = _gather(saved["prod"], u_out, group)
+    da, db, send, blocks = ops.local_backward(alpha, h, grad, continuation=rank > 0, h_prev=h_prev, prod=saved["prod"])
+    mark("bwd_local")
+    pc = _gather(send, group, ops, "bwd")
+    mark("bwd_gather")
     if rank < world - 1:
         u_in = ops.compose(pc, rank, backward=True).reshape(B, D)
         ops.fixup_backward(alpha, h, grad, da, db, u_in, h_prev, blocks, continuation=rank > 0)
+    mark("bwd_fixup")
     return da, db
 
 

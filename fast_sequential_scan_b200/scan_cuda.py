@@ -42,7 +42,7 @@ from typing import Any, Optional, Tuple
 import torch
 from torch.autograd import Function
 
-from .sequential_scan_cuda import (backward_into, forward_into, gates_reference, scan_backward,
+from .sequential_scan_cuda import (backward_into, forward_into, gates_backward, gates_forward, scan_backward,
                                    scan_backward_half, scan_forward, scan_forward_gated, scan_forward_half)
 
 BACKWARD_MODES = ("saved", "inplace", "recompute")
@@ -186,8 +186,10 @@ class GatedSequentialScan(Function):
     """``h = scan(alpha, beta)`` with ``alpha = exp(-8 softplus(lam) sigmoid(r))`` and
     ``beta = sqrt(1 - alpha^2) sigmoid(i) x`` (the RG-LRU of Hawk / Griffin, the use case the reference's
     README.md:3 names; the reference has no such entry point).  The forward computes the gates inside
-    the scan kernel, so alpha and beta never reach memory; the backward materialises them once with
-    torch, runs the reverse scan kernel and chains through the gate formulas with autograd."""
+    the scan kernel, so alpha and beta never reach memory.  The backward is three launches: the gate
+    kernel re-creates alpha with the forward's own arithmetic (so the reverse scan multiplies with
+    exactly the alpha that produced the saved ``h``), the reverse scan gives the gradients with
+    respect to alpha and beta, and the gate-backward kernel chains them to ``r, i, x, lam``."""
 
     @staticmethod
     def forward(ctx: Any, r: torch.Tensor, i: torch.Tensor, x: torch.Tensor, lam: torch.Tensor) -> torch.Tensor:
@@ -198,17 +200,14 @@ class GatedSequentialScan(Function):
     @staticmethod
     def backward(ctx: Any, grad_output: torch.Tensor):
         r, i, x, lam, h = ctx.saved_tensors
-        with torch.enable_grad():
-            leaves = [t.detach().requires_grad_() for t in (r, i, x, lam)]
-            alpha, beta = gates_reference(*leaves)
+        alpha, _ = gates_forward(r, None, None, lam, want_beta=False)
         bwd = scan_backward_half if h.dtype == torch.bfloat16 else scan_backward
-        alpha_grad, beta_grad = bwd(alpha.detach(), h, grad_output.contiguous())
-        needed = [k for k, need in enumerate(ctx.needs_input_grad) if need]
-        grads = torch.autograd.grad((alpha, beta), [leaves[k] for k in needed], (alpha_grad, beta_grad))
-        out = [None] * 4
-        for k, gk in zip(needed, grads):
-            out[k] = gk
-        return tuple(out)
+        # grad_beta may take h's place only if nobody else can see h; autograd hands out the saved tensor
+        alpha_grad, beta_grad = bwd(alpha, h, grad_output.contiguous())
+        dr, di, dx, dlam = gates_backward(r, i, x, lam, alpha_grad, beta_grad)
+        need = ctx.needs_input_grad
+        return (dr if need[0] else None, di if need[1] else None, dx if need[2] else None,
+                dlam.to(lam.dtype) if need[3] else None)
 
 
 def scan_gated(r: torch.Tensor, i: torch.Tensor, x: torch.Tensor, lam: torch.Tensor) -> torch.Tensor:

@@ -32,6 +32,19 @@ def default_algo() -> int:
     return _lib.ALGO_BY_NAME[name]
 
 
+_deterministic = os.environ.get("FSS_B200_DETERMINISTIC", "0") not in ("", "0")
+
+
+def set_deterministic(on: bool) -> bool:
+    """Ask the single-pass kernels for run-to-run identical results (``FSS_FLAG_DETERMINISTIC``: every
+    tile waits for its predecessor's final state instead of taking whichever summary is published
+    first).  Slower on long sequences.  Returns the previous setting; the environment variable
+    ``FSS_B200_DETERMINISTIC=1`` sets the initial one."""
+    global _deterministic
+    previous, _deterministic = _deterministic, bool(on)
+    return previous
+
+
 def _check_tensor(name: str, t: torch.Tensor, like: Optional[torch.Tensor], dtype: torch.dtype) -> None:
     if not isinstance(t, torch.Tensor):
         raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
@@ -92,7 +105,7 @@ def _ctx(device: torch.device, ws: workspace.Workspace, algo: Optional[int], fla
         ctx = ws.ctx = _lib.ScanCtx(ctypes.sizeof(_lib.ScanCtx), device.index if device.index is not None else -1,
                                     ws.stream_handle, ws.buf.data_ptr(), ws.buf.numel(), ws.status.data_ptr(), 0, 0)
     ctx.algo = default_algo() if algo is None else algo
-    ctx.flags = flags
+    ctx.flags = flags | (_lib.FLAG_DETERMINISTIC if _deterministic else 0)
     return ctx
 
 
@@ -203,16 +216,75 @@ def forward_gated_into(r, i, x, lam, h, *, continuation=False, h_in=None, h_last
     _lib.check(rc, "fss_scan_forward_gated")
 
 
+def _check_gate_inputs(r, i, x, lam):
+    dtype = r.dtype
+    if dtype not in _DTYPES:
+        raise RuntimeError(f"r: unsupported dtype {dtype} (bf16 or fp32)")
+    _check_tensor("r", r, None, dtype)
+    if i is not None:
+        _check_tensor("i", i, r, dtype)
+        _check_tensor("x", x, r, dtype)
+    D = r.shape[2]
+    if lam.dtype != torch.float32 or lam.shape != (D,) or lam.device != r.device or not lam.is_contiguous():
+        raise RuntimeError("lam: expected a contiguous fp32 vector of d_model values on the inputs' device")
+    return dtype
+
+
+def gates_forward(r, i, x, lam, want_beta: bool = True):
+    """``(alpha, beta)`` of the gated recurrence as the fused forward forms them internally (same
+    approximations, rounded to the I/O type); ``beta`` is None (and ``i``, ``x`` may be None) when
+    ``want_beta`` is False.  One elementwise kernel (``fss_gates_forward``)."""
+    dtype = _check_gate_inputs(r, i if want_beta else None, x if want_beta else None, lam)
+    B, T, D = r.shape
+    alpha = torch.empty(r.shape, dtype=dtype, device=r.device)
+    beta = torch.empty(r.shape, dtype=dtype, device=r.device) if want_beta else None
+    if r.numel() == 0:
+        return alpha, beta
+    rr = _rowwise(r)
+    ii, xx = (_rowwise(i), _rowwise(x)) if want_beta else (None, None)
+    ws = workspace.get(r.device, 1 << 16)
+    ctx = _ctx(r.device, ws, None)
+    vr, va = _view(rr), _view(alpha)
+    vi, vx, vb = (_view(ii), _view(xx), _view(beta)) if want_beta else (None, None, None)
+    ref = lambda v: ctypes.byref(v) if v is not None else None
+    rc = _lib.lib().fss_gates_forward(ctypes.byref(ctx), _DTYPES[dtype], B, T, D, ref(vr), ref(vi), ref(vx),
+                                      lam.data_ptr(), ref(va), ref(vb))
+    _lib.check(rc, "fss_gates_forward")
+    return alpha, beta
+
+
+def gates_backward(r, i, x, lam, grad_alpha, grad_beta):
+    """``(grad_r, grad_i, grad_x, grad_lam)`` from the scan's gradients with respect to alpha and beta
+    (``fss_gates_backward``: one elementwise kernel, per-channel atomic sums for ``grad_lam``)."""
+    dtype = _check_gate_inputs(r, i, x, lam)
+    _check_tensor("grad_alpha", grad_alpha, r, dtype)
+    _check_tensor("grad_beta", grad_beta, r, dtype)
+    B, T, D = r.shape
+    dr, di, dx = (torch.empty(r.shape, dtype=dtype, device=r.device) for _ in range(3))
+    dlam = torch.zeros(D, dtype=torch.float32, device=r.device)
+    if r.numel() == 0:
+        return dr, di, dx, dlam
+    tensors = [_rowwise(t) for t in (r, i, x, grad_alpha, grad_beta)] + [dr, di, dx]
+    views = [_view(t) for t in tensors]
+    ws = workspace.get(r.device, 1 << 16)
+    ctx = _ctx(r.device, ws, None)
+    rc = _lib.lib().fss_gates_backward(ctypes.byref(ctx), _DTYPES[dtype], B, T, D,
+                                       ctypes.byref(views[0]), ctypes.byref(views[1]), ctypes.byref(views[2]),
+                                       lam.data_ptr(), *[ctypes.byref(v) for v in views[3:]], dlam.data_ptr())
+    _lib.check(rc, "fss_gates_backward")
+    return dr, di, dx, dlam
+
+
 def scan_forward_gated(r, i, x, lam) -> torch.Tensor:
-    """Gated forward scan; falls back to torch gates + the plain scan when the layout is not
-    eligible for the fused kernel."""
+    """Gated forward scan; on layouts the fused kernel cannot take, the gate kernel followed by the
+    plain scan (the same gate arithmetic, two more tensor round trips)."""
     h = torch.empty(r.shape, dtype=r.dtype, device=r.device)
     try:
         forward_gated_into(r, i, x, lam, h)
     except _lib.FssError as e:
         if e.code != _lib.E_LAYOUT:
             raise
-        a, b = gates_reference(r, i, x, lam)
+        a, b = gates_forward(r, i, x, lam)
         forward_into(a, b, h)
     return h
 

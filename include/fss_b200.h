@@ -89,6 +89,15 @@ typedef struct fss_scan_ctx {
 /* Treat the tensors as rows s..s+T-1 of a longer sequence: row 0 DOES read alpha_0 (forward
  * h_0 = a_0*h_in + b_0; the returned product includes a_0) instead of the h_0 = b_0 rule.      */
 #define FSS_FLAG_CONTINUATION 1
+/* Run-to-run identical results from the single-pass kernels.  By default a tile takes the state
+ * that enters it from whichever is published first, its predecessor's final state or a fold of the
+ * summaries of several predecessors; the two associate the same sum differently, so the last bits
+ * of the fp32 state (rarely one ulp of a bf16 result) depend on timing.  With this flag a tile
+ * always waits for its predecessor's final state: one fixed association, bit-identical results in
+ * every run, at the price of a serial hand-over per row block (noticeable on long sequences).
+ * The chunked kernels are always deterministic.  The reference's kernels are, too: one thread walks
+ * a channel group from the first row to the last (csrc/include/sequential_scan_kernel_bf16.cuh:121-151). */
+#define FSS_FLAG_DETERMINISTIC 2
 /* Test hooks for the bounded waits of the single-pass kernels (no effect on results otherwise):
  * SHORT_WAITS lets every wait give up after a few thousand polls instead of ~a second;
  * MUTE_FIRST_BLOCK makes the tiles of the first row block publish no descriptors, so that the
@@ -97,24 +106,26 @@ typedef struct fss_scan_ctx {
 #define FSS_FLAG_TEST_SHORT_WAITS 0x100
 #define FSS_FLAG_TEST_MUTE_FIRST_BLOCK 0x200
 
-/* Optional per-column state vectors, all fp32, contiguous [B, D]; any may be NULL. */
+/* Optional per-column state vectors, all fp32, contiguous [B, D]; any may be NULL.  The single-pass
+ * kernels move them as 16-byte words: vectors that are not 16-byte aligned send an FSS_ALGO_AUTO
+ * call to the chunked kernels (FSS_ALGO_LOOKBACK: FSS_E_LAYOUT). */
 typedef struct fss_forward_state {
     const float *h_in; /* state entering row 0 (needs FSS_FLAG_CONTINUATION); NULL = 0          */
     float *h_last;     /* out: unrounded state after the last row                               */
     float *prod;       /* out: product of alpha over all rows (0 without FSS_FLAG_CONTINUATION) */
-    float *block_prod; /* out, [B, nblocks, D]: product of alpha over rows 0..(j+1)*R-1 for every
-                          block j of R = fss_block_rows() rows; feeds fss_seqpar_fixup_forward  */
-    float *block_state; /* out, [B, nblocks, D]: unrounded state after row (j+1)*R-1 (needs
-                          block_prod as well)                                                   */
+    float *block_prod; /* out, [B, nblocks, D]: product of alpha over the rows of block j, for every
+                          block j of R = fss_block_rows() rows (rows j*R .. (j+1)*R-1; alpha_0
+                          counts as 0 without FSS_FLAG_CONTINUATION); feeds the fix-up         */
+    float *block_state; /* out, [B, nblocks, D]: unrounded state after row (j+1)*R-1            */
 } fss_forward_state;
 
 typedef struct fss_backward_state {
     const float *u_in;   /* a_T*dh_T arriving from the rows after this tensor; NULL = 0         */
     const float *h_prev; /* h_{-1} for dalpha_0 (needs FSS_FLAG_CONTINUATION); NULL = dalpha_0=0 */
     float *u_out;        /* out: a_0*dh_0, what these rows hand to the rows before them         */
-    float *block_prod;   /* out, [B, nblocks, D]: product of alpha over rows j*R..T-1 for every
-                            block j of R = fss_block_rows() rows; feeds fss_seqpar_fixup_backward */
-    float *block_state;  /* out, [B, nblocks, D]: u = a*dh handed on by row j*R (needs block_prod) */
+    float *block_prod;   /* out, [B, nblocks, D]: product of alpha over the rows of block j (the same
+                            values the forward scan writes); feeds fss_seqpar_fixup_backward      */
+    float *block_state;  /* out, [B, nblocks, D]: u = a*dh handed on by row j*R                    */
 } fss_backward_state;
 
 /* ---- library information ------------------------------------------------------------- */
@@ -182,6 +193,23 @@ int fss_scan_forward_gated(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_
                            const fss_view *r, const fss_view *i, const fss_view *x,
                            const float *lambda, const fss_view *h, const fss_forward_state *state);
 
+/* The same gate formulas outside the scan, for the backward of a gated scan (no counterpart in the
+ * reference).  fss_gates_forward writes alpha (and beta, unless beta is NULL -- i and x are then
+ * unused and may be NULL) exactly as fss_scan_forward_gated forms them internally: the same
+ * approximations and the same rounding to `dtype`, so a reverse scan run on this alpha multiplies
+ * with bit for bit the values the forward scanned with. */
+int fss_gates_forward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                      const fss_view *r, const fss_view *i, const fss_view *x, const float *lambda,
+                      const fss_view *alpha, const fss_view *beta);
+/* Chain rule through the gates: from the scan's grad_alpha and grad_beta to grad_r, grad_i, grad_x
+ * (type `dtype`) and grad_lambda[D] (fp32; ADDED to with atomic operations, so the caller zeroes it
+ * first and its last bits depend on the order of the additions).  The derivatives are taken at the
+ * unrounded fp32 gate values. */
+int fss_gates_backward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                       const fss_view *r, const fss_view *i, const fss_view *x, const float *lambda,
+                       const fss_view *grad_alpha, const fss_view *grad_beta, const fss_view *grad_r,
+                       const fss_view *grad_i, const fss_view *grad_x, float *grad_lambda);
+
 /* ---- sequence-parallel pieces (no counterpart in the reference, which never splits T) ---- */
 /* Rows per block of the block_prod outputs for this problem and algorithm (> 0). */
 int64_t fss_block_rows(int dtype, int64_t B, int64_t T, int64_t D, int algo);
@@ -192,18 +220,21 @@ int64_t fss_block_rows(int dtype, int64_t B, int64_t T, int64_t D, int algo);
  *             ranks rank+1..world-1.  One small launch on ctx->stream. */
 int fss_seqpar_compose(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n,
                        const float *pc, float *carry_in);
-/* Correct a zero-state forward scan for the state carry_in that really enters row 0: every block
- * whose entering product times carry_in is not exactly zero is re-scanned from its true entering
- * state  block_state[j-1] + block_prod[j-1]*carry_in  (one rounding per stored value, like the
- * undivided scan); all other blocks already hold the exact result and are skipped.  block_prod,
- * block_state, block_rows are what the zero-state scan wrote.  Needs FSS_FLAG_CONTINUATION. */
+/* Correct a zero-state forward scan for the state carry_in that really enters row 0: block j is
+ * re-scanned from its true entering state
+ *     block_state[j-1] + (block_prod[0] * ... * block_prod[j-1]) * carry_in
+ * (one rounding per stored value, like the undivided scan) for as long as the second term is not
+ * exactly zero for some channel of a group of 32 channel vectors; from the first block where it is
+ * zero on, the column already holds the exact result and is left alone.  block_prod, block_state,
+ * block_rows are what the zero-state scan wrote.  Needs FSS_FLAG_CONTINUATION. */
 int fss_seqpar_fixup_forward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
                              const fss_view *alpha, const fss_view *beta, const fss_view *h,
                              const float *carry_in, const float *block_prod, const float *block_state,
                              int64_t block_rows);
-/* The same for the backward scan and the u_in that really arrives after the last row: blocks
- * whose leaving product times u_in is non-zero are re-scanned from
- * block_state[j+1] + block_prod[j+1]*u_in.  h_prev is h_{-1} (NULL = 0; used with
+/* The same for the backward scan and the u_in that really arrives after the last row: blocks are
+ * walked from the last one down and re-scanned from
+ *     block_state[j+1] + (block_prod[j+1] * ... * block_prod[nblocks-1]) * u_in
+ * while that second term is non-zero.  h_prev is h_{-1} (NULL = 0; used with
  * FSS_FLAG_CONTINUATION, without it row 0 keeps dalpha_0 = 0). */
 int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
                               const fss_view *alpha, const fss_view *h, const fss_view *grad_out,

@@ -247,6 +247,22 @@ def torch_loop_scan(alpha, beta):
     return torch.stack(rows, dim=1)
 
 
+def torch_slice_scan(alpha, beta):
+    """The recurrence with the operation sequence of the reference's sequential PyTorch scan
+    (sequential_scan/common.py:46-59): a preallocated output, and per row one multiply-add on the
+    running state followed by a slice assignment into the output.  Autograd differentiates through
+    the slice assignments, which is what makes the reference's CPU backward slow; this variant exists
+    so that the timed CPU baseline pays the same cost.  Values are identical to torch_loop_scan."""
+    import torch
+    out = torch.empty_like(alpha)
+    state = beta[:, 0, :]
+    out[:, 0, :] = state
+    for t in range(1, alpha.shape[1]):
+        state = state * alpha[:, t, :] + beta[:, t, :]
+        out[:, t, :] = state
+    return out
+
+
 # ------------------------------------------------------------------ error metrics
 
 def mixed_error_ratio(x, ref, tol: float) -> float:

@@ -32,17 +32,18 @@ class OracleOps:
             a[:, 0] = 0.0
         h = np.zeros_like(a)
         state = np.zeros((B, D), np.float32)
-        run = np.ones((B, D), np.float32)
+        total = np.ones((B, D), np.float32)
         nb = -(-T // self.R)
-        bp, bs = np.zeros((B, nb, D), np.float32), np.zeros((B, nb, D), np.float32)
+        bp, bs = np.ones((B, nb, D), np.float32), np.zeros((B, nb, D), np.float32)
         for t in range(T):
             state = a[:, t] * state + b[:, t]
-            run = run * a[:, t]
+            total = total * a[:, t]
+            bp[:, t // self.R] *= a[:, t]              # the block's own product
             h[:, t] = state
-            if (t + 1) % self.R == 0 or t == T - 1:
-                bp[:, t // self.R], bs[:, t // self.R] = run, state
+            bs[:, t // self.R] = state                 # ends as the state leaving the block
         blocks = (torch.from_numpy(bp), torch.from_numpy(bs), self.R)
-        return torch.from_numpy(h), torch.from_numpy(state.copy()), torch.from_numpy(run.copy()), blocks
+        send = torch.from_numpy(np.stack([total.reshape(-1), state.reshape(-1)]))
+        return torch.from_numpy(h), send, blocks
 
     @staticmethod
     def _backward_rows(a, hh, g, da, db, u, rows, continuation, h_prev):
@@ -54,22 +55,22 @@ class OracleOps:
             u = (a[:, t] if (t > 0 or continuation) else 0.0) * dh
         return u
 
-    def local_backward(self, alpha, h, grad, continuation, h_prev):
+    def local_backward(self, alpha, h, grad, continuation, h_prev, prod):
         a, hh, g = alpha.numpy(), h.numpy(), grad.numpy()
         B, T, D = a.shape
         da, db = np.zeros_like(a), np.zeros_like(a)
         u = np.zeros((B, D), np.float32)
-        run = np.ones((B, D), np.float32)
         nb = -(-T // self.R)
-        bp, bs = np.zeros((B, nb, D), np.float32), np.zeros((B, nb, D), np.float32)
+        bp, bs = np.ones((B, nb, D), np.float32), np.zeros((B, nb, D), np.float32)
         for j in range(nb - 1, -1, -1):
             rows = range(min(T, (j + 1) * self.R) - 1, j * self.R - 1, -1)
             u = self._backward_rows(a, hh, g, da, db, u, rows, continuation, h_prev)
             for t in rows:
-                run = run * (a[:, t] if (t > 0 or continuation) else 0.0)
-            bp[:, j], bs[:, j] = run, u
+                bp[:, j] *= (a[:, t] if (t > 0 or continuation) else 0.0)
+            bs[:, j] = u
         blocks = (torch.from_numpy(bp), torch.from_numpy(bs), self.R)
-        return torch.from_numpy(da), torch.from_numpy(db), torch.from_numpy(u.copy()), blocks
+        send = torch.stack([prod.reshape(-1), torch.from_numpy(u.reshape(-1).copy())])
+        return torch.from_numpy(da), torch.from_numpy(db), send, blocks
 
     def compose(self, pc, rank, backward):
         pc = pc.numpy()
@@ -84,14 +85,16 @@ class OracleOps:
         bp, bs, R = blocks
         a, b, hh = alpha.numpy(), beta.numpy(), h.numpy()        # hh shares memory with h: in place
         T = a.shape[1]
+        run = np.ones_like(carry_in.numpy())
         for j in range(-(-T // R)):
-            w = (bp[:, j - 1].numpy() if j else 1.0) * carry_in.numpy()
+            w = run * carry_in.numpy()                 # (product of the blocks before j) * carry
             if not np.any(w):
-                continue
+                break
             state = (bs[:, j - 1].numpy() if j else 0.0) + w
             for t in range(j * R, min(T, (j + 1) * R)):
                 state = a[:, t] * state + b[:, t]
                 hh[:, t] = state
+            run = run * bp[:, j].numpy()
 
     def fixup_backward(self, alpha, h, grad, da, db, u_in, h_prev, blocks, continuation):
         bp, bs, R = blocks
@@ -99,14 +102,15 @@ class OracleOps:
         T = a.shape[1]
         nb = -(-T // R)
         dan, dbn = da.numpy(), db.numpy()
-        for j in range(nb):
-            last = j == nb - 1
-            w = (1.0 if last else bp[:, j + 1].numpy()) * u_in.numpy()
+        run = np.ones_like(u_in.numpy())
+        for j in range(nb - 1, -1, -1):
+            w = run * u_in.numpy()                     # (product of the blocks after j) * u_in
             if not np.any(w):
-                continue
-            u = (0.0 if last else bs[:, j + 1].numpy()) + w
+                break
+            u = (0.0 if j == nb - 1 else bs[:, j + 1].numpy()) + w
             rows = range(min(T, (j + 1) * R) - 1, j * R - 1, -1)
             self._backward_rows(a, hh, g, dan, dbn, u, rows, continuation, h_prev)
+            run = run * bp[:, j].numpy()
 
 
 def _worker(rank, world, port, mode, out_dir):
@@ -157,6 +161,55 @@ def test_multi_rank_scan_matches_single_process(tmp_path, mode, world):
         world = 4      # 24 channels split evenly
     mp.spawn(_worker, args=(world, _free_port(), mode, str(tmp_path)), nprocs=world, join=True)
     assert sorted(p.name for p in tmp_path.iterdir()) == [f"rank{r}.ok" for r in range(world)]
+
+
+def _absent_rank_worker(rank, world, port, out_dir):
+    """Rank 1 leaves before the exchange (a host-side failure: it raises between steps, with nothing in
+    flight); rank 0 must learn of it through the short process-group timeout of its all-gather instead
+    of waiting forever."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    from fast_sequential_scan_b200 import distributed as fd
+    gen = torch.Generator().manual_seed(5)
+    a = 0.6 + 0.39 * torch.rand(1, 64, 8, generator=gen)
+    b = torch.randn(1, 64, 8, generator=gen)
+    try:
+        if rank == 1:
+            Path(out_dir, "rank1.left").write_text("x")
+            return                                   # never joins the gather
+        try:
+            fd.seqpar_forward(a, b, None, OracleOps())
+            Path(out_dir, "rank0.unnoticed").write_text("x")
+        except Exception as e:                       # gloo reports the missing peer as a RuntimeError
+            Path(out_dir, "rank0.detected").write_text(type(e).__name__)
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_a_rank_that_skips_the_exchange_is_detected(tmp_path):
+    mp.spawn(_absent_rank_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    names = sorted(p.name for p in tmp_path.iterdir())
+    assert names == ["rank0.detected", "rank1.left"], names
+
+
+def test_compose_rejects_a_rank_outside_the_world():
+    """Argument checks of the carry composition need no device: a rank index outside the gathered
+    table, or an empty world, is refused before anything is launched."""
+    import ctypes
+    from fast_sequential_scan_b200 import _lib
+    L = _lib.lib()
+    ctx = _lib.ScanCtx(ctypes.sizeof(_lib.ScanCtx), -1, None, None, 0, None, 0, 0)
+    buf = (ctypes.c_float * 64)()
+    ptr = ctypes.addressof(buf)
+    assert L.fss_seqpar_compose(ctypes.byref(ctx), 0, 4, 4, 8, ptr, ptr) == -2      # rank == world
+    assert L.fss_seqpar_compose(ctypes.byref(ctx), 0, 0, 0, 8, ptr, ptr) == -2      # empty world
+    assert L.fss_seqpar_compose(ctypes.byref(ctx), 1, 4, -1, 8, ptr, ptr) == -2     # negative rank
+    assert L.fss_seqpar_compose(ctypes.byref(ctx), 0, 4, 1, 8, None, ptr) == -1     # missing table
+    assert L.fss_seqpar_compose(ctypes.byref(ctx), 0, 4, 1, 0, ptr, ptr) == 0       # nothing to do
 
 
 def test_shard_channels_rejects_uneven_split():

@@ -399,21 +399,59 @@ def test_gated_forward_matches_the_oracle(shape, fp32):
         assert_parity(h.float().cpu(), h_unfused.float().cpu(), tol, "gated vs unfused")
 
 
-def test_gated_scan_gradients_and_state():
-    """Backward of the gated scan (torch gates + reverse-scan kernel + autograd through the gate
-    formulas) against autograd of the all-torch formulation; boundary state through the C ABI."""
+def _gated_reference_f64(r, i, x, lam, g):
+    """h and the gradients of the gated scan from float64 autograd of the formulas on the CPU."""
+    leaves = [t.detach().cpu().double().requires_grad_() for t in (r, i, x, lam)]
+    rr, ii, xx, ll = leaves
+    a = torch.exp(-8.0 * torch.nn.functional.softplus(ll) * torch.sigmoid(rr))
+    b = torch.sqrt(1.0 - a * a) * torch.sigmoid(ii) * xx
+    h = oracle.torch_loop_scan(a, b)
+    h.backward(g.detach().cpu().double())
+    return h.detach(), [t.grad for t in leaves]
+
+
+@pytest.mark.parametrize("lam_range", [(-4.3, -0.5), (4.0, 6.0)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_gated_scan_gradients(dtype, lam_range):
+    """Backward of the gated scan (gate kernel with the forward's own arithmetic, reverse-scan kernel,
+    gate-backward kernel) against float64 autograd of the formulas.  The second lambda range gives
+    exponent scales of -32 ... -48, where an alpha re-created with different arithmetic than the
+    forward's would differ by more than a rounding."""
+    pkg, native, _ = _mods()
+    gen = torch.Generator().manual_seed(9)
+    B, T, D = 2, 384, 256
+    dt = torch.float32 if dtype == "f32" else torch.bfloat16
+    lam = (lam_range[0] + (lam_range[1] - lam_range[0]) * torch.rand(D, generator=gen)).cuda()
+    r, i, x = (torch.randn(B, T, D, generator=gen).to(dt).cuda() for _ in range(3))
+    g = torch.randn(B, T, D, generator=gen).to(dt).cuda()
+    leaves = [t.clone().requires_grad_() for t in (r, i, x, lam)]
+    h = pkg.scan_gated(*leaves)
+    h.backward(g)
+    pkg.check_status()
+    h_ref, grads_ref = _gated_reference_f64(r, i, x, lam, g)
+    if dtype == "f32":
+        assert_parity(h.detach().cpu(), h_ref.float(), 1e-4, "gated h")
+        for got, ref, name in zip(leaves, grads_ref, "r i x lam".split()):
+            assert_parity(got.grad.cpu(), ref.float(), 1e-4, f"d{name}")
+    else:
+        # bf16 storage: every stored value carries 2^-9 of rounding and the gradients are formed
+        # from the rounded h, so the yardstick is the reference's own one for bf16, relative L2
+        assert_parity(h.detach().cpu(), h_ref.float(), 2e-2, "gated h")
+        for got, ref, name in zip(leaves, grads_ref, "r i x lam".split()):
+            err = oracle.relative_l2(got.grad.float().cpu(), ref.float())
+            assert err < 2e-2, (name, err)
+    # the gate kernel re-creates exactly the alpha (and beta) the fused forward scanned with
+    a_k, b_k = native.gates_forward(r, i, x, lam)
+    h_two = (pkg.scan_cu_single if dtype == "f32" else pkg.scan_cu)(a_k, b_k)
+    assert_same_up_to_association(h_two, h.detach(), "gate kernel + plain scan vs fused forward")
+
+
+def test_gated_scan_state():
+    """Boundary state of the gated entry point through the C ABI."""
     pkg, native, _ = _mods()
     from fast_sequential_scan_b200.workloads import Workload, make_gate_inputs
     w = Workload("t", 2, 512, 256, "hawk", "f32")
     r, i, x, lam = (t.cuda() for t in make_gate_inputs(w, "cpu", seed=9))
-    g = torch.randn(r.shape, generator=torch.Generator().manual_seed(1)).cuda()
-    leaves = [t.clone().requires_grad_() for t in (r, i, x, lam)]
-    pkg.scan_gated(*leaves).backward(g)
-    ref_leaves = [t.clone().requires_grad_() for t in (r, i, x, lam)]
-    a, b = native.gates_reference(*ref_leaves)
-    pkg.scan_cu_single(a, b).backward(g)
-    for got, ref, name in zip(leaves, ref_leaves, "r i x lam".split()):
-        assert_parity(got.grad.cpu(), ref.grad.cpu(), 1e-4, f"d{name}")
     # boundary state of the gated entry point against the oracle: the float64 gate formulas rounded
     # once, scanned by the oracle from a non-zero h0; and two halves chained through h_last -> h_in
     a_ref, b_ref = oracle.gated_alpha_beta(r.cpu(), i.cpu(), x.cpu(), lam.cpu())
@@ -477,32 +515,40 @@ def test_sequence_parallel_pieces_on_one_gpu(dtype, algo):
     a = (lo + span * torch.rand(shape, generator=gen, device="cuda")).to(dt)
     b = torch.randn(shape, generator=gen, device="cuda").to(dt)
     g = torch.randn(shape, generator=gen, device="cuda").to(dt)
-    ops = NativeOps(_algo_id(algo))
+    ops = [NativeOps(_algo_id(algo)) for _ in range(world)]       # one per played rank: each keeps its own buffers
     rows = [slice(r * Tl, (r + 1) * Tl) for r in range(world)]
     # forward
-    loc = [ops.local_forward(a[:, rows[r]], b[:, rows[r]], continuation=r > 0) for r in range(world)]
-    pc = torch.stack([torch.stack([l[2].reshape(-1), l[1].reshape(-1)]) for l in loc]).contiguous()
+    loc = [ops[r].local_forward(a[:, rows[r]], b[:, rows[r]], continuation=r > 0) for r in range(world)]
+    pc = torch.stack([l[1] for l in loc]).contiguous()          # [world, 2, B*D]: (product, last state) per rank
+    # the products the ranks exchange are the products of their rows (rank 0: alpha_0 counts as 0)
+    for r in range(world):
+        want = a[:, rows[r]].float().prod(dim=1)
+        if r == 0:
+            want = torch.zeros_like(want)
+        got = loc[r][1][0].view(B, D)
+        assert torch.allclose(got, want, rtol=1e-3 if dtype == "bf16" else 1e-4, atol=1e-30), f"product of rank {r}"
     hs, carries = [], []
     for r in range(world):
-        h, _, _, blocks = loc[r]
+        h, _, blocks = loc[r]
         carry = None
         if r > 0:
-            carry = ops.compose(pc, r, backward=False).reshape(B, D)
-            ops.fixup_forward(a[:, rows[r]], b[:, rows[r]], h, carry, blocks)
+            carry = ops[r].compose(pc, r, backward=False).reshape(B, D)
+            ops[r].fixup_forward(a[:, rows[r]], b[:, rows[r]], h, carry, blocks)
         hs.append(h); carries.append(carry)
     h_all = torch.cat(hs, dim=1)
     h_ref, _, _ = oracle.reference_values(a, b, None)
     assert_parity(h_all, h_ref, tol, "sequence-parallel h")
     # backward (uses the stored h of every rank, like the undivided backward uses the saved h)
-    bl = [ops.local_backward(a[:, rows[r]], hs[r], g[:, rows[r]], continuation=r > 0, h_prev=carries[r])
+    bl = [ops[r].local_backward(a[:, rows[r]], hs[r], g[:, rows[r]], continuation=r > 0, h_prev=carries[r],
+                                prod=loc[r][1][0])
           for r in range(world)]
-    pcb = torch.stack([torch.stack([loc[r][2].reshape(-1), bl[r][2].reshape(-1)]) for r in range(world)]).contiguous()
+    pcb = torch.stack([x[2] for x in bl]).contiguous()
     das, dbs = [], []
     for r in range(world):
         da, db, _, blocks = bl[r]
         if r < world - 1:
-            u_in = ops.compose(pcb, r, backward=True).reshape(B, D)
-            ops.fixup_backward(a[:, rows[r]], hs[r], g[:, rows[r]], da, db, u_in, carries[r], blocks, r > 0)
+            u_in = ops[r].compose(pcb, r, backward=True).reshape(B, D)
+            ops[r].fixup_backward(a[:, rows[r]], hs[r], g[:, rows[r]], da, db, u_in, carries[r], blocks, r > 0)
         das.append(da); dbs.append(db)
     da_ref, db_ref = oracle.scan_backward_f32(a.float().cpu().numpy(), h_all.float().cpu().numpy(),
                                               g.float().cpu().numpy())
@@ -632,6 +678,40 @@ def test_outputs_stay_inside_their_views(shape, dtype, algo):
         a.float().cpu().numpy(), h.float().cpu().numpy(), g.float().cpu().numpy()))
     assert_parity(db, o_db, tol, "dbeta")
     assert_parity(da, o_da, tol, "dalpha")
+
+
+@pytest.mark.parametrize("shape", [(8, 2048, 1024), (1, 32768, 512)])
+def test_deterministic_flag_gives_identical_bits_in_every_launch(shape):
+    """FSS_FLAG_DETERMINISTIC: a tile always starts from its predecessor's final state, so the
+    association is fixed and 20 launches of the single-pass kernels agree bit for bit (this is the
+    one place where separate launches are compared with torch.equal), and with the oracle."""
+    pkg, native, _lib = _mods()
+    gen = torch.Generator().manual_seed(13)
+    a = (0.5 + 0.4999 * torch.rand(shape, generator=gen)).bfloat16().cuda()
+    b = torch.randn(shape, generator=gen).bfloat16().cuda()
+    g = torch.randn(shape, generator=gen).bfloat16().cuda()
+    previous = native.set_deterministic(True)
+    try:
+        first = None
+        for it in range(20):
+            h, da, db = torch.empty_like(a), torch.empty_like(a), torch.empty_like(a)
+            native.forward_into(a, b, h, algo=_lib.ALGO_LOOKBACK)
+            native.backward_into(a, h, g, da, db, algo=_lib.ALGO_LOOKBACK)
+            if first is None:
+                first = (h, da, db)
+            else:
+                for x, y, what in zip((h, da, db), first, ("h", "dalpha", "dbeta")):
+                    assert torch.equal(x, y), f"launch {it}: {what} differs from launch 0"
+        pkg.check_status()
+    finally:
+        native.set_deterministic(previous)
+    h, da, db = first
+    o_h, _, _ = oracle.reference_values(a, b, None)
+    assert_parity(h, o_h, BF16_TOL, "h")
+    o_da, o_db = (torch.from_numpy(x) for x in oracle.scan_backward_f32(
+        a.float().cpu().numpy(), h.float().cpu().numpy(), g.float().cpu().numpy()))
+    assert_parity(db, o_db, BF16_TOL, "dbeta")
+    assert_parity(da, o_da, BF16_TOL, "dalpha")
 
 
 def test_launches_on_two_streams_are_ordered_and_correct():

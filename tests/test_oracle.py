@@ -113,3 +113,44 @@ def test_gate_formulas_of_the_oracle_against_torch():
     rb, ib, xb = (t.to(torch.bfloat16) for t in (r, i, x))
     ab, bb = oracle.gated_alpha_beta(rb, ib, xb, lam)
     assert ab.dtype == torch.bfloat16 and bb.dtype == torch.bfloat16
+
+
+@pytest.mark.parametrize("name", golden_cases("f32_"))
+def test_slice_assignment_loop_matches_golden(name):
+    """The restatement with the reference's own operation sequence (a slice assignment per row,
+    sequential_scan/common.py:46-59), which the bench times on the host cores, gives the golden
+    values bit for bit."""
+    z = load_golden(name)
+    a = torch.from_numpy(z["alpha"]).requires_grad_(True)
+    b = torch.from_numpy(z["beta"]).requires_grad_(True)
+    h = oracle.torch_slice_scan(a, b)
+    h.backward(torch.from_numpy(z["grad"]))
+    assert torch.equal(h.detach(), torch.from_numpy(z["h"]))
+    assert torch.equal(b.grad, torch.from_numpy(z["dbeta"]))
+    da = a.grad if a.grad is not None else torch.zeros_like(a)
+    assert torch.equal(da, torch.from_numpy(z["dalpha"]))
+
+
+def test_state_carrying_oracle_against_autograd_of_the_loop():
+    """reference_values_with_state (the C oracle on a sequence extended by one row) against autograd
+    of the sequential loop started from h0, with a gradient for the final state."""
+    gen = torch.Generator().manual_seed(0)
+    B, T, D = 2, 50, 8
+    a, b, g = torch.rand(B, T, D, generator=gen), torch.randn(B, T, D, generator=gen), torch.randn(B, T, D, generator=gen)
+    h0, g_last = torch.randn(B, D, generator=gen), torch.randn(B, D, generator=gen)
+    ar, br, h0r = (t.clone().requires_grad_() for t in (a, b, h0))
+    state, rows = h0r, []
+    for t in range(T):
+        state = state * ar[:, t] + br[:, t]
+        rows.append(state)
+    h = torch.stack(rows, 1)
+    torch.autograd.backward((h, h[:, -1]), (g, g_last))
+    got = oracle.reference_values_with_state(a, b, g, h0, g_last)
+    for x, y, what in zip(got, (h.detach(), h[:, -1].detach(), ar.grad, br.grad, h0r.grad),
+                          ("h", "h_last", "dalpha", "dbeta", "dh0")):
+        assert torch.allclose(x, y, rtol=1e-5, atol=1e-6), what
+    # without h0 it is the plain scan
+    plain = oracle.reference_values_with_state(a, b, g)
+    h_ref, da_ref, db_ref = oracle.reference_values(a, b, g)
+    assert torch.equal(plain[0], h_ref) and torch.equal(plain[2], da_ref) and torch.equal(plain[3], db_ref)
+    assert plain[4] is None

@@ -502,7 +502,7 @@ def strong_record(hs, native, fd, wl, w, dev, rank, world, algo, peak, steps, re
             "parity": "h, dalpha, dbeta of every rank's shard (first 32 channels, all rows) against the CPU checker"}
 
 
-def seqpar_record(hs, native, fd, wl, dev, rank, world, peak, steps, warmup):
+def seqpar_record(hs, native, fd, wl, dev, rank, world, peak, steps, warmup, exchange="collective"):
     """Long-context configuration: every rank holds 65,536 rows of one (65,536*N)-row sequence.
     A step is the sequence-parallel forward (local scan, all-gather of the carries, fix-up) plus the
     mirrored backward.  Also times each rank's undivided scan of the same rows, splits the step into
@@ -511,7 +511,7 @@ def seqpar_record(hs, native, fd, wl, dev, rank, world, peak, steps, warmup):
     from oracle import oracle
     w = wl.CONFIGS["c5_rank"]
     a, b, g = wl.make_inputs(w, dev, seed=rank)
-    ops = fd.NativeOps()
+    ops = fd.NativeOps(exchange=exchange)
     B, T, D = a.shape
 
     def step():
@@ -531,25 +531,27 @@ def seqpar_record(hs, native, fd, wl, dev, rank, world, peak, steps, warmup):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = stats([float(x) for x in t.tolist()])
 
-    # phases (CUDA events on the compute stream, mean over a few steps, max over ranks)
-    names = []
-    acc = {}
-    for it in range(6):
-        marks = []
-        mark = lambda name: marks.append((name, _event(torch)))
-        mark("start")
+    # phases: events recorded on the compute stream while eight steps run back to back (no host
+    # synchronisation in between, so the timeline is the one of the timed loop); mean over the last
+    # six steps, per rank, then max and min over ranks
+    marks = []
+    mark = lambda name: marks.append((name, _event(torch)))
+    mark("start")
+    for it in range(8):
         h, saved = fd.seqpar_forward(a, b, None, ops, mark=mark)
         fd.seqpar_backward(a, h, g, saved, None, ops, mark=mark)
-        torch.cuda.synchronize()
-        if it:
-            for (_, e0), (n1, e1) in zip(marks[:-1], marks[1:]):
-                acc[n1] = acc.get(n1, 0.0) + e0.elapsed_time(e1) / 5
-                if n1 not in names:
-                    names.append(n1)
+    torch.cuda.synchronize()
     all_names = ["fwd_local", "fwd_gather", "fwd_fixup", "bwd_local", "bwd_gather", "bwd_fixup"]
-    pt = torch.tensor([acc.get(n, 0.0) for n in all_names], device=dev, dtype=torch.float64)
-    dist.all_reduce(pt, op=dist.ReduceOp.MAX)
-    phases = {n: float(v) for n, v in zip(all_names, pt.tolist())}
+    acc = {n: 0.0 for n in all_names}
+    per_step = len(all_names)
+    for k in range(2 * per_step + 1, len(marks)):
+        acc[marks[k][0]] += marks[k - 1][1].elapsed_time(marks[k][1]) / 6
+    pt = torch.tensor([acc[n] for n in all_names], device=dev, dtype=torch.float64)
+    pmax, pmin = pt.clone(), pt.clone()
+    dist.all_reduce(pmax, op=dist.ReduceOp.MAX)
+    dist.all_reduce(pmin, op=dist.ReduceOp.MIN)
+    phases = {n: float(v) for n, v in zip(all_names, pmax.tolist())}
+    phases_min = {n: float(v) for n, v in zip(all_names, pmin.tolist())}
 
     # one GPU's undivided scan of the same rows (no products, no exchange)
     h1, da1, db1 = torch.empty_like(a), torch.empty_like(a), torch.empty_like(a)
@@ -592,10 +594,14 @@ def seqpar_record(hs, native, fd, wl, dev, rank, world, peak, steps, warmup):
     gbs = w.elems * 16 / (ms["median"] * 1e-3) / 1e9
     one_gpu_rate = w.elems / (ms_plain["median"] * 1e-3)
     return {"workload": f"c5: ONE sequence, B1 T{T * world} D{D} bf16, {T} rows per GPU, a~U(0.9,0.9999)",
-            "parallelism": f"sequence split x{world}: local scan, NCCL all-gather of (product, carry), fix-up; mirrored backward",
+            "parallelism": f"sequence split x{world}: local scan, exchange of (product, carry), fix-up; mirrored backward",
+            "exchange": ("NCCL all_gather_into_tensor of [2, B*D] fp32 per rank" if exchange == "collective" else
+                         "peer memory: a push kernel stores the pair into every GPU's table over NVLink and publishes an "
+                         "epoch, the consumer waits for it (bounded), composes and acknowledges"),
             "ms_per_step": ms["median"], "ms_per_step_min": ms["min"], "ms_per_step_max": ms["max"], "steps": steps,
             "elems_per_s": total / (ms["median"] * 1e-3), "per_gpu_achieved_gbs": gbs, "per_gpu_frac": gbs / peak,
-            "phases_ms": phases,
+            "phases_ms": phases, "phases_ms_min_over_ranks": phases_min,
+            "phases_note": "fwd_gather / bwd_gather include the wait for the slowest rank; *_fixup = carry composition + fix-up",
             "one_gpu_undivided": {"ms_per_step": ms_plain["median"], "elems_per_s": one_gpu_rate,
                                   "what": "plain fwd+bwd scan of one rank's rows on one GPU (max over ranks)"},
             "vs_one_gpu_undivided": (total / (ms["median"] * 1e-3)) / one_gpu_rate,
@@ -793,6 +799,19 @@ def main():
                 strong = strong_record(hs, native, fd, wl, w, dev, rank, world, algo, peak, args.steps, sr)
             torch.cuda.empty_cache()
             seqpar = seqpar_record(hs, native, fd, wl, dev, rank, world, peak, max(10, args.steps), args.warmup)
+            # the same step with the carries exchanged through peer memory instead of the collective
+            try:
+                peer = seqpar_record(hs, native, fd, wl, dev, rank, world, peak, max(10, args.steps), args.warmup,
+                                     exchange="peer")
+            except Exception as e:      # no peer access / no symmetric memory on this box
+                peer = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+            if peer.get("parity_ok") and peer["ms_per_step"] < seqpar["ms_per_step"]:
+                peer["nccl_exchange"] = {k: seqpar[k] for k in ("ms_per_step", "ms_per_step_min", "ms_per_step_max",
+                                                                "elems_per_s", "vs_one_gpu_undivided", "parity_ok",
+                                                                "parity_max_ratio", "phases_ms", "exchange")}
+                seqpar = peer
+            else:
+                seqpar["peer_exchange"] = peer
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:

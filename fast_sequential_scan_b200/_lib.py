@@ -25,6 +25,7 @@ ALGO_BY_NAME = {"auto": ALGO_AUTO, "chunked": ALGO_CHUNKED, "lookback": ALGO_LOO
 STATUS_TEXT = {
     1: "a tile gave up waiting for its predecessor's carry (look-back timeout)",
     2: "a tile gave up waiting for its own TMA loads",
+    3: "a rank gave up waiting for another rank's carry (peer exchange timeout)",
 }
 
 
@@ -73,6 +74,10 @@ SIGNATURES = {
                                    c_void_p] + [_P(View)] * 5 + [c_void_p]),
     "fss_block_rows": (c_int64, [c_int, c_int64, c_int64, c_int64, c_int]),
     "fss_seqpar_compose": (c_int, [_P(ScanCtx), c_int, c_int, c_int, c_int64, c_void_p, c_void_p]),
+    "fss_seqpar_push": (c_int, [_P(ScanCtx), c_int, c_int, c_int, c_int64, c_void_p, c_void_p, _P(c_void_p), _P(c_void_p),
+                                c_uint32]),
+    "fss_seqpar_compose_peer": (c_int, [_P(ScanCtx), c_int, c_int, c_int, c_int64, _P(c_void_p), _P(c_void_p), c_uint32,
+                                        c_void_p]),
     "fss_seqpar_fixup_forward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View),
                                          c_void_p, c_void_p, c_void_p, c_int64]),
     "fss_seqpar_fixup_backward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64] + [_P(View)] * 5

@@ -349,6 +349,59 @@ FSS_API int fss_seqpar_compose(const fss_scan_ctx *ctx, int backward, int world,
 }
 
 namespace fss {
+static int fill_peers(seqpar::PeerTables *peers, int world, void *const *tables, void *const *words) {
+    if (!tables || !words) return FSS_E_NULL;
+    for (int q = 0; q < world; ++q) {
+        if (!tables[q] || !words[q]) return FSS_E_NULL;
+        peers->table[q] = static_cast<float *>(tables[q]);
+        peers->words[q] = static_cast<uint32_t *>(words[q]);
+    }
+    return FSS_OK;
+}
+static int check_exchange(const fss_scan_ctx *ctx, int world, int rank, int64_t n, uint32_t epoch) {
+    if (int rc = check_ctx(ctx)) return rc;
+    if (world < 1 || world > seqpar::kMaxPeers || rank < 0 || rank >= world || n < 0 || epoch == 0) return FSS_E_SHAPE;
+    return FSS_OK;
+}
+static uint32_t exchange_spins(const fss_scan_ctx *ctx) {
+    return (ctx->flags & FSS_FLAG_TEST_SHORT_WAITS) ? 4096u : (1u << 22);
+}
+}  // namespace fss
+
+FSS_API int fss_seqpar_push(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n, const float *prod,
+                            const float *state, void *const *peer_tables, void *const *peer_words, uint32_t epoch) {
+    int rc;
+    if ((rc = check_exchange(ctx, world, rank, n, epoch))) return rc;
+    if (!prod || !state) return FSS_E_NULL;
+    seqpar::PeerTables peers{};
+    if ((rc = fill_peers(&peers, world, peer_tables, peer_words))) return rc;
+    if (n == 0) return FSS_OK;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    int64_t blocks = ceil_div(n, (int64_t)seqpar::kPushThreads * 4);
+    if (blocks > 64) blocks = 64;
+    seqpar::peer_push<<<(unsigned)blocks, seqpar::kPushThreads, 0, (cudaStream_t)ctx->stream>>>(
+        peers, backward, world, rank, n, prod, state, epoch, ctx->status, exchange_spins(ctx));
+    return launch_check("carry push launch");
+}
+
+FSS_API int fss_seqpar_compose_peer(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n,
+                                    void *const *peer_tables, void *const *peer_words, uint32_t epoch,
+                                    float *carry_in) {
+    int rc;
+    if ((rc = check_exchange(ctx, world, rank, n, epoch))) return rc;
+    if (!carry_in) return FSS_E_NULL;
+    seqpar::PeerTables peers{};
+    if ((rc = fill_peers(&peers, world, peer_tables, peer_words))) return rc;
+    if (n == 0) return FSS_OK;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    seqpar::peer_compose<<<(unsigned)ceil_div(n, 256), 256, 0, (cudaStream_t)ctx->stream>>>(
+        peers, backward, world, rank, n, epoch, carry_in, ctx->status, exchange_spins(ctx));
+    return launch_check("carry compose launch");
+}
+
+namespace fss {
 // multiprocessors of the current device (cached per device; 148 if the query fails)
 static int sm_count() {
     static int cached[64] = {0};
@@ -396,6 +449,7 @@ static int fixup_backward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn,
         make_view<T>(db), u_in, h_prev, bp, bs, (ctx->flags & FSS_FLAG_CONTINUATION) != 0);
     return launch_check("seqpar backward fix-up launch");
 }
+
 }  // namespace fss
 
 FSS_API int fss_seqpar_fixup_forward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,

@@ -36,15 +36,65 @@ def shard_channels(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     return t[..., rank * w:(rank + 1) * w]
 
 
+class PeerExchange:
+    """Carry exchange through peer memory: every rank's gather table and control words are allocated
+    in torch's symmetric memory, so that each process holds device pointers to the tables of all GPUs
+    of the box; a push kernel writes this rank's pair into every table with plain stores over NVLink
+    and publishes an epoch, and the consumer waits (bounded) for the epochs it needs and acknowledges
+    them.  One instance serves one direction of one shape; exchanges are numbered from 1."""
+
+    def __init__(self, n: int, device: torch.device, backward: bool, group=None):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 16:
+            raise RuntimeError("peer exchange serves at most 16 ranks")
+        self.n, self.device, self.backward = n, device, backward
+        words = self.world * 2 * n
+        # one allocation: the table, then the control words (epochs start at 1, so zero = nothing yet)
+        self.buf = symm_mem.empty(words + 64, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group.group_name)
+        ptrs = list(self.handle.buffer_ptrs)
+        self.tables = (ctypes.c_void_p * self.world)(*ptrs)
+        self.words = (ctypes.c_void_p * self.world)(*[p + words * 4 for p in ptrs])
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                 # every table is zeroed before anyone pushes
+
+    def push(self, prod: torch.Tensor, state: torch.Tensor) -> int:
+        from . import sequential_scan_cuda as native
+        self.epoch += 1
+        native.seqpar_push(prod, state, self.rank, self.backward, self.tables, self.words, self.epoch)
+        return self.epoch
+
+    def compose(self, epoch: int) -> torch.Tensor:
+        from . import sequential_scan_cuda as native
+        return native.seqpar_compose_peer(self.n, self.device, self.rank, self.backward, self.tables, self.words, epoch)
+
+
 class NativeOps:
     """Local pieces on the GPU through the C ABI.  The small fp32 vectors and block tables of a step
     live in buffers that are kept between calls (one set per shape): a training loop calls this
     with the same shapes every step, and the kernels write the (product, state) pair straight into
     the buffer that is handed to the all-gather."""
 
-    def __init__(self, algo: Optional[int] = None):
+    def __init__(self, algo: Optional[int] = None, exchange: str = "collective"):
+        """``exchange``: "collective" = ``all_gather_into_tensor`` of the process group (NCCL);
+        "peer" = :class:`PeerExchange` (GPUs of one box with peer access)."""
+        if exchange not in ("collective", "peer"):
+            raise ValueError("exchange must be 'collective' or 'peer'")
         self.algo = algo
+        self.exchange = exchange
         self._bufs: dict = {}
+
+    def peer(self, which: str, send, group) -> PeerExchange:
+        key = ("peer", which, send.device, send.shape[1])
+        got = self._bufs.get(key)
+        if got is None:
+            got = self._bufs[key] = PeerExchange(send.shape[1], send.device, which == "bwd", group)
+        return got
 
     def _algo_for(self, *tensors):
         """The kernel family that will really run: block sizes of the two families differ, so a
@@ -92,7 +142,8 @@ class NativeOps:
         algo = self._algo_for(alpha, h, grad)
         send, bp, bs, R = self._buffers("bwd", alpha, algo)
         da, db = torch.empty_like(alpha), torch.empty_like(alpha)
-        send[0].copy_(prod.reshape(-1))
+        if self.exchange == "collective":          # the all-gather sends one contiguous [2, n] pair
+            send[0].copy_(prod.reshape(-1))
         native.backward_into(alpha, h, grad, da, db, algo=algo, continuation=continuation, h_prev=h_prev,
                              u_out=send[1].view(B, D), block_prod=bp, block_state=bs)
         return da, db, send, (bp, bs, R)
@@ -142,6 +193,19 @@ def _no_mark(_name: str) -> None:
     pass
 
 
+def _exchange_and_compose(ops, which: str, send, prod, rank: int, world: int, backward: bool, needed: bool, group, mark):
+    """Hand this rank's pair (prod, send[1]) to the others and fold what this rank needs; returns the carry
+    ([n]) or None."""
+    if world > 1 and getattr(ops, "exchange", "collective") == "peer":
+        peer = ops.peer(which, send, group)
+        epoch = peer.push(prod.reshape(-1), send[1])
+        mark(which + "_gather")
+        return peer.compose(epoch) if needed else None
+    pc = _gather(send, group, ops, which)
+    mark(which + "_gather")
+    return ops.compose(pc, rank, backward=backward) if needed else None
+
+
 def seqpar_forward(alpha, beta, group=None, ops=None, mark=_no_mark):
     """Forward of the sequence-parallel scan on this rank's rows.  Returns ``(h, saved)`` where
     ``saved`` carries what the backward needs (state entering the rows, local product).  ``mark``
@@ -151,11 +215,9 @@ def seqpar_forward(alpha, beta, group=None, ops=None, mark=_no_mark):
     B, T, D = alpha.shape
     h, send, blocks = ops.local_forward(alpha, beta, continuation=rank > 0)
     mark("fwd_local")
-    pc = _gather(send, group, ops, "fwd")
-    mark("fwd_gather")
-    carry_in = None
-    if rank > 0:
-        carry_in = ops.compose(pc, rank, backward=False).reshape(B, D)
+    carry_in = _exchange_and_compose(ops, "fwd", send, send[0], rank, world, False, rank > 0, group, mark)
+    if carry_in is not None:
+        carry_in = carry_in.reshape(B, D)
         ops.fixup_forward(alpha, beta, h, carry_in, blocks)
     mark("fwd_fixup")
     return h, dict(carry_in=carry_in, prod=send[0].clone())
@@ -169,11 +231,9 @@ def seqpar_backward(alpha, h, grad, saved, group=None, ops=None, mark=_no_mark):
     h_prev = saved["carry_in"]
     da, db, send, blocks = ops.local_backward(alpha, h, grad, continuation=rank > 0, h_prev=h_prev, prod=saved["prod"])
     mark("bwd_local")
-    pc = _gather(send, group, ops, "bwd")
-    mark("bwd_gather")
-    if rank < world - 1:
-        u_in = ops.compose(pc, rank, backward=True).reshape(B, D)
-        ops.fixup_backward(alpha, h, grad, da, db, u_in, h_prev, blocks, continuation=rank > 0)
+    u_in = _exchange_and_compose(ops, "bwd", send, saved["prod"], rank, world, True, rank < world - 1, group, mark)
+    if u_in is not None:
+        ops.fixup_backward(alpha, h, grad, da, db, u_in.reshape(B, D), h_prev, blocks, continuation=rank > 0)
     mark("bwd_fixup")
     return da, db
 
@@ -195,5 +255,6 @@ class _SeqParScan(torch.autograd.Function):
 
 def seqpar_scan(alpha: torch.Tensor, beta: torch.Tensor, group=None, ops=None) -> torch.Tensor:
     """``scan_cu`` for a sequence split across the ranks of ``group`` (this rank's rows in, this
-    rank's rows of ``h`` out; differentiable)."""
+    rank's rows of ``h`` out; differentiable).  Pass one ``NativeOps`` object for all calls of a
+    training loop: it keeps the exchange buffers (and, with ``exchange="peer"``, the peer mappings)."""
     return _SeqParScan.apply(alpha, beta, group, ops)

@@ -410,6 +410,33 @@ def seqpar_compose(pc: torch.Tensor, rank: int, backward: bool) -> torch.Tensor:
     return out
 
 
+def seqpar_push(prod: torch.Tensor, state: torch.Tensor, rank: int, backward: bool, peer_tables, peer_words, epoch: int,
+                short_waits: bool = False) -> None:
+    """Write this rank's (product, state) pair -- two fp32 vectors of n values -- into slot ``rank`` of every
+    rank's table and publish the epoch (``fss_seqpar_push``).  ``peer_tables`` / ``peer_words``: ctypes arrays of
+    device pointers, one per rank."""
+    for name, t in (("prod", prod), ("state", state)):
+        if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous() or t.numel() != prod.numel():
+            raise RuntimeError(f"{name}: expected a contiguous fp32 CUDA vector of {prod.numel()} values")
+    ws = workspace.get(prod.device, 1 << 16)
+    ctx = _ctx(prod.device, ws, None, _lib.FLAG_TEST_SHORT_WAITS if short_waits else 0)
+    rc = _lib.lib().fss_seqpar_push(ctypes.byref(ctx), int(backward), len(peer_tables), rank, prod.numel(),
+                                    prod.data_ptr(), state.data_ptr(), peer_tables, peer_words, epoch)
+    _lib.check(rc, "fss_seqpar_push")
+
+
+def seqpar_compose_peer(n: int, device: torch.device, rank: int, backward: bool, peer_tables, peer_words, epoch: int,
+                        short_waits: bool = False) -> torch.Tensor:
+    """``fss_seqpar_compose_peer``: wait (bounded) for the pairs this rank folds, compose them, acknowledge."""
+    out = torch.empty(n, dtype=torch.float32, device=device)
+    ws = workspace.get(device, 1 << 16)
+    ctx = _ctx(device, ws, None, _lib.FLAG_TEST_SHORT_WAITS if short_waits else 0)
+    rc = _lib.lib().fss_seqpar_compose_peer(ctypes.byref(ctx), int(backward), len(peer_tables), rank, n,
+                                            peer_tables, peer_words, epoch, out.data_ptr())
+    _lib.check(rc, "fss_seqpar_compose_peer")
+    return out
+
+
 def seqpar_fixup_forward(alpha, beta, h, carry_in, block_prod, block_state, rows_per_block: int) -> None:
     """In place: re-scan the blocks of a zero-state forward scan that ``carry_in`` still reaches."""
     dtype = alpha.dtype

@@ -64,6 +64,7 @@ extern "C" {
 #define FSS_STATUS_OK 0
 #define FSS_STATUS_LOOKBACK_TIMEOUT 1 /* a tile gave up waiting for its predecessor's carry  */
 #define FSS_STATUS_TMA_TIMEOUT 2      /* a tile gave up waiting for its own TMA loads        */
+#define FSS_STATUS_EXCHANGE_TIMEOUT 3 /* a rank gave up waiting for another rank's carry     */
 
 /* One [B, T, D] tensor: element (b,t,d) lives at ptr + (b*stride_b + t*stride_t + d) elements. */
 typedef struct fss_view {
@@ -220,6 +221,26 @@ int64_t fss_block_rows(int dtype, int64_t B, int64_t T, int64_t D, int algo);
  *             ranks rank+1..world-1.  One small launch on ctx->stream. */
 int fss_seqpar_compose(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n,
                        const float *pc, float *carry_in);
+/* Carry exchange through peer memory instead of a library all-gather (ranks = GPUs of one box whose
+ * memory is mapped into each other's address space, e.g. with CUDA IPC or torch symmetric memory).
+ * Rank q owns a table of world*2*n floats and 2*world+2 32-bit words, all zeroed once before the
+ * first exchange (with a barrier between the zeroing and the first push of any rank).
+ * peer_tables / peer_words are HOST arrays of `world` device pointers: entry q is rank q's table /
+ * words as mapped in the calling process (entry `rank` is the caller's own, local memory).
+ * fss_seqpar_push writes this rank's pair (prod[n], state[n]) into slot `rank` of every table
+ * and then publishes `epoch` in every rank's words; epochs start at 1 and grow by one per exchange
+ * over the same tables.  Before overwriting its slot the push waits until the readers of that slot
+ * (forward: later ranks; backward: earlier ranks) have acknowledged exchange epoch-1.
+ * fss_seqpar_compose_peer is fss_seqpar_compose on the caller's own table after a wait for the pairs
+ * of the ranks it folds, followed by the acknowledgement.  Every wait is bounded; one that runs out
+ * sets the status word to FSS_STATUS_EXCHANGE_TIMEOUT and the kernel returns.  world <= 16.  Plain
+ * peer stores only: no multicast, no remote loads. */
+int fss_seqpar_push(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n, const float *prod,
+                    const float *state, void *const *peer_tables, void *const *peer_words, uint32_t epoch);
+int fss_seqpar_compose_peer(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n,
+                            void *const *peer_tables, void *const *peer_words, uint32_t epoch,
+                            float *carry_in);
+
 /* Correct a zero-state forward scan for the state carry_in that really enters row 0: block j is
  * re-scanned from its true entering state
  *     block_state[j-1] + (block_prod[0] * ... * block_prod[j-1]) * carry_in

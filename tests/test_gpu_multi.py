@@ -20,7 +20,7 @@ sys.path.insert(0, str(ROOT))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, exchange):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -36,8 +36,11 @@ def _worker(rank, world, port, out_dir):
         rows = slice(rank * T // world, (rank + 1) * T // world)
         al = a[:, rows].cuda().requires_grad_(True)
         bl = b[:, rows].cuda().requires_grad_(True)
-        h = fd.seqpar_scan(al, bl)
-        h.backward(g[:, rows].cuda())
+        ops = fd.NativeOps(exchange=exchange)
+        for _ in range(2):                     # twice: the second step reuses buffers, slots and epochs
+            al.grad = bl.grad = None
+            h = fd.seqpar_scan(al, bl, None, ops)
+            h.backward(g[:, rows].cuda())
         pkg.check_status()
         # the CPU checker on the whole, undivided sequence (every rank computes it for itself)
         from oracle import oracle
@@ -61,10 +64,13 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def test_sequence_parallel_scan_over_nccl(tmp_path):
+@pytest.mark.parametrize("exchange", ["collective", "peer"])
+def test_sequence_parallel_scan_over_nccl(tmp_path, exchange):
+    """``exchange``: the carries travel by NCCL all-gather, or through peer memory (plain stores into
+    every GPU's table, bounded waits; NVLS is off in both)."""
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), exchange), nprocs=world, join=True)
     assert sorted(p.name for p in tmp_path.iterdir()) == [f"rank{r}.ok" for r in range(world)]

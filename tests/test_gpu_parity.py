@@ -558,6 +558,65 @@ def test_sequence_parallel_pieces_on_one_gpu(dtype, algo):
     pkg.check_status()
 
 
+def _local_peers(world, n):
+    """Tables and control words of `world` ranks, all in this GPU's memory (the ranks are played one
+    after the other on one stream, so no kernel ever waits for a kernel that has not run)."""
+    import ctypes
+    bufs = [torch.zeros(world * 2 * n + 64, dtype=torch.float32, device="cuda") for _ in range(world)]
+    tables = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    words = (ctypes.c_void_p * world)(*[b.data_ptr() + world * 2 * n * 4 for b in bufs])
+    return bufs, tables, words
+
+
+@pytest.mark.parametrize("backward", [False, True])
+def test_carry_exchange_through_tables_played_on_one_gpu(backward):
+    """fss_seqpar_push / fss_seqpar_compose_peer with the four ranks' tables in one GPU's memory: every
+    rank pushes, then every rank composes; the result must equal the fold of the pairs in float64,
+    for three exchanges in a row (epochs 1..3: slots are overwritten, acknowledgements are checked)."""
+    pkg, native, _ = _mods()
+    world, n = 4, 2048 + 12
+    bufs, tables, words = _local_peers(world, n)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    for epoch in (1, 2, 3):
+        pairs = [torch.stack([torch.rand(n, generator=gen, device="cuda") * 0.9 + 0.05,
+                              torch.randn(n, generator=gen, device="cuda")]) for _ in range(world)]
+        for r in range(world):
+            native.seqpar_push(pairs[r][0], pairs[r][1], r, backward, tables, words, epoch, short_waits=True)
+        for r in range(world):
+            needed = r < world - 1 if backward else r > 0
+            if not needed:
+                continue
+            got = native.seqpar_compose_peer(n, torch.device("cuda", 0), r, backward, tables, words, epoch, short_waits=True)
+            carry = torch.zeros(n, dtype=torch.float64)
+            order = range(world - 1, r, -1) if backward else range(r)
+            for q in order:
+                carry = pairs[q][0].double().cpu() * carry + pairs[q][1].double().cpu()
+            assert torch.allclose(got.cpu().double(), carry, rtol=1e-5, atol=1e-6), (epoch, r)
+    pkg.check_status()
+
+
+def test_carry_exchange_wait_gives_up_and_reports():
+    """Failure detection without a fault: a rank waits for a pair that nobody pushes (a flag that
+    nothing sets), with shortened waits; the kernel must end by itself, the status word must say so,
+    and a slot must not be overwritten while a reader has not acknowledged the previous exchange."""
+    pkg, native, _ = _mods()
+    world, n = 2, 512
+    bufs, tables, words = _local_peers(world, n)
+    one = torch.ones(n, device="cuda")
+    native.seqpar_compose_peer(n, torch.device("cuda", 0), 1, False, tables, words, 1, short_waits=True)
+    torch.cuda.synchronize()                       # ended by itself
+    with pytest.raises(RuntimeError, match="peer exchange timeout"):
+        pkg.check_status()
+    # rank 0 pushes exchange 1, nobody reads it; its push of exchange 2 must refuse to overwrite
+    native.seqpar_push(one, one, 0, False, tables, words, 1, short_waits=True)
+    native.seqpar_push(one * 2, one * 2, 0, False, tables, words, 2, short_waits=True)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="peer exchange timeout"):
+        pkg.check_status()
+    assert float(bufs[1][0]) == 1.0                # rank 1's copy of rank 0's slot still holds exchange 1
+    pkg.check_status()                             # the status word was cleared; nothing else pending
+
+
 @pytest.mark.parametrize("algo", ["chunked", "lookback"])
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 @pytest.mark.parametrize("shape", [(2, 1000, 128), (3, 257, 264), (2, 70, 7)])

@@ -799,12 +799,21 @@ def main():
                 strong = strong_record(hs, native, fd, wl, w, dev, rank, world, algo, peak, args.steps, sr)
             torch.cuda.empty_cache()
             seqpar = seqpar_record(hs, native, fd, wl, dev, rank, world, peak, max(10, args.steps), args.warmup)
-            # the same step with the carries exchanged through peer memory instead of the collective
+            # the same step with the carries exchanged through peer memory instead of the collective, when
+            # every rank can reach every other GPU's memory (decided together, so no rank waits alone)
+            able = 1.0
             try:
+                import torch.distributed._symmetric_memory  # noqa: F401
+                able = float(all(torch.cuda.can_device_access_peer(local, r) for r in range(world) if r != local))
+            except Exception:
+                able = 0.0
+            flag = torch.tensor([able], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if flag.item() == 1.0:
                 peer = seqpar_record(hs, native, fd, wl, dev, rank, world, peak, max(10, args.steps), args.warmup,
                                      exchange="peer")
-            except Exception as e:      # no peer access / no symmetric memory on this box
-                peer = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+            else:
+                peer = {"unavailable": "not every GPU pair of this box has peer access / symmetric memory"}
             if peer.get("parity_ok") and peer["ms_per_step"] < seqpar["ms_per_step"]:
                 peer["nccl_exchange"] = {k: seqpar[k] for k in ("ms_per_step", "ms_per_step_min", "ms_per_step_max",
                                                                 "elems_per_s", "vs_one_gpu_undivided", "parity_ok",

@@ -49,6 +49,11 @@ class BackwardState(Structure):
                 ("block_state", c_void_p)]
 
 
+class CarrySource(Structure):
+    _fields_ = [("world", c_int32), ("rank", c_int32), ("table", c_void_p), ("peer_tables", POINTER(c_void_p)),
+                ("peer_words", POINTER(c_void_p)), ("epoch", c_uint32), ("carry_out", c_void_p)]
+
+
 _P = POINTER
 
 # name -> (restype, argtypes); every symbol include/fss_b200.h declares
@@ -76,12 +81,18 @@ SIGNATURES = {
     "fss_seqpar_compose": (c_int, [_P(ScanCtx), c_int, c_int, c_int, c_int64, c_void_p, c_void_p]),
     "fss_seqpar_push": (c_int, [_P(ScanCtx), c_int, c_int, c_int, c_int64, c_void_p, c_void_p, _P(c_void_p), _P(c_void_p),
                                 c_uint32]),
+    "fss_seqpar_push_blocks": (c_int, [_P(ScanCtx), c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                       _P(c_void_p), _P(c_void_p), c_uint32]),
     "fss_seqpar_compose_peer": (c_int, [_P(ScanCtx), c_int, c_int, c_int, c_int64, _P(c_void_p), _P(c_void_p), c_uint32,
                                         c_void_p]),
     "fss_seqpar_fixup_forward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View),
                                          c_void_p, c_void_p, c_void_p, c_int64]),
     "fss_seqpar_fixup_backward": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64] + [_P(View)] * 5
                                   + [c_void_p, c_void_p, c_void_p, c_void_p, c_int64]),
+    "fss_seqpar_fixup_forward_from": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View),
+                                              _P(CarrySource), c_void_p, c_void_p, c_int64]),
+    "fss_seqpar_fixup_backward_from": (c_int, [_P(ScanCtx), c_int, c_int64, c_int64, c_int64] + [_P(View)] * 5
+                                       + [_P(CarrySource), c_void_p, c_void_p, c_void_p, c_int64]),
     "fss_scan_forward_noalloc": (c_int, [c_int, c_int, c_void_p, c_int64, c_int64, c_int64, _P(View), _P(View), _P(View)]),
 }
 

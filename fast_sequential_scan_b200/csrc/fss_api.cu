@@ -353,7 +353,7 @@ static int fill_peers(seqpar::PeerTables *peers, int world, void *const *tables,
     if (!tables || !words) return FSS_E_NULL;
     for (int q = 0; q < world; ++q) {
         if (!tables[q] || !words[q]) return FSS_E_NULL;
-        peers->table[q] = static_cast<float *>(tables[q]);
+        peers->table[q] = static_cast<unsigned long long *>(tables[q]);
         peers->words[q] = static_cast<uint32_t *>(words[q]);
     }
     return FSS_OK;
@@ -378,10 +378,29 @@ FSS_API int fss_seqpar_push(const fss_scan_ctx *ctx, int backward, int world, in
     if (n == 0) return FSS_OK;
     DeviceGuard guard(ctx->device);
     if (guard.error) return guard.error;
-    int64_t blocks = ceil_div(n, (int64_t)seqpar::kPushThreads * 4);
-    if (blocks > 64) blocks = 64;
+    int64_t blocks = ceil_div(2 * n, (int64_t)seqpar::kPushThreads);
+    if (blocks > 148) blocks = 148;
     seqpar::peer_push<<<(unsigned)blocks, seqpar::kPushThreads, 0, (cudaStream_t)ctx->stream>>>(
         peers, backward, world, rank, n, prod, state, epoch, ctx->status, exchange_spins(ctx));
+    return launch_check("carry push launch");
+}
+
+FSS_API int fss_seqpar_push_blocks(const fss_scan_ctx *ctx, int world, int rank, int64_t B, int64_t nblocks, int64_t D,
+                                   const float *block_prod, const float *state, float *prod_out,
+                                   void *const *peer_tables, void *const *peer_words, uint32_t epoch) {
+    int rc;
+    if ((rc = check_exchange(ctx, world, rank, B * D, epoch))) return rc;
+    if (!block_prod || !state || !prod_out) return FSS_E_NULL;
+    if (B < 0 || nblocks < 1 || D < 0 || B > 65535) return FSS_E_SHAPE;
+    if (D % 4 || !aligned16(block_prod) || !aligned16(state) || !aligned16(prod_out)) return FSS_E_LAYOUT;
+    seqpar::PeerTables peers{};
+    if ((rc = fill_peers(&peers, world, peer_tables, peer_words))) return rc;
+    if (B == 0 || D == 0) return FSS_OK;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    const dim3 grid((unsigned)ceil_div(D, 4 * seqpar::kPushVecs), (unsigned)B);
+    seqpar::peer_push_blocks<<<grid, seqpar::kPushSlices * seqpar::kPushVecs, 0, (cudaStream_t)ctx->stream>>>(
+        peers, world, rank, nblocks, D, block_prod, state, prod_out, epoch, ctx->status, exchange_spins(ctx));
     return launch_check("carry push launch");
 }
 
@@ -427,29 +446,75 @@ static bool fixup_grid_ok(const seqpar::Geometry &g) { return g.vblocks <= 65535
 
 template <typename T, int V>
 static int fixup_forward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *alpha,
-                                const fss_view *beta, const fss_view *h, const float *carry_in, const float *bp,
+                                const fss_view *beta, const fss_view *h, const seqpar::CarrySource &carry_in, const float *bp,
                                 const float *bs, int64_t R) {
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
     if (!fixup_grid_ok(g)) return FSS_E_SHAPE;
     const dim3 grid((unsigned)g.slots, (unsigned)g.vblocks, (unsigned)B);
     seqpar::fixup_forward<T, V><<<grid, seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
-        g, make_view<const T>(alpha), make_view<const T>(beta), make_view<T>(h), carry_in, bp, bs);
+        g, make_view<const T>(alpha), make_view<const T>(beta), make_view<T>(h), carry_in, bp, bs, ctx->status);
     return launch_check("seqpar forward fix-up launch");
 }
 
 template <typename T, int V>
 static int fixup_backward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *alpha,
                                  const fss_view *h, const fss_view *grad, const fss_view *da, const fss_view *db,
-                                 const float *u_in, const float *h_prev, const float *bp, const float *bs, int64_t R) {
+                                 const seqpar::CarrySource &u_in, const float *h_prev, const float *bp, const float *bs,
+                                 int64_t R) {
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
     if (!fixup_grid_ok(g)) return FSS_E_SHAPE;
     const dim3 grid((unsigned)g.slots, (unsigned)g.vblocks, (unsigned)B);
     seqpar::fixup_backward<T, V><<<grid, seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
         g, make_view<const T>(alpha), make_view<const T>(h), make_view<const T>(grad), make_view<T>(da),
-        make_view<T>(db), u_in, h_prev, bp, bs, (ctx->flags & FSS_FLAG_CONTINUATION) != 0);
+        make_view<T>(db), u_in, h_prev, bp, bs, (ctx->flags & FSS_FLAG_CONTINUATION) != 0, ctx->status);
     return launch_check("seqpar backward fix-up launch");
 }
 
+static int fixup_forward_dispatch(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D, const fss_view *alpha,
+                                  const fss_view *beta, const fss_view *h, const seqpar::CarrySource &src, const float *bp,
+                                  const float *bs, int64_t R) {
+    if (dtype == FSS_DTYPE_BF16) {
+        if (chunked::vector_ok<bf16>(D, {alpha, beta, h}))
+            return fixup_forward_launch<bf16, 8>(ctx, B, T, D, alpha, beta, h, src, bp, bs, R);
+        return fixup_forward_launch<bf16, 1>(ctx, B, T, D, alpha, beta, h, src, bp, bs, R);
+    }
+    if (chunked::vector_ok<float>(D, {alpha, beta, h}))
+        return fixup_forward_launch<float, 4>(ctx, B, T, D, alpha, beta, h, src, bp, bs, R);
+    return fixup_forward_launch<float, 1>(ctx, B, T, D, alpha, beta, h, src, bp, bs, R);
+}
+static int fixup_backward_dispatch(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D, const fss_view *alpha,
+                                   const fss_view *h, const fss_view *grad, const fss_view *da, const fss_view *db,
+                                   const seqpar::CarrySource &src, const float *h_prev, const float *bp, const float *bs,
+                                   int64_t R) {
+#define FSS_FIXB(TT, VV) fixup_backward_launch<TT, VV>(ctx, B, T, D, alpha, h, grad, da, db, src, h_prev, bp, bs, R)
+    if (dtype == FSS_DTYPE_BF16)
+        return chunked::vector_ok<bf16>(D, {alpha, h, grad, da, db}) ? FSS_FIXB(bf16, 8) : FSS_FIXB(bf16, 1);
+    return chunked::vector_ok<float>(D, {alpha, h, grad, da, db}) ? FSS_FIXB(float, 4) : FSS_FIXB(float, 1);
+#undef FSS_FIXB
+}
+static seqpar::CarrySource ready_carry(const float *carry) {
+    seqpar::CarrySource s{};
+    s.carry = carry;
+    return s;
+}
+// From the caller's description of a gathered table; FSS_OK or an error code.
+static int table_carry(const fss_scan_ctx *ctx, const fss_carry_source *src, int64_t n, seqpar::CarrySource *out) {
+    if (!src || (!src->table && !src->epoch)) return FSS_E_NULL;
+    if (src->world < 1 || src->world > seqpar::kMaxPeers || src->rank < 0 || src->rank >= src->world) return FSS_E_SHAPE;
+    seqpar::CarrySource s{};
+    s.table = src->table;
+    s.carry_out = src->carry_out;
+    s.n = n;
+    s.world = src->world;
+    s.rank = src->rank;
+    s.epoch = src->epoch;
+    s.max_spins = exchange_spins(ctx);
+    if (src->epoch) {
+        if (int rc = fill_peers(&s.peers, src->world, src->peer_tables, src->peer_words)) return rc;
+    }
+    *out = s;
+    return FSS_OK;
+}
 }  // namespace fss
 
 FSS_API int fss_seqpar_fixup_forward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
@@ -466,14 +531,26 @@ FSS_API int fss_seqpar_fixup_forward(const fss_scan_ctx *ctx, int dtype, int64_t
     if (block_rows < 1) return FSS_E_SHAPE;
     DeviceGuard guard(ctx->device);
     if (guard.error) return guard.error;
-    if (dtype == FSS_DTYPE_BF16) {
-        if (chunked::vector_ok<bf16>(D, {alpha, beta, h}))
-            return fixup_forward_launch<bf16, 8>(ctx, B, T, D, alpha, beta, h, carry_in, block_prod, block_state, block_rows);
-        return fixup_forward_launch<bf16, 1>(ctx, B, T, D, alpha, beta, h, carry_in, block_prod, block_state, block_rows);
-    }
-    if (chunked::vector_ok<float>(D, {alpha, beta, h}))
-        return fixup_forward_launch<float, 4>(ctx, B, T, D, alpha, beta, h, carry_in, block_prod, block_state, block_rows);
-    return fixup_forward_launch<float, 1>(ctx, B, T, D, alpha, beta, h, carry_in, block_prod, block_state, block_rows);
+    return fixup_forward_dispatch(ctx, dtype, B, T, D, alpha, beta, h, ready_carry(carry_in), block_prod, block_state, block_rows);
+}
+
+FSS_API int fss_seqpar_fixup_forward_from(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                                          const fss_view *alpha, const fss_view *beta, const fss_view *h,
+                                          const fss_carry_source *source, const float *block_prod,
+                                          const float *block_state, int64_t block_rows) {
+    int rc;
+    if ((rc = check_ctx(ctx))) return rc;
+    if ((rc = check_shape(dtype, B, T, D))) return rc;
+    if (B == 0 || T == 0 || D == 0) return FSS_OK;
+    for (const fss_view *v : {alpha, beta, h})
+        if ((rc = check_view(v, B, T, D))) return rc;
+    if (!block_prod || !block_state) return FSS_E_NULL;
+    if (block_rows < 1) return FSS_E_SHAPE;
+    seqpar::CarrySource src;
+    if ((rc = table_carry(ctx, source, B * D, &src))) return rc;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    return fixup_forward_dispatch(ctx, dtype, B, T, D, alpha, beta, h, src, block_prod, block_state, block_rows);
 }
 
 FSS_API int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
@@ -491,12 +568,29 @@ FSS_API int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_
     if (block_rows < 1) return FSS_E_SHAPE;
     DeviceGuard guard(ctx->device);
     if (guard.error) return guard.error;
-#define FSS_FIXB(TT, VV) fixup_backward_launch<TT, VV>(ctx, B, T, D, alpha, h, grad_out, grad_alpha, grad_beta, \
-                                                       u_in, h_prev, block_prod, block_state, block_rows)
-    if (dtype == FSS_DTYPE_BF16)
-        return chunked::vector_ok<bf16>(D, {alpha, h, grad_out, grad_alpha, grad_beta}) ? FSS_FIXB(bf16, 8) : FSS_FIXB(bf16, 1);
-    return chunked::vector_ok<float>(D, {alpha, h, grad_out, grad_alpha, grad_beta}) ? FSS_FIXB(float, 4) : FSS_FIXB(float, 1);
-#undef FSS_FIXB
+    return fixup_backward_dispatch(ctx, dtype, B, T, D, alpha, h, grad_out, grad_alpha, grad_beta, ready_carry(u_in), h_prev,
+                                   block_prod, block_state, block_rows);
+}
+
+FSS_API int fss_seqpar_fixup_backward_from(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                                           const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
+                                           const fss_view *grad_alpha, const fss_view *grad_beta,
+                                           const fss_carry_source *source, const float *h_prev, const float *block_prod,
+                                           const float *block_state, int64_t block_rows) {
+    int rc;
+    if ((rc = check_ctx(ctx))) return rc;
+    if ((rc = check_shape(dtype, B, T, D))) return rc;
+    if (B == 0 || T == 0 || D == 0) return FSS_OK;
+    for (const fss_view *v : {alpha, h, grad_out, grad_alpha, grad_beta})
+        if ((rc = check_view(v, B, T, D))) return rc;
+    if (!block_prod || !block_state) return FSS_E_NULL;
+    if (block_rows < 1) return FSS_E_SHAPE;
+    seqpar::CarrySource src;
+    if ((rc = table_carry(ctx, source, B * D, &src))) return rc;
+    DeviceGuard guard(ctx->device);
+    if (guard.error) return guard.error;
+    return fixup_backward_dispatch(ctx, dtype, B, T, D, alpha, h, grad_out, grad_alpha, grad_beta, src, h_prev, block_prod,
+                                   block_state, block_rows);
 }
 
 // ---------------------------------------------------------------------- gates outside the scan

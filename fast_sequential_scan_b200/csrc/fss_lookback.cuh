@@ -59,6 +59,9 @@ constexpr int kLookbackWarp0 = 2 * kW + 2;    // first of the look-back warps
 constexpr int kLookbackWarps = 2;             // three were measured slower on every workload
 constexpr int kGens = 4;                      // generations of summary buffers: pass 1 may run this far ahead of pass 2
 constexpr int kThreads = (2 * kW + 2 + kLookbackWarps) * 32;
+constexpr int kGateWarp0 = 2 * kW + 2 + kLookbackWarps;      // gated forward only: kW more warps that evaluate the gates
+constexpr int kThreadsGated = kThreads + kW * 32;
+template <bool kGate> constexpr int threads_of() { return kGate ? kThreadsGated : kThreads; }
 constexpr int kStagesFwd = 6;                 // 6 x 32 KiB
 constexpr int kStagesBwd = 4;                 // 4 x 48 KiB
 constexpr uint32_t kMaxSpins = 1u << 21;      // per wait; ~a second before giving up
@@ -301,7 +304,7 @@ template <int kTensors, int kStages> struct Smem {
     // summaries: [generation][warp][P|C][lane] as 8-byte (fp32 x2) or 16-byte (fp32 x4) entries
     static constexpr int kAggBytes = kGens * kW * 2 * 32 * 16;
     static constexpr int kSumBytes = kGens * 3 * 32 * 16;      // [generation][tile P | tile C | entering state][lane]
-    static constexpr int kBarriers = 3 * kStages + 3 * kGens;
+    static constexpr int kBarriers = 4 * kStages + 3 * kGens;      // full, done, info, gate per stage; agg, carry, sum per generation
     static constexpr int kBytes = 128 /* alignment slack */ + kStages * kStageBytes + kAggBytes + kSumBytes +
                                   kBarriers * 8 + 16 + kStages * 16 /* unit descriptors */;
 };
@@ -397,13 +400,61 @@ template <bool kTickets, int kStages> struct UnitCursor {
     __device__ __forceinline__ bool next_known() const { return have && nxt.k >= 0; }
 };
 
+// Gated forward: turns kRh rows (from row `base` of this lane's group) of a stage from (r, x, i) into
+// (alpha, beta) in place, rounded to the I/O type as if they had come from memory.  The odd row
+// group of a 64-byte-row tile reads row r^1 in the slot of row r (see pair_slot); every value goes
+// back to the slot it came from, so nothing has to be swapped here.
+template <typename T, int kRowStride>
+__device__ __forceinline__ void gate_rows(typename Lane<T>::Raw *a_t, typename Lane<T>::Raw *x_t,
+                                          const typename Lane<T>::Raw *i_t, int base, int dsw, bool odd_grp,
+                                          const float (&gsc)[Lane<T>::V], bool head, int nvalid, bool edge_rows) {
+    constexpr int V = Lane<T>::V;
+    using Raw = typename Lane<T>::Raw;
+    Raw ra[kRh], rx[kRh], rg[kRh];
+#pragma unroll
+    for (int r = 0; r < kRh; ++r) {
+        ra[r] = pair_slot<kRowStride>(a_t, base + r, dsw);
+        rx[r] = pair_slot<kRowStride>(x_t, base + r, dsw);
+        rg[r] = pair_slot<kRowStride>(i_t, base + r, dsw);
+    }
+#pragma unroll
+    for (int r = 0; r < kRh; ++r) {
+        float rr[V], ii[V], xx[V], a[V], b[V];
+        Lane<T>::unpack(ra[r], rr);
+        Lane<T>::unpack(rg[r], ii);
+        Lane<T>::unpack(rx[r], xx);
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            a[v] = Gate<T>::exp_scaled(gsc[v] * Gate<T>::sigmoid(rr[v]));
+            b[v] = Gate<T>::root(fmaf(-a[v], a[v], 1.0f)) * Gate<T>::sigmoid(ii[v]) * xx[v];
+        }
+        if (edge_rows) {       // warp-uniform and rare: first row of the sequence, rows after its end
+            const int row = base + (odd_grp ? (r ^ 1) : r);      // the row this register holds
+            const bool first_row = head && row == 0;             // alpha_0 is not part of the recurrence
+            const bool past_end = row >= nvalid;                 // identity rows after the sequence
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                if (first_row) a[v] = 0.0f;
+                if (past_end) { a[v] = 1.0f; b[v] = 0.0f; }
+            }
+        }
+        ra[r] = Lane<T>::pack(a);
+        rx[r] = Lane<T>::pack(b);
+    }
+#pragma unroll
+    for (int r = 0; r < kRh; ++r) {
+        pair_slot<kRowStride>(a_t, base + r, dsw) = ra[r];
+        pair_slot<kRowStride>(x_t, base + r, dsw) = rx[r];
+    }
+}
+
 // ------------------------------------------------------------------ the kernel
 // Forward: tiles of (alpha, beta) are loaded, h is stored from beta's stage slot.
 // Backward: (alpha, grad, h shifted one row down) are loaded; dbeta is stored from grad's slot,
 // dalpha from h's slot.  Results are written in place in shared memory and leave through TMA
 // stores issued by the producer, so the consumer warps never stall on the global write path.
 template <typename T, bool kBackward, int kSp, bool kTickets, bool kGate = false>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads_of<kGate>(), 1)
 scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant__ CUtensorMap map_x,
             const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_out0,
             const __grid_constant__ CUtensorMap map_out1, const Params p) {
@@ -432,6 +483,7 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     Unit *units = reinterpret_cast<Unit *>(smem_raw + kStages * SM::kStageBytes + SM::kAggBytes + SM::kSumBytes +
                                            SM::kBarriers * 8 + 16);
     auto bar_info = [&](int s) { return bars + 8u * (2 * kStages + 3 * kGens + s); };
+    auto bar_gate = [&](int s) { return bars + 8u * (3 * kStages + 3 * kGens + s); };
     auto bar_full = [&](int s) { return bars + 8u * s; };
     auto bar_done = [&](int s) { return bars + 8u * (kStages + s); };
     auto bar_agg = [&](int g) { return bars + 8u * (2 * kStages + g); };
@@ -458,7 +510,9 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         if (kBackward) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out1) : "memory");
     }
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_done(s), kW); mbar_init(bar_info(s), 1); }
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full(s), 1); mbar_init(bar_done(s), kW); mbar_init(bar_info(s), 1); mbar_init(bar_gate(s), kW);
+        }
         for (int g = 0; g < kGens; ++g) { mbar_init(bar_agg(g), kW); mbar_init(bar_carry(g), 1); mbar_init(bar_sum(g), 1); }
         *cta_abort = 0;
         asm volatile("griddepcontrol.wait;" ::: "memory");      // the previous launch and its writes are complete
@@ -662,6 +716,49 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 }
             }
         }
+    } else if (kGate && warp >= kGateWarp0) {
+        // ============================================================ gates (gated forward only)
+        // The alpha slot of a stage arrives holding r, the third slot i, the beta slot x.  These
+        // warps turn them into alpha and beta in place as soon as the tile has landed, one warp per
+        // row-group mapping of the pass-1 warps, so that the special-function work runs beside the
+        // scan instead of inside it.  (Measured on the c4 shape, bf16: gates inside pass 1 0.44 ms,
+        // here 0.40 ms; giving half of the rows back to the pass-1 warps 0.61 ms.)
+        using Raw = typename Lane<T>::Raw;
+        constexpr int kRowStride = kRowB / (int)sizeof(Raw);
+        const int gw = warp - kGateWarp0;
+        const int grp = q * kW + gw;
+        constexpr bool kPairSwap = kRowB == 64;
+        const bool odd_grp = kPairSwap && (q & 1);
+        const int dsw = odd_grp ? kRowStride : 0;
+        const uint32_t lane_off = (uint32_t)(grp * kR) * kRowB + (uint32_t)cl * kLaneBytes;
+        Cursor cursor(p, ctl, units, bar_info(0));
+        cursor.init(u0, 0, 1);
+#pragma unroll 1
+        for (int i = 0;; ++i) {
+            const int st = i % kStages;
+            if (!cursor.advance(i)) break;
+            const Unit u = cursor.cur;
+            const int32_t row0 = u.template row0<kBackward>(p);
+            const bool head = (row0 == 0) && (grp == 0) && !p.continuation;
+            const int64_t left = p.T - row0 - (int64_t)grp * kR;
+            const int nvalid = left >= kR ? kR : (left > 0 ? (int)left : 0);
+            float gsc[V];      // this lane's channel scales, fetched while the tile is still on its way
+            {
+                const int64_t dch = (int64_t)u.cg * Dc + cl * V;
+#pragma unroll
+                for (int v = 0; v < V; ++v) gsc[v] = dch + v < p.D ? Gate<T>::prescale(gate_scale(p.lambda[dch + v])) : 0.0f;
+            }
+            if (!ctl.wait(bar_full(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
+            Raw *a_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + lane_off);
+            Raw *x_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + kTileBytes + lane_off);
+            const Raw *i_t = reinterpret_cast<const Raw *>(smem_raw + st * SM::kStageBytes + 2 * kTileBytes + lane_off);
+            const bool edge_rows = __any_sync(0xffffffffu, head || nvalid < kR);
+#pragma unroll 1
+            for (int hb = 0; hb < kR / kRh; ++hb)
+                gate_rows<T, kRowStride>(a_t, x_t, i_t, kRh * hb, dsw, odd_grp, gsc, head, nvalid, edge_rows);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_gate(st));
+        }
     } else if (warp >= kLookbackWarp0) {
         // ============================================================ look-back
         // kLookbackWarps warps share the work units round-robin, so several carry resolutions
@@ -862,13 +959,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             // rows of this group that exist in the sequence (fewer than kR only in the last row block)
             const int64_t left = p.T - row0 - (int64_t)grp * kR;
             const int nvalid = left >= kR ? kR : (left > 0 ? (int)left : 0);
-            // gated forward: this lane's channel scales, fetched while the tile is still on its way
-            float gsc[V];
-            if (kGate) {
-                const int64_t dch = (int64_t)u.cg * Dc + cl * V;
-#pragma unroll
-                for (int v = 0; v < V; ++v) gsc[v] = dch + v < p.D ? Gate<T>::prescale(gate_scale(p.lambda[dch + v])) : 0.0f;
-            }
             if (i >= kGens) {      // the summary buffers of this generation are free once pass 2 of unit i-kGens is done
                 const int o = i - kGens;
                 if (!ctl.wait(bar_done((int)(o % kStages)), (uint32_t)((o / kStages) & 1), FSS_STATUS_LOOKBACK_TIMEOUT)) break;
@@ -876,9 +966,8 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             if (!ctl.wait(bar_full(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
             Raw *a_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + lane_off);
             Raw *x_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + kTileBytes + lane_off);
-            // gated forward: the alpha slot arrives holding r, the third slot i; this pass turns them
-            // into alpha and beta in place (rounded to the I/O type, as if they had come from memory)
-            const Raw *i_t = reinterpret_cast<const Raw *>(smem_raw + st * SM::kStageBytes + 2 * kTileBytes + lane_off);
+            // gated forward: the gate warps turn the stage into (alpha, beta), edge rows included
+            if (kGate && !ctl.wait(bar_gate(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
             // row 0 of the whole sequence: alpha_0 is not part of the recurrence
             if (!kGate && head) a_t[0] = Lane<T>::zero();
             // rows past the end of the sequence arrive zero-filled; alpha = 1 (beta, grad = 0) makes
@@ -901,46 +990,6 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
                 }
                 pair_fix<kPairSwap>(ra, odd_grp);
                 pair_fix<kPairSwap>(rx, odd_grp);
-                if (kGate) {
-                    const bool edge_rows = __any_sync(0xffffffffu, head || nvalid < kR);
-                    Raw rg[kRh];
-#pragma unroll
-                    for (int r = 0; r < kRh; ++r) rg[r] = pair_slot<kRowStride>(i_t, base + r, dsw);
-                    pair_fix<kPairSwap>(rg, odd_grp);
-#pragma unroll
-                    for (int r = 0; r < kRh; ++r) {
-                        float rr[V], ii[V], xx[V], a[V], b[V];
-                        Lane<T>::unpack(ra[r], rr);
-                        Lane<T>::unpack(rg[r], ii);
-                        Lane<T>::unpack(rx[r], xx);
-#pragma unroll
-                        for (int v = 0; v < V; ++v) {
-                            a[v] = Gate<T>::exp_scaled(gsc[v] * Gate<T>::sigmoid(rr[v]));
-                            b[v] = Gate<T>::root(fmaf(-a[v], a[v], 1.0f)) * Gate<T>::sigmoid(ii[v]) * xx[v];
-                        }
-                        if (edge_rows) {       // warp-uniform and rare: first row of the sequence, rows after its end
-                            const bool first_row = head && base + r == 0;   // alpha_0 is not part of the recurrence
-                            const bool past_end = base + r >= nvalid;       // identity rows after the sequence
-#pragma unroll
-                            for (int v = 0; v < V; ++v) {
-                                if (first_row) a[v] = 0.0f;
-                                if (past_end) { a[v] = 1.0f; b[v] = 0.0f; }
-                            }
-                        }
-                        ra[r] = Lane<T>::pack(a);
-                        rx[r] = Lane<T>::pack(b);
-                    }
-                    Raw wa[kRh], wx[kRh];
-#pragma unroll
-                    for (int r = 0; r < kRh; ++r) { wa[r] = ra[r]; wx[r] = rx[r]; }
-                    pair_fix<kPairSwap>(wa, odd_grp);
-                    pair_fix<kPairSwap>(wx, odd_grp);
-#pragma unroll
-                    for (int r = 0; r < kRh; ++r) {
-                        pair_slot<kRowStride>(a_t, base + r, dsw) = wa[r];
-                        pair_slot<kRowStride>(x_t, base + r, dsw) = wx[r];
-                    }
-                }
 #pragma unroll
                 for (int j = 0; j < kRh; ++j) {
                     const int r = kBackward ? kRh - 1 - j : j;
@@ -1255,7 +1304,7 @@ template <typename T, bool kBackward, int kSp, bool kTickets, bool kGate> inline
         *err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (*err != cudaSuccess) return 0;
         int per_sm = 0, sms = 0;
-        *err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem_bytes);
+        *err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads_of<kGate>(), smem_bytes);
         if (*err != cudaSuccess) return 0;
         *err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         if (*err != cudaSuccess) return 0;
@@ -1331,7 +1380,7 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(threads_of<kGate>());
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = (cudaStream_t)ctx->stream;
     cudaLaunchAttribute attr[1];

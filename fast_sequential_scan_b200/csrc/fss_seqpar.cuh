@@ -35,23 +35,24 @@ __global__ void compose(int backward, int world, int rank, int64_t n,
 
 // ------------------------------------------------------------------ carry exchange through peer memory
 // Instead of a library all-gather, every rank can write its (product, state) pair straight into the
-// gather tables of all ranks of the box (plain stores to peer-mapped memory: NVLink / NVSwitch), and
-// then raise a flag there.  The consumer waits -- bounded -- for the flags of the ranks whose maps it
-// folds.  For the 32 KB pairs of a long-context run this takes a few microseconds where the
-// library collective costs 20-30.
+// gather tables of all ranks of the box with plain stores to peer-mapped memory (NVLink /
+// NVSwitch).  The values travel as 8-byte cells {fp32 value, 32-bit epoch}: an aligned 64-bit store
+// arrives whole, so a cell that carries the epoch of the current exchange holds the value written
+// with it -- no flag word, no fence, no second round trip; the consumer simply polls (bounded) the
+// cells it needs.  For the 32 KB pairs of a long-context run the exchange then costs a small launch
+// on the producer's side where the library collective costs 20-50 microseconds.
 //
-// Rank q owns  table[q] = [world][2][n] floats  and  words[q] = 2*world + 2 32-bit words:
-//   words[q][r]          epoch of the last pair rank r wrote into table[q][r]
-//   words[q][world + r]  epoch of the last exchange whose pair from rank q rank r has finished reading
-//   words[q][2*world], [2*world + 1]   counters of the two kernels below (local use)
-// Exchange number `epoch` (1, 2, ...; never 0, so nothing is ever cleared): rank r fills table[q][r]
-// for every q, then sets words[q][r] = epoch.  Before it overwrites its slot it waits until every
-// reader of that slot (forward: the ranks after r; backward: the ranks before r) has acknowledged
-// exchange epoch - 1; in a training loop that is always already the case, in a forward-only loop
-// it keeps a fast rank from running more than one exchange ahead of a slow reader.
+// Rank q owns  table[q] = [world][2][n] cells  and  words[q] = world + 1 32-bit words:
+//   words[q][r]      epoch of the last exchange whose pair from rank q rank r has finished reading
+//   words[q][world]  counter of the acknowledging kernel (local use)
+// Exchange number `epoch` (1, 2, ...; never 0, so nothing is ever cleared).  Before rank r
+// overwrites its slot it waits until every reader of that slot (forward: the ranks after r;
+// backward: the ranks before r) has acknowledged exchange epoch - 1; in a training loop that is
+// always already the case, in a forward-only loop it keeps a fast rank from running more than one
+// exchange ahead of a slow reader.
 constexpr int kMaxPeers = 16;
 struct PeerTables {
-    float *table[kMaxPeers];
+    unsigned long long *table[kMaxPeers];
     uint32_t *words[kMaxPeers];
 };
 constexpr int kPushThreads = 256;
@@ -64,6 +65,25 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_cell(unsigned long long *p, float x, uint32_t epoch) {
+    const unsigned long long c = (unsigned long long)__float_as_uint(x) | ((unsigned long long)epoch << 32);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(c) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_cell(const unsigned long long *p) {
+    unsigned long long c;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(c) : "l"(p) : "memory");
+    return c;
+}
+// the value of a cell once it carries `epoch` (bounded poll); false = it never did
+__device__ __forceinline__ bool wait_cell(const unsigned long long *p, uint32_t epoch, uint32_t max_spins, float *out) {
+    uint32_t spins = 0;
+    for (;;) {
+        const unsigned long long c = ld_cell(p);
+        if ((uint32_t)(c >> 32) == epoch) { *out = __uint_as_float((uint32_t)c); return true; }
+        if (++spins >= max_spins) return false;
+        __nanosleep(32);
+    }
+}
 // true when *p has reached `want` (epochs only grow) within max_spins polls
 __device__ __forceinline__ bool wait_epoch(const uint32_t *p, uint32_t want, uint32_t max_spins) {
     uint32_t spins = 0;
@@ -74,18 +94,17 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t *p, uint32_t want, uin
     return true;
 }
 
-// prod, state: this rank's two [n] vectors (local).  The last CTA to finish raises the flags.
+// prod, state: this rank's two [n] vectors (local).  Writes them as cells into slot `rank` of every table.
 __global__ void __launch_bounds__(kPushThreads)
 peer_push(PeerTables peers, int backward, int world, int rank, int64_t n, const float *__restrict__ prod,
           const float *__restrict__ state, uint32_t epoch, int32_t *status, uint32_t max_spins) {
     __shared__ int ok;
-    __shared__ bool last;
     if (threadIdx.x == 0) ok = 1;
     __syncthreads();
     // readers of this rank's slot must be done with the previous exchange
     const int lo = backward ? 0 : rank + 1, hi = backward ? rank : world;
     if ((int)threadIdx.x >= lo && (int)threadIdx.x < hi && epoch > 1) {
-        if (!wait_epoch(peers.words[rank] + world + threadIdx.x, epoch - 1, max_spins)) ok = 0;
+        if (!wait_epoch(peers.words[rank] + threadIdx.x, epoch - 1, max_spins)) ok = 0;
     }
     __syncthreads();
     if (!ok) {
@@ -93,84 +112,198 @@ peer_push(PeerTables peers, int backward, int world, int rank, int64_t n, const 
         return;
     }
     const int64_t base = (int64_t)rank * 2 * n;
-    const bool vec = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(prod) | reinterpret_cast<uintptr_t>(state)) & 15u) == 0;
-    for (int half = 0; half < 2; ++half) {
-        const float *src = half ? state : prod;
-        const int64_t off = base + (int64_t)half * n;
-        for (int64_t i = ((int64_t)blockIdx.x * kPushThreads + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * kPushThreads * 4) {
-            if (vec) {
-                const float4 v = *reinterpret_cast<const float4 *>(src + i);
-                for (int q = 0; q < world; ++q) *reinterpret_cast<float4 *>(peers.table[q] + off + i) = v;
-            } else {
-                for (int64_t k = i; k < n && k < i + 4; ++k) {
-                    const float v = src[k];
-                    for (int q = 0; q < world; ++q) peers.table[q][off + k] = v;
-                }
-            }
-        }
-    }
-    __threadfence_system();      // this thread's stores before anything that follows, for every observer
-    __syncthreads();
-    uint32_t *counter = peers.words[rank] + 2 * world;      // local
-    if (threadIdx.x == 0) {
-        const uint32_t done = atomicAdd(counter, 1u);
-        last = (done + 1 == gridDim.x);
-        if (last) *counter = 0;
-    }
-    __syncthreads();
-    if (last && (int)threadIdx.x < world) {
-        __threadfence_system();
-        st_release_sys(peers.words[threadIdx.x] + rank, epoch);
+    for (int64_t i = (int64_t)blockIdx.x * kPushThreads + threadIdx.x; i < 2 * n; i += (int64_t)gridDim.x * kPushThreads) {
+        const float v = i < n ? prod[i] : state[i - n];
+        for (int q = 0; q < world; ++q) st_cell(peers.table[q] + base + i, v, epoch);
     }
 }
 
-// Waits for the pairs of the ranks this rank folds (forward: ranks before it; backward: ranks after
-// it), composes them like `compose`, and acknowledges the exchange to those ranks.  Every wait is
-// bounded: when one runs out the status word is set to FSS_STATUS_EXCHANGE_TIMEOUT and the kernel
-// leaves (carry_in is then undefined).
-__global__ void __launch_bounds__(256)
-peer_compose(PeerTables peers, int backward, int world, int rank, int64_t n, uint32_t epoch,
-             float *__restrict__ carry_in, int32_t *status, uint32_t max_spins) {
+// The forward's push fused with the fold of the per-block products: prod[b, d] = product over the
+// row blocks of block_prod[b, :, d] is computed here (a CTA owns 8 channel vectors of one batch row,
+// its 64 thread rows split the blocks and combine through shared memory), written to prod_out for
+// the caller to keep, and sent to every table together with the state -- one launch instead of two
+// between the local scan and the exchange.
+constexpr int kPushSlices = 64, kPushVecs = 8;
+__global__ void __launch_bounds__(kPushSlices * kPushVecs)
+peer_push_blocks(PeerTables peers, int world, int rank, int64_t S, int64_t D, const float *__restrict__ block_prod,
+                 const float *__restrict__ state, float *__restrict__ prod_out, uint32_t epoch, int32_t *status,
+                 uint32_t max_spins) {
+    __shared__ float4 part[kPushSlices][kPushVecs];
     __shared__ int ok;
-    __shared__ bool last;
     if (threadIdx.x == 0) ok = 1;
     __syncthreads();
-    const float *table = peers.table[rank];
-    const int lo = backward ? rank + 1 : 0, hi = backward ? world : rank;
-    if ((int)threadIdx.x >= lo && (int)threadIdx.x < hi) {
-        if (!wait_epoch(peers.words[rank] + threadIdx.x, epoch, max_spins)) ok = 0;
+    if ((int)threadIdx.x > rank && (int)threadIdx.x < world && epoch > 1) {      // forward: the later ranks read this slot
+        if (!wait_epoch(peers.words[rank] + threadIdx.x, epoch - 1, max_spins)) ok = 0;
     }
+    const int vec = threadIdx.x % kPushVecs, slice = threadIdx.x / kPushVecs;
+    const int64_t b = blockIdx.y, B = gridDim.y;
+    const int64_t d0 = ((int64_t)blockIdx.x * kPushVecs + vec) * 4;
+    const int64_t n = B * D;
+    float4 acc = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    if (d0 < D) {      // D is a multiple of 4 here (checked by the launcher)
+        const float *base = block_prod + b * S * D + d0;
+#pragma unroll 4
+        for (int64_t s = slice; s < S; s += kPushSlices) {
+            const float4 v = *reinterpret_cast<const float4 *>(base + s * D);
+            acc.x *= v.x; acc.y *= v.y; acc.z *= v.z; acc.w *= v.w;
+        }
+    }
+    part[slice][vec] = acc;
     __syncthreads();
+    for (int half = kPushSlices / 2; half > 0; half /= 2) {
+        if (slice < half) {
+            const float4 o = part[slice + half][vec];
+            float4 m = part[slice][vec];
+            m.x *= o.x; m.y *= o.y; m.z *= o.z; m.w *= o.w;
+            part[slice][vec] = m;
+        }
+        __syncthreads();
+    }
     if (!ok) {
-        if (threadIdx.x == 0 && blockIdx.x == 0) report_status(status, FSS_STATUS_EXCHANGE_TIMEOUT);
+        if (threadIdx.x == 0 && blockIdx.x + blockIdx.y == 0) report_status(status, FSS_STATUS_EXCHANGE_TIMEOUT);
         return;
     }
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) {
-        float carry = 0.0f;
-        if (!backward) {
-            for (int r = 0; r < rank; ++r)
-                carry = fold(__ldcg(table + ((int64_t)r * 2 + 0) * n + i), carry, __ldcg(table + ((int64_t)r * 2 + 1) * n + i));
+    if (slice < 2 && d0 < D) {      // thread row 0 sends the products, thread row 1 the states
+        const int64_t i = b * D + d0;
+        float4 v;
+        if (slice == 0) {
+            v = part[0][vec];
+            *reinterpret_cast<float4 *>(prod_out + i) = v;
         } else {
-            for (int r = world - 1; r > rank; --r)
-                carry = fold(__ldcg(table + ((int64_t)r * 2 + 0) * n + i), carry, __ldcg(table + ((int64_t)r * 2 + 1) * n + i));
+            v = *reinterpret_cast<const float4 *>(state + i);
         }
-        carry_in[i] = carry;
+        const int64_t off = (int64_t)rank * 2 * n + (int64_t)slice * n + i;
+        for (int q = 0; q < world; ++q) {
+            unsigned long long *t = peers.table[q] + off;
+            st_cell(t, v.x, epoch); st_cell(t + 1, v.y, epoch); st_cell(t + 2, v.z, epoch); st_cell(t + 3, v.w, epoch);
+        }
     }
-    // the last CTA tells the writers that their slots may be reused
+}
+
+// A reader's acknowledgement: after ALL CTAs of the consuming kernel have read the pairs, its last
+// CTA tells the writers (ranks lo .. hi-1) that their slots may be reused.
+__device__ __forceinline__ void acknowledge(const PeerTables &peers, int world, int rank, int lo, int hi, uint32_t epoch) {
+    __shared__ bool last;
     __syncthreads();
-    uint32_t *counter = peers.words[rank] + 2 * world + 1;
+    uint32_t *counter = peers.words[rank] + world;
     if (threadIdx.x == 0) {
         __threadfence();
         const uint32_t done = atomicAdd(counter, 1u);
-        last = (done + 1 == gridDim.x);
+        last = (done + 1 == gridDim.x * gridDim.y * gridDim.z);
         if (last) *counter = 0;
     }
     __syncthreads();
     if (last && (int)threadIdx.x >= lo && (int)threadIdx.x < hi) {
         __threadfence_system();
-        st_release_sys(peers.words[threadIdx.x] + world + rank, epoch);
+        st_release_sys(peers.words[threadIdx.x] + rank, epoch);
     }
+}
+
+// Folds the cells of the ranks this rank depends on (forward: ranks before it; backward: ranks after
+// it) for V consecutive channels starting at idx; false = a cell never arrived.
+template <int V>
+__device__ __forceinline__ bool fold_cells(const unsigned long long *table, int64_t n, int64_t idx, int lo, int hi,
+                                           bool backward, uint32_t epoch, uint32_t max_spins, float (&carry)[V]) {
+    bool ok = true;
+    for (int k = 0; k < hi - lo && ok; ++k) {
+        const int r = backward ? hi - 1 - k : lo + k;
+        const unsigned long long *p = table + ((int64_t)r * 2) * n + idx;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            float P, C;
+            ok = ok && wait_cell(p + i, epoch, max_spins, &P) && wait_cell(p + n + i, epoch, max_spins, &C);
+            if (ok) carry[i] = fold(P, carry[i], C);
+        }
+    }
+    return ok;
+}
+
+// The stand-alone consumer: waits for the pairs, composes them like `compose`, acknowledges.  Every
+// wait is bounded: when one runs out the status word is set to FSS_STATUS_EXCHANGE_TIMEOUT
+// (carry_in is then undefined).
+__global__ void __launch_bounds__(256)
+peer_compose(PeerTables peers, int backward, int world, int rank, int64_t n, uint32_t epoch,
+             float *__restrict__ carry_in, int32_t *status, uint32_t max_spins) {
+    const int lo = backward ? rank + 1 : 0, hi = backward ? world : rank;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    bool ok = true;
+    if (i < n) {
+        float carry[1] = {0.0f};
+        ok = fold_cells<1>(peers.table[rank], n, i, lo, hi, backward != 0, epoch, max_spins, carry);
+        carry_in[i] = carry[0];
+    }
+    if (__syncthreads_or(!ok)) {
+        if (threadIdx.x == 0) report_status(status, FSS_STATUS_EXCHANGE_TIMEOUT);
+        return;      // no acknowledgement: the writers must not reuse what was not read
+    }
+    acknowledge(peers, world, rank, lo, hi, epoch);
+}
+
+// V consecutive floats, as 16-byte loads when the address allows it
+template <int V> __device__ __forceinline__ void load_floats(const float *__restrict__ p, float (&out)[V]) {
+    if (V % 4 == 0 && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+#pragma unroll
+        for (int i = 0; i < V / 4; ++i) {
+            const float4 q = reinterpret_cast<const float4 *>(p)[i];
+            out[4 * i] = q.x; out[4 * i + 1] = q.y; out[4 * i + 2] = q.z; out[4 * i + 3] = q.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) out[i] = p[i];
+    }
+}
+
+// ------------------------------------------------------------------ where a fix-up gets its carry from
+// Either a ready-made vector (world == 0), or the gathered table of pairs, which the fix-up kernel
+// then folds itself -- plain floats filled by a collective (epoch == 0), or the cells of a peer
+// exchange, polled until they carry `epoch` and acknowledged afterwards -- so that no separate
+// composition launch sits between the exchange and the fix-up.
+struct CarrySource {
+    const float *carry;      // [B*D], used when world == 0
+    const float *table;      // [world][2][n] floats in local memory (epoch == 0)
+    PeerTables peers;        // cells and control words (epoch != 0)
+    float *carry_out;        // optional [n]: the folded carry, for the caller to keep
+    int64_t n;
+    int32_t world, rank;
+    uint32_t epoch, max_spins;
+};
+
+// Every thread of the CTA calls this; false = a wait ran out (reported; the caller returns).
+template <int V>
+__device__ __forceinline__ bool obtain_carry(const CarrySource &src, bool backward, int64_t idx, bool has, bool writer,
+                                             float (&carry)[V], int32_t *status) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) carry[i] = 0.0f;
+    if (src.world == 0) {
+        if (has) load_floats<V>(src.carry + idx, carry);
+        return true;
+    }
+    const int lo = backward ? src.rank + 1 : 0, hi = backward ? src.world : src.rank;
+    bool ok = true;
+    if (has) {
+        if (src.epoch) {
+            ok = fold_cells<V>(src.peers.table[src.rank], src.n, idx, lo, hi, backward, src.epoch, src.max_spins, carry);
+        } else {
+            for (int k = 0; k < hi - lo; ++k) {
+                const int r = backward ? hi - 1 - k : lo + k;      // forward: ranks 0..rank-1; backward: world-1 down to rank+1
+                const float *p = src.table + ((int64_t)r * 2) * src.n + idx;
+#pragma unroll
+                for (int i = 0; i < V; ++i) carry[i] = fold(__ldcg(p + i), carry[i], __ldcg(p + src.n + i));
+            }
+        }
+        if (ok && writer && src.carry_out) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) src.carry_out[idx + i] = carry[i];
+        }
+    }
+    if (src.epoch) {
+        if (__syncthreads_or(!ok)) {
+            if (threadIdx.x == 0 && blockIdx.x + blockIdx.y + blockIdx.z == 0) report_status(status, FSS_STATUS_EXCHANGE_TIMEOUT);
+            return false;
+        }
+        acknowledge(src.peers, src.world, src.rank, lo, hi, src.epoch);
+    }
+    return true;
 }
 
 // ------------------------------------------------------------------ fix-up
@@ -198,20 +331,6 @@ struct Geometry {
     int64_t nvec, vblocks;   // channel vectors per row, CTAs along the channel axis (32 vectors each)
     int slots;        // CTAs along the block axis
 };
-
-// V consecutive floats, as 16-byte loads when the address allows it
-template <int V> __device__ __forceinline__ void load_floats(const float *__restrict__ p, float (&out)[V]) {
-    if (V % 4 == 0 && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
-#pragma unroll
-        for (int i = 0; i < V / 4; ++i) {
-            const float4 q = reinterpret_cast<const float4 *>(p)[i];
-            out[4 * i] = q.x; out[4 * i + 1] = q.y; out[4 * i + 2] = q.z; out[4 * i + 3] = q.w;
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < V; ++i) out[i] = p[i];
-    }
-}
 
 inline int choose_slots(int64_t NB, int64_t vblocks, int64_t B, int sms) {
     // one CTA per SM in total (a CTA takes a whole SM's registers); a column whose carry reaches
@@ -253,8 +372,8 @@ __device__ __forceinline__ void block_range_product(const float *__restrict__ bp
 
 template <typename T, int V>
 __global__ void __launch_bounds__(kFixThreads)
-fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, const float *__restrict__ carry_in,
-              const float *__restrict__ block_prod, const float *__restrict__ block_state) {
+fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, const CarrySource src,
+              const float *__restrict__ block_prod, const float *__restrict__ block_state, int32_t *status) {
     __shared__ float sP[kFixWarps * 32 * V], sC[kFixWarps * 32 * V];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t b = blockIdx.z;
@@ -265,8 +384,8 @@ fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, co
     const float *bs_col = block_state + b * g.NB * g.D + d0;
     float carry[V], run[V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) { carry[i] = 0.0f; run[i] = 1.0f; }
-    if (has) load_floats<V>(carry_in + b * g.D + d0, carry);
+    for (int i = 0; i < V; ++i) run[i] = 1.0f;
+    if (!obtain_carry<V>(src, false, b * g.D + d0, has, blockIdx.x == 0, carry, status)) return;
 
     int64_t done = 0;      // blocks whose product is already in `run`
     for (int64_t j = blockIdx.x; j < g.NB; j += g.slots) {
@@ -357,8 +476,9 @@ fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, co
 template <typename T, int V>
 __global__ void __launch_bounds__(kFixThreads)
 fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> grad, View<T> dalpha,
-               View<T> dbeta, const float *__restrict__ u_in, const float *__restrict__ h_prev,
-               const float *__restrict__ block_prod, const float *__restrict__ block_state, bool continuation) {
+               View<T> dbeta, const CarrySource src, const float *__restrict__ h_prev,
+               const float *__restrict__ block_prod, const float *__restrict__ block_state, bool continuation,
+               int32_t *status) {
     __shared__ float sP[kFixWarps * 32 * V], sC[kFixWarps * 32 * V];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t b = blockIdx.z;
@@ -369,8 +489,8 @@ fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> g
     const float *bs_col = block_state + b * g.NB * g.D + d0;
     float carry[V], run[V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) { carry[i] = 0.0f; run[i] = 1.0f; }
-    if (has) load_floats<V>(u_in + b * g.D + d0, carry);
+    for (int i = 0; i < V; ++i) run[i] = 1.0f;
+    if (!obtain_carry<V>(src, true, b * g.D + d0, has, blockIdx.x == 0, carry, status)) return;
 
     int64_t done = g.NB;      // blocks [done, NB) are already in `run`
     for (int64_t k = blockIdx.x; k < g.NB; k += g.slots) {

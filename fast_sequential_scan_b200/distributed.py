@@ -39,9 +39,10 @@ def shard_channels(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
 class PeerExchange:
     """Carry exchange through peer memory: every rank's gather table and control words are allocated
     in torch's symmetric memory, so that each process holds device pointers to the tables of all GPUs
-    of the box; a push kernel writes this rank's pair into every table with plain stores over NVLink
-    and publishes an epoch, and the consumer waits (bounded) for the epochs it needs and acknowledges
-    them.  One instance serves one direction of one shape; exchanges are numbered from 1."""
+    of the box; a push kernel writes this rank's pair into every table with plain stores over NVLink,
+    as 8-byte cells that carry the exchange number, and the consumer polls (bounded) the cells it needs
+    and acknowledges them.  One instance serves one direction of one shape; exchanges are numbered
+    from 1."""
 
     def __init__(self, n: int, device: torch.device, backward: bool, group=None):
         import ctypes
@@ -51,14 +52,14 @@ class PeerExchange:
         if self.world > 16:
             raise RuntimeError("peer exchange serves at most 16 ranks")
         self.n, self.device, self.backward = n, device, backward
-        words = self.world * 2 * n
-        # one allocation: the table, then the control words (epochs start at 1, so zero = nothing yet)
-        self.buf = symm_mem.empty(words + 64, dtype=torch.float32, device=device)
+        cell_floats = self.world * 2 * n * 2          # 8-byte cells {value, exchange number}
+        # one allocation: the cells, then the control words (exchange numbers start at 1, so zero = nothing yet)
+        self.buf = symm_mem.empty(cell_floats + 64, dtype=torch.float32, device=device)
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, group.group_name)
         ptrs = list(self.handle.buffer_ptrs)
         self.tables = (ctypes.c_void_p * self.world)(*ptrs)
-        self.words = (ctypes.c_void_p * self.world)(*[p + words * 4 for p in ptrs])
+        self.words = (ctypes.c_void_p * self.world)(*[p + cell_floats * 4 for p in ptrs])
         self.epoch = 0
         torch.cuda.synchronize(device)
         dist.barrier(group)                 # every table is zeroed before anyone pushes
@@ -130,8 +131,10 @@ class NativeOps:
         algo = self._algo_for(alpha, beta)
         send, bp, bs, R = self._buffers("fwd", alpha, algo)
         h = torch.empty_like(alpha)
+        # with the peer exchange the product over the rows is folded by the push kernel (one launch less)
+        self._prod_pending = self.exchange == "peer" and D % 4 == 0
         native.forward_into(alpha, beta, h, algo=algo, continuation=continuation, h_last=send[1].view(B, D),
-                            prod=send[0].view(B, D), block_prod=bp, block_state=bs)
+                            prod=None if self._prod_pending else send[0].view(B, D), block_prod=bp, block_state=bs)
         return h, send, (bp, bs, R)
 
     def local_backward(self, alpha, h, grad, continuation: bool, h_prev, prod):
@@ -162,6 +165,48 @@ class NativeOps:
     def fixup_forward(self, alpha, beta, h, carry_in, blocks):
         from . import sequential_scan_cuda as native
         native.seqpar_fixup_forward(alpha, beta, h, carry_in, blocks[0], blocks[1], blocks[2])
+
+    # The fix-up kernels can fold the exchanged table themselves (one launch less per direction): these two
+    # are what seqpar_forward / seqpar_backward use when the ops object has them.
+    def exchange_and_fixup_forward(self, alpha, beta, h, send, prod, blocks, rank: int, world: int, group, mark):
+        from . import sequential_scan_cuda as native
+        if self.exchange == "peer":
+            peer = self.peer("fwd", send, group)
+            if getattr(self, "_prod_pending", False):
+                peer.epoch += 1
+                epoch = peer.epoch
+                native.seqpar_push_blocks(blocks[0], send[1], send[0], rank, peer.tables, peer.words, epoch)
+            else:
+                epoch = peer.push(prod.reshape(-1), send[1])
+            mark("fwd_gather")
+            if rank == 0:
+                return None
+            return native.seqpar_fixup_forward_from(alpha, beta, h, None, rank, blocks[0], blocks[1], blocks[2],
+                                                    peer_tables=peer.tables, peer_words=peer.words, epoch=epoch)
+        pc = _gather(send, group, self, "fwd")
+        mark("fwd_gather")
+        if rank == 0:
+            return None
+        return native.seqpar_fixup_forward_from(alpha, beta, h, pc, rank, blocks[0], blocks[1], blocks[2])
+
+    def exchange_and_fixup_backward(self, alpha, h, grad, da, db, send, prod, h_prev, blocks, rank: int, world: int,
+                                    continuation: bool, group, mark):
+        from . import sequential_scan_cuda as native
+        if self.exchange == "peer":
+            peer = self.peer("bwd", send, group)
+            epoch = peer.push(prod.reshape(-1), send[1])
+            mark("bwd_gather")
+            if rank == world - 1:
+                return None
+            return native.seqpar_fixup_backward_from(alpha, h, grad, da, db, None, rank, h_prev, blocks[0], blocks[1],
+                                                     blocks[2], continuation, peer_tables=peer.tables,
+                                                     peer_words=peer.words, epoch=epoch)
+        pc = _gather(send, group, self, "bwd")
+        mark("bwd_gather")
+        if rank == world - 1:
+            return None
+        return native.seqpar_fixup_backward_from(alpha, h, grad, da, db, pc, rank, h_prev, blocks[0], blocks[1], blocks[2],
+                                                 continuation)
 
     def fixup_backward(self, alpha, h, grad, da, db, u_in, h_prev, blocks, continuation: bool):
         from . import sequential_scan_cuda as native
@@ -215,10 +260,13 @@ def seqpar_forward(alpha, beta, group=None, ops=None, mark=_no_mark):
     B, T, D = alpha.shape
     h, send, blocks = ops.local_forward(alpha, beta, continuation=rank > 0)
     mark("fwd_local")
-    carry_in = _exchange_and_compose(ops, "fwd", send, send[0], rank, world, False, rank > 0, group, mark)
-    if carry_in is not None:
-        carry_in = carry_in.reshape(B, D)
-        ops.fixup_forward(alpha, beta, h, carry_in, blocks)
+    if world > 1 and hasattr(ops, "exchange_and_fixup_forward"):
+        carry_in = ops.exchange_and_fixup_forward(alpha, beta, h, send, send[0], blocks, rank, world, group, mark)
+    else:
+        carry_in = _exchange_and_compose(ops, "fwd", send, send[0], rank, world, False, rank > 0, group, mark)
+        if carry_in is not None:
+            carry_in = carry_in.reshape(B, D)
+            ops.fixup_forward(alpha, beta, h, carry_in, blocks)
     mark("fwd_fixup")
     return h, dict(carry_in=carry_in, prod=send[0].clone())
 
@@ -231,9 +279,13 @@ def seqpar_backward(alpha, h, grad, saved, group=None, ops=None, mark=_no_mark):
     h_prev = saved["carry_in"]
     da, db, send, blocks = ops.local_backward(alpha, h, grad, continuation=rank > 0, h_prev=h_prev, prod=saved["prod"])
     mark("bwd_local")
-    u_in = _exchange_and_compose(ops, "bwd", send, saved["prod"], rank, world, True, rank < world - 1, group, mark)
-    if u_in is not None:
-        ops.fixup_backward(alpha, h, grad, da, db, u_in.reshape(B, D), h_prev, blocks, continuation=rank > 0)
+    if world > 1 and hasattr(ops, "exchange_and_fixup_backward"):
+        ops.exchange_and_fixup_backward(alpha, h, grad, da, db, send, saved["prod"], h_prev, blocks, rank, world,
+                                        rank > 0, group, mark)
+    else:
+        u_in = _exchange_and_compose(ops, "bwd", send, saved["prod"], rank, world, True, rank < world - 1, group, mark)
+        if u_in is not None:
+            ops.fixup_backward(alpha, h, grad, da, db, u_in.reshape(B, D), h_prev, blocks, continuation=rank > 0)
     mark("bwd_fixup")
     return da, db
 

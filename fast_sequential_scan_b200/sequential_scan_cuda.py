@@ -425,6 +425,19 @@ def seqpar_push(prod: torch.Tensor, state: torch.Tensor, rank: int, backward: bo
     _lib.check(rc, "fss_seqpar_push")
 
 
+def seqpar_push_blocks(block_prod: torch.Tensor, state: torch.Tensor, prod_out: torch.Tensor, rank: int, peer_tables,
+                       peer_words, epoch: int) -> None:
+    """Forward push fused with the fold of the per-block products (``fss_seqpar_push_blocks``): ``block_prod``
+    ``[B, nblocks, D]``, ``state`` and ``prod_out`` ``[B*D]`` fp32; raises ``FssError(E_LAYOUT)`` when D is not a
+    multiple of 4."""
+    B, nb, D = block_prod.shape
+    ws = workspace.get(state.device, 1 << 16)
+    ctx = _ctx(state.device, ws, None)
+    rc = _lib.lib().fss_seqpar_push_blocks(ctypes.byref(ctx), len(peer_tables), rank, B, nb, D, _blocks(block_prod, "block_prod"),
+                                           state.data_ptr(), prod_out.data_ptr(), peer_tables, peer_words, epoch)
+    _lib.check(rc, "fss_seqpar_push_blocks")
+
+
 def seqpar_compose_peer(n: int, device: torch.device, rank: int, backward: bool, peer_tables, peer_words, epoch: int,
                         short_waits: bool = False) -> torch.Tensor:
     """``fss_seqpar_compose_peer``: wait (bounded) for the pairs this rank folds, compose them, acknowledge."""
@@ -472,3 +485,54 @@ def seqpar_fixup_backward(alpha, h, grad_out, grad_alpha, grad_beta, u_in, h_pre
                                                   _blocks(block_prod, "block_prod"),
                                                   _blocks(block_state, "block_state"), rows_per_block)
     _lib.check(rc, "fss_seqpar_fixup_backward")
+
+
+def _carry_source(table: Optional[torch.Tensor], rank: int, peer_tables, peer_words, epoch: int, carry_out: torch.Tensor):
+    if epoch:                      # cells of a peer exchange: the table lives behind peer_tables[rank]
+        return _lib.CarrySource(len(peer_tables), rank, None, peer_tables, peer_words, epoch, carry_out.data_ptr())
+    if table.dtype != torch.float32 or not table.is_cuda or not table.is_contiguous() or table.dim() != 3 or table.shape[1] != 2:
+        raise RuntimeError("table: expected a contiguous fp32 CUDA tensor [world, 2, n]")
+    return _lib.CarrySource(table.shape[0], rank, table.data_ptr(), None, None, 0, carry_out.data_ptr())
+
+
+def seqpar_fixup_forward_from(alpha, beta, h, table, rank: int, block_prod, block_state, rows_per_block: int, *,
+                              peer_tables=None, peer_words=None, epoch: int = 0) -> torch.Tensor:
+    """Forward fix-up that folds the gathered ``[world, 2, B*D]`` table itself (``fss_seqpar_fixup_forward_from``);
+    with ``epoch`` it first waits for that peer exchange and acknowledges it.  Returns the folded carry ``[B, D]``."""
+    dtype = alpha.dtype
+    _check_tensor("alpha", alpha, None, dtype)
+    _check_tensor("beta", beta, alpha, dtype)
+    _check_tensor("h", h, alpha, dtype)
+    B, T, D = alpha.shape
+    a, b = _rowwise(alpha), _rowwise(beta)
+    carry = torch.empty(B, D, dtype=torch.float32, device=alpha.device)
+    src = _carry_source(table, rank, peer_tables, peer_words, epoch, carry)
+    va, vb, vh = _view(a), _view(b), _view(h)
+    ws = workspace.get(alpha.device, 1 << 16)
+    ctx = _ctx(alpha.device, ws, None, _lib.FLAG_CONTINUATION)
+    rc = _lib.lib().fss_seqpar_fixup_forward_from(ctypes.byref(ctx), _DTYPES[dtype], B, T, D, ctypes.byref(va), ctypes.byref(vb),
+                                                  ctypes.byref(vh), ctypes.byref(src), _blocks(block_prod, "block_prod"),
+                                                  _blocks(block_state, "block_state"), rows_per_block)
+    _lib.check(rc, "fss_seqpar_fixup_forward_from")
+    return carry
+
+
+def seqpar_fixup_backward_from(alpha, h, grad_out, grad_alpha, grad_beta, table, rank: int, h_prev, block_prod, block_state,
+                               rows_per_block: int, continuation: bool, *, peer_tables=None, peer_words=None,
+                               epoch: int = 0) -> torch.Tensor:
+    """Backward counterpart of :func:`seqpar_fixup_forward_from`; returns the folded ``u`` ``[B, D]``."""
+    dtype = alpha.dtype
+    B, T, D = alpha.shape
+    a, hh, g = _rowwise(alpha), _rowwise(h), _rowwise(grad_out)
+    views = [_view(t) for t in (a, hh, g, grad_alpha, grad_beta)]
+    u_in = torch.empty(B, D, dtype=torch.float32, device=alpha.device)
+    src = _carry_source(table, rank, peer_tables, peer_words, epoch, u_in)
+    ws = workspace.get(alpha.device, 1 << 16)
+    ctx = _ctx(alpha.device, ws, None, _lib.FLAG_CONTINUATION if continuation else 0)
+    rc = _lib.lib().fss_seqpar_fixup_backward_from(ctypes.byref(ctx), _DTYPES[dtype], B, T, D,
+                                                   *[ctypes.byref(v) for v in views], ctypes.byref(src),
+                                                   _vec(h_prev, B, D, "h_prev") if h_prev is not None else None,
+                                                   _blocks(block_prod, "block_prod"), _blocks(block_state, "block_state"),
+                                                   rows_per_block)
+    _lib.check(rc, "fss_seqpar_fixup_backward_from")
+    return u_in

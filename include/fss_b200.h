@@ -223,20 +223,30 @@ int fss_seqpar_compose(const fss_scan_ctx *ctx, int backward, int world, int ran
                        const float *pc, float *carry_in);
 /* Carry exchange through peer memory instead of a library all-gather (ranks = GPUs of one box whose
  * memory is mapped into each other's address space, e.g. with CUDA IPC or torch symmetric memory).
- * Rank q owns a table of world*2*n floats and 2*world+2 32-bit words, all zeroed once before the
- * first exchange (with a barrier between the zeroing and the first push of any rank).
- * peer_tables / peer_words are HOST arrays of `world` device pointers: entry q is rank q's table /
- * words as mapped in the calling process (entry `rank` is the caller's own, local memory).
- * fss_seqpar_push writes this rank's pair (prod[n], state[n]) into slot `rank` of every table
- * and then publishes `epoch` in every rank's words; epochs start at 1 and grow by one per exchange
- * over the same tables.  Before overwriting its slot the push waits until the readers of that slot
- * (forward: later ranks; backward: earlier ranks) have acknowledged exchange epoch-1.
- * fss_seqpar_compose_peer is fss_seqpar_compose on the caller's own table after a wait for the pairs
- * of the ranks it folds, followed by the acknowledgement.  Every wait is bounded; one that runs out
- * sets the status word to FSS_STATUS_EXCHANGE_TIMEOUT and the kernel returns.  world <= 16.  Plain
- * peer stores only: no multicast, no remote loads. */
+ * Rank q owns a table of world*2*n 8-byte cells {fp32 value, 32-bit exchange number} and world+1
+ * 32-bit words, all zeroed once before the first exchange (with a barrier between the zeroing and
+ * the first push of any rank).  peer_tables / peer_words are HOST arrays of `world` device pointers:
+ * entry q is rank q's table / words as mapped in the calling process (entry `rank` is the caller's
+ * own, local memory).
+ * fss_seqpar_push writes this rank's pair (prod[n], state[n]) as cells into slot `rank` of every
+ * table; exchange numbers (`epoch`) start at 1 and grow by one per exchange over the same tables.  A
+ * cell that carries the current epoch is complete by itself, so there is no flag and no fence.
+ * Before overwriting its slot the push waits until the readers of that slot (forward: later ranks;
+ * backward: earlier ranks) have acknowledged exchange epoch-1.
+ * fss_seqpar_compose_peer polls the cells of the ranks it folds, composes them like
+ * fss_seqpar_compose and acknowledges.  Every wait is bounded; one that runs out sets the status
+ * word to FSS_STATUS_EXCHANGE_TIMEOUT and the kernel returns.  world <= 16.  Plain peer stores only:
+ * no multicast, no remote loads. */
 int fss_seqpar_push(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n, const float *prod,
                     const float *state, void *const *peer_tables, void *const *peer_words, uint32_t epoch);
+/* The forward push fused with the fold of the per-block products that fss_scan_forward_ex wrote
+ * (block_prod [B][nblocks][D], state = h_last [B][D]): computes prod[b][d] = product over the blocks,
+ * stores it to prod_out [B][D] and pushes (prod, state) like fss_seqpar_push (forward direction).
+ * Needs D % 4 == 0 and 16-byte aligned vectors (else FSS_E_LAYOUT: use fss_scan_forward_ex's prod
+ * output and fss_seqpar_push). */
+int fss_seqpar_push_blocks(const fss_scan_ctx *ctx, int world, int rank, int64_t B, int64_t nblocks, int64_t D,
+                           const float *block_prod, const float *state, float *prod_out,
+                           void *const *peer_tables, void *const *peer_words, uint32_t epoch);
 int fss_seqpar_compose_peer(const fss_scan_ctx *ctx, int backward, int world, int rank, int64_t n,
                             void *const *peer_tables, void *const *peer_words, uint32_t epoch,
                             float *carry_in);
@@ -283,6 +293,35 @@ int fss_seqpar_fixup_backward(const fss_scan_ctx *ctx, int dtype, int64_t B, int
 #define FSS_NOALLOC_SCRATCH_BYTES (8u << 20)
 int fss_scan_forward_noalloc(int dtype, int device, void *stream, int64_t B, int64_t T, int64_t D,
                              const fss_view *alpha, const fss_view *beta, const fss_view *h);
+
+/* ---- fix-up that folds the exchanged pairs itself ----------------------------------------------
+ * The two fix-ups above take a ready-made carry (from fss_seqpar_compose[_peer]).  These variants
+ * take the gathered table instead and fold it in their prologue, which saves the composition launch
+ * between the exchange and the fix-up:
+ *   table       [world][2][B*D] floats in the caller's own memory, filled by a collective (epoch 0);
+ *   epoch       0 = `table` is complete when the kernel starts; otherwise the number of the peer
+ *               exchange whose cells (in this rank's entry of peer_tables) are polled -- bounded --
+ *               and then acknowledged; peer_tables / peer_words are the arrays given to
+ *               fss_seqpar_push, `table` is ignored;
+ *   carry_out   optional [B*D]: receives the folded carry (the state entering row 0 / the u arriving
+ *               after the last row), which the caller needs again (h_prev of the backward). */
+typedef struct fss_carry_source {
+    int32_t world, rank;
+    const float *table;
+    void *const *peer_tables;
+    void *const *peer_words;
+    uint32_t epoch;
+    float *carry_out;
+} fss_carry_source;
+int fss_seqpar_fixup_forward_from(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                                  const fss_view *alpha, const fss_view *beta, const fss_view *h,
+                                  const fss_carry_source *source, const float *block_prod,
+                                  const float *block_state, int64_t block_rows);
+int fss_seqpar_fixup_backward_from(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
+                                   const fss_view *alpha, const fss_view *h, const fss_view *grad_out,
+                                   const fss_view *grad_alpha, const fss_view *grad_beta,
+                                   const fss_carry_source *source, const float *h_prev, const float *block_prod,
+                                   const float *block_state, int64_t block_rows);
 
 #ifdef __cplusplus
 }

@@ -497,12 +497,15 @@ def test_lookback_descriptors_survive_reuse_with_different_data(shape):
     pkg.check_status()
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("algo", ["chunked", "auto"])
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
-def test_sequence_parallel_pieces_on_one_gpu(dtype, algo):
+def test_sequence_parallel_pieces_on_one_gpu(dtype, algo, fused):
     """The sequence-parallel protocol with its ranks played one after the other on one device:
     zero-state local scans with products, the gathered (product, state) table, carry folding and
-    the fix-up kernels, forward and backward, against the undivided scan."""
+    the fix-up kernels, forward and backward, against the undivided scan.  ``fused``: the fix-up kernels
+    fold the gathered table themselves (fss_seqpar_fixup_*_from) instead of taking a composed carry."""
+    from fast_sequential_scan_b200 import sequential_scan_cuda as native
     from fast_sequential_scan_b200.distributed import NativeOps
     dt = torch.bfloat16 if dtype == "bf16" else torch.float32
     tol = BF16_TOL if dtype == "bf16" else F32_TOL
@@ -531,7 +534,10 @@ def test_sequence_parallel_pieces_on_one_gpu(dtype, algo):
     for r in range(world):
         h, _, blocks = loc[r]
         carry = None
-        if r > 0:
+        if r > 0 and fused:
+            carry = native.seqpar_fixup_forward_from(a[:, rows[r]], b[:, rows[r]], h, pc, r, blocks[0], blocks[1], blocks[2])
+            assert torch.equal(carry.reshape(-1), ops[r].compose(pc, r, backward=False))
+        elif r > 0:
             carry = ops[r].compose(pc, r, backward=False).reshape(B, D)
             ops[r].fixup_forward(a[:, rows[r]], b[:, rows[r]], h, carry, blocks)
         hs.append(h); carries.append(carry)
@@ -546,7 +552,10 @@ def test_sequence_parallel_pieces_on_one_gpu(dtype, algo):
     das, dbs = [], []
     for r in range(world):
         da, db, _, blocks = bl[r]
-        if r < world - 1:
+        if r < world - 1 and fused:
+            native.seqpar_fixup_backward_from(a[:, rows[r]], hs[r], g[:, rows[r]], da, db, pcb, r, carries[r], blocks[0],
+                                              blocks[1], blocks[2], r > 0)
+        elif r < world - 1:
             u_in = ops[r].compose(pcb, r, backward=True).reshape(B, D)
             ops[r].fixup_backward(a[:, rows[r]], hs[r], g[:, rows[r]], da, db, u_in, carries[r], blocks, r > 0)
         das.append(da); dbs.append(db)
@@ -562,9 +571,10 @@ def _local_peers(world, n):
     """Tables and control words of `world` ranks, all in this GPU's memory (the ranks are played one
     after the other on one stream, so no kernel ever waits for a kernel that has not run)."""
     import ctypes
-    bufs = [torch.zeros(world * 2 * n + 64, dtype=torch.float32, device="cuda") for _ in range(world)]
+    cell_floats = world * 2 * n * 2                    # 8-byte cells {value, exchange number}
+    bufs = [torch.zeros(cell_floats + 64, dtype=torch.float32, device="cuda") for _ in range(world)]
     tables = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
-    words = (ctypes.c_void_p * world)(*[b.data_ptr() + world * 2 * n * 4 for b in bufs])
+    words = (ctypes.c_void_p * world)(*[b.data_ptr() + cell_floats * 4 for b in bufs])
     return bufs, tables, words
 
 
@@ -595,6 +605,29 @@ def test_carry_exchange_through_tables_played_on_one_gpu(backward):
     pkg.check_status()
 
 
+def test_forward_push_fused_with_the_product_fold():
+    """fss_seqpar_push_blocks: the product over the row blocks is folded inside the push kernel; what
+    the reader composes from it must equal the fold of (product of the blocks, state) in float64."""
+    pkg, native, _ = _mods()
+    world, B, nb, D = 2, 3, 37, 136
+    n = B * D
+    bufs, tables, words = _local_peers(world, n)
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    block_prod = torch.rand(B, nb, D, generator=gen, device="cuda") * 0.2 + 0.8
+    state = torch.randn(n, generator=gen, device="cuda")
+    prod_out = torch.empty(n, device="cuda")
+    native.seqpar_push_blocks(block_prod, state, prod_out, 0, tables, words, 1)
+    want_prod = block_prod.double().prod(dim=1).reshape(-1)
+    assert torch.allclose(prod_out.double(), want_prod, rtol=1e-5)
+    # rank 1 composes: carry = prod_0 * 0 + state_0 = state_0 (the product matters from rank 2 on)
+    got = native.seqpar_compose_peer(n, torch.device("cuda", 0), 1, False, tables, words, 1, short_waits=True)
+    assert torch.equal(got, state)
+    cells = bufs[1][:world * 2 * n * 2].view(world, 2, n, 2)         # rank 1's table: [rank][prod|state][n][value, epoch]
+    assert torch.allclose(cells[0, 0, :, 0].double(), want_prod, rtol=1e-5)
+    assert bool((cells[0, :, :, 1].view(torch.int32) == 1).all())
+    pkg.check_status()
+
+
 def test_carry_exchange_wait_gives_up_and_reports():
     """Failure detection without a fault: a rank waits for a pair that nobody pushes (a flag that
     nothing sets), with shortened waits; the kernel must end by itself, the status word must say so,
@@ -613,7 +646,8 @@ def test_carry_exchange_wait_gives_up_and_reports():
     torch.cuda.synchronize()
     with pytest.raises(RuntimeError, match="peer exchange timeout"):
         pkg.check_status()
-    assert float(bufs[1][0]) == 1.0                # rank 1's copy of rank 0's slot still holds exchange 1
+    assert float(bufs[1][0]) == 1.0                # rank 1's copy of rank 0's slot still holds exchange 1 ...
+    assert int(bufs[1][:2].view(torch.int32)[1]) == 1      # ... with its exchange number
     pkg.check_status()                             # the status word was cleared; nothing else pending
 
 

@@ -83,10 +83,11 @@ def load_workloads():
 
 
 def kernel_revision() -> str:
-    """Hash of the kernel sources; a profiler capture is only attributed to the sources it was taken from."""
+    """Hash of the sources the single-pass scan kernels are compiled from; a profiler capture is only
+    attributed to the sources it was taken from."""
     h = hashlib.sha256()
-    for f in sorted((ROOT / "fast_sequential_scan_b200" / "csrc").glob("*.cu*")):
-        h.update(f.read_bytes())
+    for name in ("fss_common.cuh", "fss_gates.cuh", "fss_lookback.cuh"):
+        h.update((ROOT / "fast_sequential_scan_b200" / "csrc" / name).read_bytes())
     return h.hexdigest()[:16]
 
 

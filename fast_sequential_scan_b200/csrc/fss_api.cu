@@ -88,6 +88,25 @@ static int need_workspace(const fss_scan_ctx *ctx, int64_t B, int64_t T, int64_t
     return FSS_OK;
 }
 
+// Launch with the programmatic-dependent-launch attribute: the kernel may be placed while its
+// predecessor on the stream drains; it must execute griddepcontrol.wait before it touches anything
+// the predecessor wrote (the kernels launched this way do so first thing).
+template <typename... Params, typename... Args>
+static cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+
 static int launch_check(const char *what) {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? FSS_OK : cuda_fail(e, what, FSS_E_LAUNCH);
@@ -380,8 +399,10 @@ FSS_API int fss_seqpar_push(const fss_scan_ctx *ctx, int backward, int world, in
     if (guard.error) return guard.error;
     int64_t blocks = ceil_div(2 * n, (int64_t)seqpar::kPushThreads);
     if (blocks > 148) blocks = 148;
-    seqpar::peer_push<<<(unsigned)blocks, seqpar::kPushThreads, 0, (cudaStream_t)ctx->stream>>>(
-        peers, backward, world, rank, n, prod, state, epoch, ctx->status, exchange_spins(ctx));
+    FSS_CUDA(launch_dependent(seqpar::peer_push, dim3((unsigned)blocks), dim3(seqpar::kPushThreads), 0,
+                              (cudaStream_t)ctx->stream, peers, backward, world, rank, n, prod, state, epoch, ctx->status,
+                              exchange_spins(ctx)),
+             "carry push launch");
     return launch_check("carry push launch");
 }
 
@@ -399,8 +420,10 @@ FSS_API int fss_seqpar_push_blocks(const fss_scan_ctx *ctx, int world, int rank,
     DeviceGuard guard(ctx->device);
     if (guard.error) return guard.error;
     const dim3 grid((unsigned)ceil_div(D, 4 * seqpar::kPushVecs), (unsigned)B);
-    seqpar::peer_push_blocks<<<grid, seqpar::kPushSlices * seqpar::kPushVecs, 0, (cudaStream_t)ctx->stream>>>(
-        peers, world, rank, nblocks, D, block_prod, state, prod_out, epoch, ctx->status, exchange_spins(ctx));
+    FSS_CUDA(launch_dependent(seqpar::peer_push_blocks, grid, dim3(seqpar::kPushSlices * seqpar::kPushVecs), 0,
+                              (cudaStream_t)ctx->stream, peers, world, rank, nblocks, D, block_prod, state, prod_out, epoch,
+                              ctx->status, exchange_spins(ctx)),
+             "carry push launch");
     return launch_check("carry push launch");
 }
 
@@ -451,8 +474,10 @@ static int fixup_forward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, 
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
     if (!fixup_grid_ok(g)) return FSS_E_SHAPE;
     const dim3 grid((unsigned)g.slots, (unsigned)g.vblocks, (unsigned)B);
-    seqpar::fixup_forward<T, V><<<grid, seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
-        g, make_view<const T>(alpha), make_view<const T>(beta), make_view<T>(h), carry_in, bp, bs, ctx->status);
+    FSS_CUDA(launch_dependent(seqpar::fixup_forward<T, V>, grid, dim3(seqpar::kFixThreads), 0, (cudaStream_t)ctx->stream, g,
+                              make_view<const T>(alpha), make_view<const T>(beta), make_view<T>(h), carry_in, bp, bs,
+                              ctx->status),
+             "seqpar forward fix-up launch");
     return launch_check("seqpar forward fix-up launch");
 }
 
@@ -464,9 +489,10 @@ static int fixup_backward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn,
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
     if (!fixup_grid_ok(g)) return FSS_E_SHAPE;
     const dim3 grid((unsigned)g.slots, (unsigned)g.vblocks, (unsigned)B);
-    seqpar::fixup_backward<T, V><<<grid, seqpar::kFixThreads, 0, (cudaStream_t)ctx->stream>>>(
-        g, make_view<const T>(alpha), make_view<const T>(h), make_view<const T>(grad), make_view<T>(da),
-        make_view<T>(db), u_in, h_prev, bp, bs, (ctx->flags & FSS_FLAG_CONTINUATION) != 0, ctx->status);
+    FSS_CUDA(launch_dependent(seqpar::fixup_backward<T, V>, grid, dim3(seqpar::kFixThreads), 0, (cudaStream_t)ctx->stream, g,
+                              make_view<const T>(alpha), make_view<const T>(h), make_view<const T>(grad), make_view<T>(da),
+                              make_view<T>(db), u_in, h_prev, bp, bs, (ctx->flags & FSS_FLAG_CONTINUATION) != 0, ctx->status),
+             "seqpar backward fix-up launch");
     return launch_check("seqpar backward fix-up launch");
 }
 

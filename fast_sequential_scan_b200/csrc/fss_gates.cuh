@@ -65,6 +65,14 @@ namespace gates {
 constexpr int kThreads = 256;
 constexpr int kRowsPerCta = 32;      // rows one CTA walks (bounds the partial sums it adds to dlambda)
 
+// scales[d] = -8 * softplus(lambda[d]) * log2(e): the per-channel factor of the exponent, computed once
+// per launch of the fused forward instead of once per tile
+template <typename T>
+__global__ void prescale(const float *__restrict__ lambda, float *__restrict__ scales, int64_t D) {
+    const int64_t d = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (d < D) scales[d] = Gate<T>::prescale(gate_scale(lambda[d]));
+}
+
 // alpha (and beta when asked) as the fused forward scan computes them, rounded to T.
 template <typename T, int V>
 __global__ void __launch_bounds__(kThreads)

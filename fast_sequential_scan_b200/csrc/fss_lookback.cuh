@@ -95,7 +95,7 @@ struct Params {
     float *block_prod;       // [B, S, D]: product of alpha over the rows of each row block
     float *block_state;      // [B, S, D]: state leaving each row block
     const float *h_prev;     // backward only
-    const float *lambda;     // gated forward only: [D]
+    const float *lambda;     // gated forward only: [D] exponent scales -8*softplus(lambda)*log2(e), made by gates::prescale
     int continuation;
     int32_t tile_rows;       // rows per tile: 64 * split
     uint32_t max_spins;      // iterations a wait may take before it gives up
@@ -733,6 +733,15 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
         const uint32_t lane_off = (uint32_t)(grp * kR) * kRowB + (uint32_t)cl * kLaneBytes;
         Cursor cursor(p, ctl, units, bar_info(0));
         cursor.init(u0, 0, 1);
+        // this lane's channel scales (a table made once per launch), always fetched one unit ahead so
+        // that the load's latency never sits between a landed tile and its gates
+        auto load_scales = [&](const Unit &un, float (&out)[V]) {
+            const int64_t dch = (int64_t)un.cg * Dc + cl * V;
+#pragma unroll
+            for (int v = 0; v < V; ++v) out[v] = dch + v < p.D ? __ldg(p.lambda + dch + v) : 0.0f;
+        };
+        float gsc_next[V];
+        load_scales(u0, gsc_next);
 #pragma unroll 1
         for (int i = 0;; ++i) {
             const int st = i % kStages;
@@ -742,12 +751,10 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
             const bool head = (row0 == 0) && (grp == 0) && !p.continuation;
             const int64_t left = p.T - row0 - (int64_t)grp * kR;
             const int nvalid = left >= kR ? kR : (left > 0 ? (int)left : 0);
-            float gsc[V];      // this lane's channel scales, fetched while the tile is still on its way
-            {
-                const int64_t dch = (int64_t)u.cg * Dc + cl * V;
+            float gsc[V];
 #pragma unroll
-                for (int v = 0; v < V; ++v) gsc[v] = dch + v < p.D ? Gate<T>::prescale(gate_scale(p.lambda[dch + v])) : 0.0f;
-            }
+            for (int v = 0; v < V; ++v) gsc[v] = gsc_next[v];
+            if (cursor.next_known()) load_scales(cursor.nxt, gsc_next);
             if (!ctl.wait(bar_full(st), (uint32_t)((i / kStages) & 1), FSS_STATUS_TMA_TIMEOUT)) break;
             Raw *a_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + lane_off);
             Raw *x_t = reinterpret_cast<Raw *>(smem_raw + st * SM::kStageBytes + kTileBytes + lane_off);
@@ -1516,7 +1523,15 @@ inline int forward_gated(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, i
         p.state_in = cont ? st->h_in : nullptr;
         p.state_out = st->h_last;
     }
-    p.lambda = lambda;
+    // the per-channel exponent scales, once per launch, into the float scratch of the workspace
+    if ((size_t)D * sizeof(float) > ws.float_bytes) return FSS_E_WORKSPACE;
+    float *scales = reinterpret_cast<float *>(ws.floats);
+    gates::prescale<T><<<(unsigned)ceil_div(D, 256), 256, 0, (cudaStream_t)ctx->stream>>>(lambda, scales, D);
+    {
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { *err_text = std::string("gate scale launch: ") + cudaGetErrorString(e); return FSS_E_LAUNCH; }
+    }
+    p.lambda = scales;
     const int dtype = sizeof(T) == 2 ? FSS_DTYPE_BF16 : FSS_DTYPE_F32;
     switch (choose_split(dtype, B, Tn, D)) {
     case 4: return launch_split<T, false, 4, false, true>(ctx, ws, B, Tn, D, r, x, i, h, nullptr, p, 0, err_text);

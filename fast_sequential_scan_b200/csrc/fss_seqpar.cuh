@@ -98,6 +98,10 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t *p, uint32_t want, uin
 __global__ void __launch_bounds__(kPushThreads)
 peer_push(PeerTables peers, int backward, int world, int rank, int64_t n, const float *__restrict__ prod,
           const float *__restrict__ state, uint32_t epoch, int32_t *status, uint32_t max_spins) {
+    // placed early (programmatic dependent launch): let the successor do the same, then wait for
+    // everything before this kernel on the stream
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ int ok;
     if (threadIdx.x == 0) ok = 1;
     __syncthreads();
@@ -128,6 +132,10 @@ __global__ void __launch_bounds__(kPushSlices * kPushVecs)
 peer_push_blocks(PeerTables peers, int world, int rank, int64_t S, int64_t D, const float *__restrict__ block_prod,
                  const float *__restrict__ state, float *__restrict__ prod_out, uint32_t epoch, int32_t *status,
                  uint32_t max_spins) {
+    // placed early (programmatic dependent launch): let the successor do the same, then wait for
+    // everything before this kernel on the stream
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float4 part[kPushSlices][kPushVecs];
     __shared__ int ok;
     if (threadIdx.x == 0) ok = 1;
@@ -374,6 +382,10 @@ template <typename T, int V>
 __global__ void __launch_bounds__(kFixThreads)
 fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, const CarrySource src,
               const float *__restrict__ block_prod, const float *__restrict__ block_state, int32_t *status) {
+    // placed early (programmatic dependent launch): let the successor do the same, then wait for
+    // everything before this kernel on the stream
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float sP[kFixWarps * 32 * V], sC[kFixWarps * 32 * V];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t b = blockIdx.z;
@@ -479,6 +491,10 @@ fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> g
                View<T> dbeta, const CarrySource src, const float *__restrict__ h_prev,
                const float *__restrict__ block_prod, const float *__restrict__ block_state, bool continuation,
                int32_t *status) {
+    // placed early (programmatic dependent launch): let the successor do the same, then wait for
+    // everything before this kernel on the stream
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float sP[kFixWarps * 32 * V], sC[kFixWarps * 32 * V];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t b = blockIdx.z;

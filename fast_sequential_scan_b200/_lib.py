@@ -17,6 +17,7 @@ DTYPE_BF16, DTYPE_F32 = 0, 1
 ALGO_AUTO, ALGO_CHUNKED, ALGO_LOOKBACK = 0, 1, 2
 FLAG_CONTINUATION = 1
 FLAG_DETERMINISTIC = 2
+FLAG_HOLD_DEPENDENTS = 4
 E_LAYOUT = -5      # FSS_E_LAYOUT
 FLAG_TEST_SHORT_WAITS, FLAG_TEST_MUTE_FIRST_BLOCK = 0x100, 0x200
 
@@ -51,7 +52,8 @@ class BackwardState(Structure):
 
 class CarrySource(Structure):
     _fields_ = [("world", c_int32), ("rank", c_int32), ("table", c_void_p), ("peer_tables", POINTER(c_void_p)),
-                ("peer_words", POINTER(c_void_p)), ("epoch", c_uint32), ("carry_out", c_void_p)]
+                ("peer_words", POINTER(c_void_p)), ("epoch", c_uint32), ("carry_out", c_void_p),
+                ("push_state", c_void_p), ("push_prod", c_void_p), ("push_prod_out", c_void_p)]
 
 
 _P = POINTER

@@ -467,32 +467,109 @@ static seqpar::Geometry fixup_geometry(int64_t B, int64_t T, int64_t D, int64_t 
 }
 static bool fixup_grid_ok(const seqpar::Geometry &g) { return g.vblocks <= 65535 && g.B <= 65535; }
 
+// A fix-up kernel publishes this rank's own pair itself only when all its CTAs are on the GPU at
+// the same time: they wait for pairs that the same kernel publishes on the other ranks, so a grid
+// that runs in waves could wait for a CTA that has not started.  For such a grid the pair is sent
+// by a push launch placed before the fix-up, as a caller without `push_state` would do.
+static int publish_before(const fss_scan_ctx *ctx, const seqpar::Geometry &g, int backward, seqpar::CarrySource *src,
+                          const float *bp) {
+    if (!src->push_state) return FSS_OK;
+    if ((int64_t)g.slots * g.vblocks * g.B <= sm_count()) return FSS_OK;
+    const int64_t n = g.B * g.D;
+    if (src->push_prod) {
+        int64_t blocks = ceil_div(2 * n, (int64_t)seqpar::kPushThreads);
+        if (blocks > 148) blocks = 148;
+        FSS_CUDA(launch_dependent(seqpar::peer_push, dim3((unsigned)blocks), dim3(seqpar::kPushThreads), 0,
+                                  (cudaStream_t)ctx->stream, src->peers, backward, (int)src->world, (int)src->rank, n,
+                                  src->push_prod, src->push_state, src->epoch, ctx->status, src->max_spins),
+                 "carry push launch");
+    } else {
+        if (g.D % 4 || !src->push_prod_out || !aligned16(bp) || !aligned16(src->push_state) || !aligned16(src->push_prod_out))
+            return FSS_E_LAYOUT;
+        const dim3 grid((unsigned)ceil_div(g.D, 4 * seqpar::kPushVecs), (unsigned)g.B);
+        FSS_CUDA(launch_dependent(seqpar::peer_push_blocks, grid, dim3(seqpar::kPushSlices * seqpar::kPushVecs), 0,
+                                  (cudaStream_t)ctx->stream, src->peers, (int)src->world, (int)src->rank, g.NB, g.D, bp,
+                                  src->push_state, src->push_prod_out, src->epoch, ctx->status, src->max_spins),
+                 "carry push launch");
+    }
+    if (int rc = launch_check("carry push launch")) return rc;
+    src->push_state = nullptr;
+    src->push_prod = nullptr;
+    src->push_prod_out = nullptr;
+    return FSS_OK;
+}
+
+// Room for the alpha rows of one block in shared memory (see the fix-up kernels): 16 warps x `per`
+// rows x 32 lanes of the packed fragment; 0 = the block is too tall, the kernels then read alpha twice.
+template <typename T, int V, typename Kernel>
+static size_t fixup_stage_bytes(const seqpar::Geometry &g, Kernel kernel) {
+    const int64_t per = (g.R + seqpar::kFixWarps - 1) / seqpar::kFixWarps;
+    const size_t bytes = (size_t)seqpar::kFixWarps * per * 32 * sizeof(typename Frag<T, V>::Raw);
+    constexpr size_t kMost = 160 * 1024;
+    if (bytes == 0 || bytes > kMost) return 0;
+    // the limit is raised once per device and kernel instantiation (the template parameters make this function unique)
+    static bool raised[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (!raised[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMost) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+        raised[dev] = true;
+    }
+    return bytes;
+}
+
 template <typename T, int V>
 static int fixup_forward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *alpha,
-                                const fss_view *beta, const fss_view *h, const seqpar::CarrySource &carry_in, const float *bp,
+                                const fss_view *beta, const fss_view *h, const seqpar::CarrySource &carry_from, const float *bp,
                                 const float *bs, int64_t R) {
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
     if (!fixup_grid_ok(g)) return FSS_E_SHAPE;
+    seqpar::CarrySource carry_in = carry_from;
+    if (int rc = publish_before(ctx, g, 0, &carry_in, bp)) return rc;
     const dim3 grid((unsigned)g.slots, (unsigned)g.vblocks, (unsigned)B);
-    FSS_CUDA(launch_dependent(seqpar::fixup_forward<T, V>, grid, dim3(seqpar::kFixThreads), 0, (cudaStream_t)ctx->stream, g,
-                              make_view<const T>(alpha), make_view<const T>(beta), make_view<T>(h), carry_in, bp, bs,
-                              ctx->status),
-             "seqpar forward fix-up launch");
+    const size_t stage = fixup_stage_bytes<T, V>(g, seqpar::fixup_forward<T, V, true>);
+    if (stage) {
+        FSS_CUDA(launch_dependent(seqpar::fixup_forward<T, V, true>, grid, dim3(seqpar::kFixThreads), stage,
+                                  (cudaStream_t)ctx->stream, g, make_view<const T>(alpha), make_view<const T>(beta),
+                                  make_view<T>(h), carry_in, bp, bs, ctx->status),
+                 "seqpar forward fix-up launch");
+    } else {
+        FSS_CUDA(launch_dependent(seqpar::fixup_forward<T, V, false>, grid, dim3(seqpar::kFixThreads), 0,
+                                  (cudaStream_t)ctx->stream, g, make_view<const T>(alpha), make_view<const T>(beta),
+                                  make_view<T>(h), carry_in, bp, bs, ctx->status),
+                 "seqpar forward fix-up launch");
+    }
     return launch_check("seqpar forward fix-up launch");
 }
 
 template <typename T, int V>
 static int fixup_backward_launch(const fss_scan_ctx *ctx, int64_t B, int64_t Tn, int64_t D, const fss_view *alpha,
                                  const fss_view *h, const fss_view *grad, const fss_view *da, const fss_view *db,
-                                 const seqpar::CarrySource &u_in, const float *h_prev, const float *bp, const float *bs,
+                                 const seqpar::CarrySource &u_from, const float *h_prev, const float *bp, const float *bs,
                                  int64_t R) {
     const seqpar::Geometry g = fixup_geometry(B, Tn, D, R, V);
     if (!fixup_grid_ok(g)) return FSS_E_SHAPE;
+    seqpar::CarrySource u_in = u_from;
+    if (int rc = publish_before(ctx, g, 1, &u_in, bp)) return rc;
     const dim3 grid((unsigned)g.slots, (unsigned)g.vblocks, (unsigned)B);
-    FSS_CUDA(launch_dependent(seqpar::fixup_backward<T, V>, grid, dim3(seqpar::kFixThreads), 0, (cudaStream_t)ctx->stream, g,
-                              make_view<const T>(alpha), make_view<const T>(h), make_view<const T>(grad), make_view<T>(da),
-                              make_view<T>(db), u_in, h_prev, bp, bs, (ctx->flags & FSS_FLAG_CONTINUATION) != 0, ctx->status),
-             "seqpar backward fix-up launch");
+    const size_t stage = fixup_stage_bytes<T, V>(g, seqpar::fixup_backward<T, V, true>);
+    const bool cont = (ctx->flags & FSS_FLAG_CONTINUATION) != 0;
+    if (stage) {
+        FSS_CUDA(launch_dependent(seqpar::fixup_backward<T, V, true>, grid, dim3(seqpar::kFixThreads), stage,
+                                  (cudaStream_t)ctx->stream, g, make_view<const T>(alpha), make_view<const T>(h),
+                                  make_view<const T>(grad), make_view<T>(da), make_view<T>(db), u_in, h_prev, bp, bs, cont,
+                                  ctx->status),
+                 "seqpar backward fix-up launch");
+    } else {
+        FSS_CUDA(launch_dependent(seqpar::fixup_backward<T, V, false>, grid, dim3(seqpar::kFixThreads), 0,
+                                  (cudaStream_t)ctx->stream, g, make_view<const T>(alpha), make_view<const T>(h),
+                                  make_view<const T>(grad), make_view<T>(da), make_view<T>(db), u_in, h_prev, bp, bs, cont,
+                                  ctx->status),
+                 "seqpar backward fix-up launch");
+    }
     return launch_check("seqpar backward fix-up launch");
 }
 
@@ -537,6 +614,12 @@ static int table_carry(const fss_scan_ctx *ctx, const fss_carry_source *src, int
     s.max_spins = exchange_spins(ctx);
     if (src->epoch) {
         if (int rc = fill_peers(&s.peers, src->world, src->peer_tables, src->peer_words)) return rc;
+    }
+    if (src->push_state) {
+        if (!src->epoch) return FSS_E_NULL;      // only a peer exchange can be published from inside the kernel
+        s.push_state = src->push_state;
+        s.push_prod = src->push_prod;
+        s.push_prod_out = src->push_prod_out;
     }
     *out = s;
     return FSS_OK;
@@ -613,6 +696,7 @@ FSS_API int fss_seqpar_fixup_backward_from(const fss_scan_ctx *ctx, int dtype, i
     if (block_rows < 1) return FSS_E_SHAPE;
     seqpar::CarrySource src;
     if ((rc = table_carry(ctx, source, B * D, &src))) return rc;
+    if (src.push_state && !src.push_prod) return FSS_E_NULL;      // the backward has no block products of alpha to fold
     DeviceGuard guard(ctx->device);
     if (guard.error) return guard.error;
     return fixup_backward_dispatch(ctx, dtype, B, T, D, alpha, h, grad_out, grad_alpha, grad_beta, src, h_prev, block_prod,

@@ -101,6 +101,7 @@ struct Params {
     uint32_t max_spins;      // iterations a wait may take before it gives up
     int mute_first_block;    // test hook: row block 0 publishes no descriptors (its successors' waits run out)
     int deterministic;       // a tile only ever starts from its predecessor's inclusive state
+    int hold_dependents;     // no early release of the next launch on the stream
     int64_t grid;            // CTAs of the launch
     // fixed tile order (CTA x takes tiles x, x+G, ...): ntiles = units_q * grid + units_r, so CTA x
     // owns units_q + (x < units_r) tiles; one grid stride = grid_q row blocks + grid_b batch rows +
@@ -499,8 +500,10 @@ scan_kernel(const __grid_constant__ CUtensorMap map_alpha, const __grid_constant
     const Unit u0 = unit_of_tile(p, first);
     // Programmatic dependent launch: let the next launch on the stream start its own set-up as SMs
     // become free, and do everything that touches no global memory before waiting for the previous
-    // launch to finish (both instructions do nothing for an ordinary launch).
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // launch to finish (both instructions do nothing for an ordinary launch).  With hold_dependents
+    // the next launch is not released early and starts when this one has finished
+    // (FSS_FLAG_HOLD_DEPENDENTS).
+    if (!p.hold_dependents) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == kProducerWarp * 32) {
         // the descriptors are kernel parameters, not data of the previous launch: fetch them now
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_alpha) : "memory");
@@ -1369,6 +1372,7 @@ inline int launch_split(const fss_scan_ctx *ctx, const WsPlan &ws, int64_t B, in
     p.max_spins = (ctx->flags & FSS_FLAG_TEST_SHORT_WAITS) ? 4096u : kMaxSpins;
     p.mute_first_block = (ctx->flags & FSS_FLAG_TEST_MUTE_FIRST_BLOCK) ? 1 : 0;
     p.deterministic = (ctx->flags & FSS_FLAG_DETERMINISTIC) ? 1 : 0;
+    p.hold_dependents = (ctx->flags & FSS_FLAG_HOLD_DEPENDENTS) ? 1 : 0;
 
     const unsigned grid = (unsigned)(p.ntiles < resident ? p.ntiles : resident);
     p.grid = grid;

@@ -134,7 +134,8 @@ class NativeOps:
         # with the peer exchange the product over the rows is folded by the push kernel (one launch less)
         self._prod_pending = self.exchange == "peer" and D % 4 == 0
         native.forward_into(alpha, beta, h, algo=algo, continuation=continuation, h_last=send[1].view(B, D),
-                            prod=None if self._prod_pending else send[0].view(B, D), block_prod=bp, block_state=bs)
+                            prod=None if self._prod_pending else send[0].view(B, D), block_prod=bp, block_state=bs,
+                            hold_dependents=self.exchange == "peer" and continuation)      # a fix-up follows directly
         return h, send, (bp, bs, R)
 
     def local_backward(self, alpha, h, grad, continuation: bool, h_prev, prod):
@@ -148,7 +149,8 @@ class NativeOps:
         if self.exchange == "collective":          # the all-gather sends one contiguous [2, n] pair
             send[0].copy_(prod.reshape(-1))
         native.backward_into(alpha, h, grad, da, db, algo=algo, continuation=continuation, h_prev=h_prev,
-                             u_out=send[1].view(B, D), block_prod=bp, block_state=bs)
+                             u_out=send[1].view(B, D), block_prod=bp, block_state=bs,
+                             hold_dependents=self.exchange == "peer")
         return da, db, send, (bp, bs, R)
 
     def gather_buffer(self, which: str, send, world: int):
@@ -169,38 +171,50 @@ class NativeOps:
     # The fix-up kernels can fold the exchanged table themselves (one launch less per direction): these two
     # are what seqpar_forward / seqpar_backward use when the ops object has them.
     def exchange_and_fixup_forward(self, alpha, beta, h, send, prod, blocks, rank: int, world: int, group, mark):
+        """Returns ``(carry_in or None, prod)``: the state entering this rank's rows and the product of alpha
+        over them, in a tensor of its own (the backward needs it after ``send`` has been reused)."""
         from . import sequential_scan_cuda as native
         if self.exchange == "peer":
             peer = self.peer("fwd", send, group)
-            if getattr(self, "_prod_pending", False):
-                peer.epoch += 1
-                epoch = peer.epoch
-                native.seqpar_push_blocks(blocks[0], send[1], send[0], rank, peer.tables, peer.words, epoch)
-            else:
-                epoch = peer.push(prod.reshape(-1), send[1])
+            pending = getattr(self, "_prod_pending", False)      # the product is still to be folded from the blocks
+            kept = torch.empty_like(send[0]) if pending else None
+            peer.epoch += 1
+            if rank == 0:                                        # no fix-up here: a push launch of its own
+                if pending:
+                    native.seqpar_push_blocks(blocks[0], send[1], kept, rank, peer.tables, peer.words, peer.epoch)
+                else:
+                    native.seqpar_push(send[0], send[1], rank, False, peer.tables, peer.words, peer.epoch)
+                mark("fwd_gather")
+                return None, kept if pending else send[0].clone()
+            # the fix-up kernel publishes this rank's pair itself, right after the local scan
             mark("fwd_gather")
-            if rank == 0:
-                return None
-            return native.seqpar_fixup_forward_from(alpha, beta, h, None, rank, blocks[0], blocks[1], blocks[2],
-                                                    peer_tables=peer.tables, peer_words=peer.words, epoch=epoch)
+            push = (send[1], None, kept) if pending else (send[1], send[0], None)
+            carry = native.seqpar_fixup_forward_from(alpha, beta, h, None, rank, blocks[0], blocks[1], blocks[2],
+                                                     peer_tables=peer.tables, peer_words=peer.words, epoch=peer.epoch,
+                                                     push=push)
+            return carry, kept if pending else send[0].clone()
         pc = _gather(send, group, self, "fwd")
         mark("fwd_gather")
+        kept = send[0].clone()
         if rank == 0:
-            return None
-        return native.seqpar_fixup_forward_from(alpha, beta, h, pc, rank, blocks[0], blocks[1], blocks[2])
+            return None, kept
+        return native.seqpar_fixup_forward_from(alpha, beta, h, pc, rank, blocks[0], blocks[1], blocks[2]), kept
 
     def exchange_and_fixup_backward(self, alpha, h, grad, da, db, send, prod, h_prev, blocks, rank: int, world: int,
                                     continuation: bool, group, mark):
         from . import sequential_scan_cuda as native
         if self.exchange == "peer":
             peer = self.peer("bwd", send, group)
-            epoch = peer.push(prod.reshape(-1), send[1])
-            mark("bwd_gather")
             if rank == world - 1:
+                peer.push(prod.reshape(-1), send[1])
+                mark("bwd_gather")
                 return None
+            peer.epoch += 1
+            mark("bwd_gather")
             return native.seqpar_fixup_backward_from(alpha, h, grad, da, db, None, rank, h_prev, blocks[0], blocks[1],
                                                      blocks[2], continuation, peer_tables=peer.tables,
-                                                     peer_words=peer.words, epoch=epoch)
+                                                     peer_words=peer.words, epoch=peer.epoch,
+                                                     push=(send[1], prod.reshape(-1), None))
         pc = _gather(send, group, self, "bwd")
         mark("bwd_gather")
         if rank == world - 1:
@@ -258,17 +272,19 @@ def seqpar_forward(alpha, beta, group=None, ops=None, mark=_no_mark):
     ops = ops or NativeOps()
     rank, world = _rank(group), _world(group)
     B, T, D = alpha.shape
+    fused = world > 1 and hasattr(ops, "exchange_and_fixup_forward")
     h, send, blocks = ops.local_forward(alpha, beta, continuation=rank > 0)
     mark("fwd_local")
-    if world > 1 and hasattr(ops, "exchange_and_fixup_forward"):
-        carry_in = ops.exchange_and_fixup_forward(alpha, beta, h, send, send[0], blocks, rank, world, group, mark)
+    if fused:
+        carry_in, prod = ops.exchange_and_fixup_forward(alpha, beta, h, send, send[0], blocks, rank, world, group, mark)
     else:
         carry_in = _exchange_and_compose(ops, "fwd", send, send[0], rank, world, False, rank > 0, group, mark)
         if carry_in is not None:
             carry_in = carry_in.reshape(B, D)
             ops.fixup_forward(alpha, beta, h, carry_in, blocks)
+        prod = send[0].clone()
     mark("fwd_fixup")
-    return h, dict(carry_in=carry_in, prod=send[0].clone())
+    return h, dict(carry_in=carry_in, prod=prod)
 
 
 def seqpar_backward(alpha, h, grad, saved, group=None, ops=None, mark=_no_mark):
@@ -277,9 +293,10 @@ def seqpar_backward(alpha, h, grad, saved, group=None, ops=None, mark=_no_mark):
     rank, world = _rank(group), _world(group)
     B, T, D = alpha.shape
     h_prev = saved["carry_in"]
+    fused = world > 1 and hasattr(ops, "exchange_and_fixup_backward")
     da, db, send, blocks = ops.local_backward(alpha, h, grad, continuation=rank > 0, h_prev=h_prev, prod=saved["prod"])
     mark("bwd_local")
-    if world > 1 and hasattr(ops, "exchange_and_fixup_backward"):
+    if fused:
         ops.exchange_and_fixup_backward(alpha, h, grad, da, db, send, saved["prod"], h_prev, blocks, rank, world,
                                         rank > 0, group, mark)
     else:

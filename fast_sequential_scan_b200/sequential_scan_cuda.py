@@ -152,8 +152,11 @@ def _launch_backward(a, hh, g, grad_alpha, grad_beta, dtype_id: int, algo, flags
 
 
 def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_last=None,
-                 prod=None, block_prod=None, block_state=None, _extra_flags: int = 0) -> None:
-    """h <- scan(alpha, beta) into a caller-owned tensor, with the optional boundary state."""
+                 prod=None, block_prod=None, block_state=None, hold_dependents: bool = False,
+                 _extra_flags: int = 0) -> None:
+    """h <- scan(alpha, beta) into a caller-owned tensor, with the optional boundary state.
+    ``hold_dependents`` = ``FSS_FLAG_HOLD_DEPENDENTS``: the next launch on the stream is placed only when this
+    scan has finished."""
     dtype = alpha.dtype
     if dtype not in _DTYPES:
         raise RuntimeError(f"alpha: unsupported dtype {dtype} (bf16 or fp32)")
@@ -171,7 +174,8 @@ def forward_into(alpha, beta, h, *, algo=None, continuation=False, h_in=None, h_
         state = _lib.ForwardState(_vec(h_in, B, D, "h_in"), _vec(h_last, B, D, "h_last"),
                                   _vec(prod, B, D, "prod"), _blocks(block_prod, "block_prod"),
                                   _blocks(block_state, "block_state"))
-    _launch_forward(a, b, h, _DTYPES[dtype], algo, (_lib.FLAG_CONTINUATION if continuation else 0) | _extra_flags, state)
+    flags = (_lib.FLAG_CONTINUATION if continuation else 0) | (_lib.FLAG_HOLD_DEPENDENTS if hold_dependents else 0)
+    _launch_forward(a, b, h, _DTYPES[dtype], algo, flags | _extra_flags, state)
 
 
 def gates_reference(r, i, x, lam):
@@ -290,7 +294,10 @@ def scan_forward_gated(r, i, x, lam) -> torch.Tensor:
 
 
 def backward_into(alpha, h, grad_out, grad_alpha, grad_beta, *, algo=None, continuation=False,
-                  u_in=None, h_prev=None, u_out=None, block_prod=None, block_state=None) -> None:
+                  u_in=None, h_prev=None, u_out=None, block_prod=None, block_state=None,
+                  hold_dependents: bool = False) -> None:
+    """Reverse scan into caller-owned gradient tensors, with the optional boundary state (``hold_dependents``:
+    see :func:`forward_into`)."""
     dtype = alpha.dtype
     if dtype not in _DTYPES:
         raise RuntimeError(f"alpha_saved: unsupported dtype {dtype} (bf16 or fp32)")
@@ -312,7 +319,8 @@ def backward_into(alpha, h, grad_out, grad_alpha, grad_beta, *, algo=None, conti
                                    _vec(u_out, B, D, "u_out"), _blocks(block_prod, "block_prod"),
                                    _blocks(block_state, "block_state"))
     _launch_backward(a, hh, g, grad_alpha, grad_beta, _DTYPES[dtype], algo,
-                     _lib.FLAG_CONTINUATION if continuation else 0, state)
+                     (_lib.FLAG_CONTINUATION if continuation else 0)
+                     | (_lib.FLAG_HOLD_DEPENDENTS if hold_dependents else 0), state)
 
 
 def _forward(alpha: torch.Tensor, beta: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
@@ -487,18 +495,32 @@ def seqpar_fixup_backward(alpha, h, grad_out, grad_alpha, grad_beta, u_in, h_pre
     _lib.check(rc, "fss_seqpar_fixup_backward")
 
 
-def _carry_source(table: Optional[torch.Tensor], rank: int, peer_tables, peer_words, epoch: int, carry_out: torch.Tensor):
+def _carry_source(table: Optional[torch.Tensor], rank: int, peer_tables, peer_words, epoch: int, carry_out: torch.Tensor,
+                  push=None):
+    """``push``: ``(state, prod or None, prod_out or None)`` -- this rank's own pair, published by the fix-up kernel."""
     if epoch:                      # cells of a peer exchange: the table lives behind peer_tables[rank]
-        return _lib.CarrySource(len(peer_tables), rank, None, peer_tables, peer_words, epoch, carry_out.data_ptr())
+        src = _lib.CarrySource(len(peer_tables), rank, None, peer_tables, peer_words, epoch, carry_out.data_ptr())
+        if push is not None:
+            n = carry_out.numel()
+            for name, t in zip(("push state", "push prod", "push prod_out"), push):
+                if t is not None and (t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous() or t.numel() != n):
+                    raise RuntimeError(f"{name}: expected a contiguous fp32 CUDA vector of {n} values")
+            src.push_state, src.push_prod, src.push_prod_out = (t.data_ptr() if t is not None else None for t in push)
+        return src
+    if push is not None:
+        raise RuntimeError("a fix-up can publish this rank's pair only with a peer exchange (epoch != 0)")
     if table.dtype != torch.float32 or not table.is_cuda or not table.is_contiguous() or table.dim() != 3 or table.shape[1] != 2:
         raise RuntimeError("table: expected a contiguous fp32 CUDA tensor [world, 2, n]")
     return _lib.CarrySource(table.shape[0], rank, table.data_ptr(), None, None, 0, carry_out.data_ptr())
 
 
 def seqpar_fixup_forward_from(alpha, beta, h, table, rank: int, block_prod, block_state, rows_per_block: int, *,
-                              peer_tables=None, peer_words=None, epoch: int = 0) -> torch.Tensor:
+                              peer_tables=None, peer_words=None, epoch: int = 0, push=None) -> torch.Tensor:
     """Forward fix-up that folds the gathered ``[world, 2, B*D]`` table itself (``fss_seqpar_fixup_forward_from``);
-    with ``epoch`` it first waits for that peer exchange and acknowledges it.  Returns the folded carry ``[B, D]``."""
+    with ``epoch`` it first waits for that peer exchange and acknowledges it.  Returns the folded carry ``[B, D]``.
+
+    ``push = (state, prod or None, prod_out or None)`` (peer exchange only): the kernel also publishes this rank's own
+    pair for exchange ``epoch`` -- no ``seqpar_push`` for it then; without ``prod`` it folds ``block_prod``."""
     dtype = alpha.dtype
     _check_tensor("alpha", alpha, None, dtype)
     _check_tensor("beta", beta, alpha, dtype)
@@ -506,7 +528,7 @@ def seqpar_fixup_forward_from(alpha, beta, h, table, rank: int, block_prod, bloc
     B, T, D = alpha.shape
     a, b = _rowwise(alpha), _rowwise(beta)
     carry = torch.empty(B, D, dtype=torch.float32, device=alpha.device)
-    src = _carry_source(table, rank, peer_tables, peer_words, epoch, carry)
+    src = _carry_source(table, rank, peer_tables, peer_words, epoch, carry, push)
     va, vb, vh = _view(a), _view(b), _view(h)
     ws = workspace.get(alpha.device, 1 << 16)
     ctx = _ctx(alpha.device, ws, None, _lib.FLAG_CONTINUATION)
@@ -519,14 +541,15 @@ def seqpar_fixup_forward_from(alpha, beta, h, table, rank: int, block_prod, bloc
 
 def seqpar_fixup_backward_from(alpha, h, grad_out, grad_alpha, grad_beta, table, rank: int, h_prev, block_prod, block_state,
                                rows_per_block: int, continuation: bool, *, peer_tables=None, peer_words=None,
-                               epoch: int = 0) -> torch.Tensor:
-    """Backward counterpart of :func:`seqpar_fixup_forward_from`; returns the folded ``u`` ``[B, D]``."""
+                               epoch: int = 0, push=None) -> torch.Tensor:
+    """Backward counterpart of :func:`seqpar_fixup_forward_from` (``push`` needs the product); returns the folded
+    ``u`` ``[B, D]``."""
     dtype = alpha.dtype
     B, T, D = alpha.shape
     a, hh, g = _rowwise(alpha), _rowwise(h), _rowwise(grad_out)
     views = [_view(t) for t in (a, hh, g, grad_alpha, grad_beta)]
     u_in = torch.empty(B, D, dtype=torch.float32, device=alpha.device)
-    src = _carry_source(table, rank, peer_tables, peer_words, epoch, u_in)
+    src = _carry_source(table, rank, peer_tables, peer_words, epoch, u_in, push)
     ws = workspace.get(alpha.device, 1 << 16)
     ctx = _ctx(alpha.device, ws, None, _lib.FLAG_CONTINUATION if continuation else 0)
     rc = _lib.lib().fss_seqpar_fixup_backward_from(ctypes.byref(ctx), _DTYPES[dtype], B, T, D,

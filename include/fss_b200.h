@@ -99,6 +99,14 @@ typedef struct fss_scan_ctx {
  * The chunked kernels are always deterministic.  The reference's kernels are, too: one thread walks
  * a channel group from the first row to the last (csrc/include/sequential_scan_kernel_bf16.cuh:121-151). */
 #define FSS_FLAG_DETERMINISTIC 2
+/* For the scans.  The single-pass kernels normally release the launch that follows them on the
+ * stream at once, so that it can be placed and set itself up while they drain (programmatic
+ * dependent launch; the follower still waits for their completion before it touches memory).  With
+ * this flag the follower is placed only when the scan has finished.  Measured on B200: the
+ * sequence-parallel fix-up kernels, which occupy whole multiprocessors and start with a burst of
+ * loads, run 5-9 microseconds faster when they are placed on an empty GPU than when their CTAs were
+ * parked one by one behind the scan's last tiles; the local scans of a sequence-parallel step set it. */
+#define FSS_FLAG_HOLD_DEPENDENTS 4
 /* Test hooks for the bounded waits of the single-pass kernels (no effect on results otherwise):
  * SHORT_WAITS lets every wait give up after a few thousand polls instead of ~a second;
  * MUTE_FIRST_BLOCK makes the tiles of the first row block publish no descriptors, so that the
@@ -304,7 +312,18 @@ int fss_scan_forward_noalloc(int dtype, int device, void *stream, int64_t B, int
  *               and then acknowledged; peer_tables / peer_words are the arrays given to
  *               fss_seqpar_push, `table` is ignored;
  *   carry_out   optional [B*D]: receives the folded carry (the state entering row 0 / the u arriving
- *               after the last row), which the caller needs again (h_prev of the backward). */
+ *               after the last row), which the caller needs again (h_prev of the backward);
+ *   push_state  optional, peer exchange only (epoch != 0): [B*D], the state THIS rank hands on in the
+ *               same exchange.  The fix-up kernel then also does the work of fss_seqpar_push /
+ *               fss_seqpar_push_blocks for this rank -- it waits (bounded) until the readers have
+ *               acknowledged exchange epoch - 1 and writes the pair into their tables as soon as the
+ *               launch before it has finished -- so the caller issues no push for this rank and
+ *               exchange.  (A problem whose fix-up grid does not fit on the GPU at once gets the push
+ *               as a launch of its own from inside this call; with push_prod NULL that needs D % 4 == 0
+ *               and push_prod_out, else FSS_E_LAYOUT.)  With it:
+ *   push_prod   [B*D], the product of alpha over this rank's rows; NULL (forward only) = fold
+ *               block_prod over the row blocks;
+ *   push_prod_out  optional [B*D]: receives that product. */
 typedef struct fss_carry_source {
     int32_t world, rank;
     const float *table;
@@ -312,6 +331,9 @@ typedef struct fss_carry_source {
     void *const *peer_words;
     uint32_t epoch;
     float *carry_out;
+    const float *push_state;
+    const float *push_prod;
+    float *push_prod_out;
 } fss_carry_source;
 int fss_seqpar_fixup_forward_from(const fss_scan_ctx *ctx, int dtype, int64_t B, int64_t T, int64_t D,
                                   const fss_view *alpha, const fss_view *beta, const fss_view *h,

@@ -578,6 +578,67 @@ def _local_peers(world, n):
     return bufs, tables, words
 
 
+@pytest.mark.parametrize("dtype,D", [("bf16", 256), ("f32", 256), ("bf16", 100)])
+def test_fixups_that_publish_their_own_pair_played_on_one_gpu(dtype, D):
+    """The peer-exchange step in which every rank's fix-up kernel publishes that rank's own pair
+    (fss_carry_source.push_state) -- only the rank without a fix-up uses a push launch.  Four ranks
+    played in dependency order on one GPU, two steps in a row (the second one waits for the
+    acknowledgements of the first), forward and backward against the CPU checker's undivided scan.
+    Forward fix-ups fold the product from the block table and must hand back the scan's own product."""
+    pkg, native, _ = _mods()
+    from fast_sequential_scan_b200.distributed import NativeOps
+    dt = torch.bfloat16 if dtype == "bf16" else torch.float32
+    tol = BF16_TOL if dtype == "bf16" else F32_TOL
+    world, B, Tl = 4, 2, 1500
+    n = B * D
+    gen = torch.Generator(device="cuda").manual_seed(41)
+    shape = (B, world * Tl, D)
+    lo, span = (0.9, 0.0999) if dtype == "bf16" else (0.5, 0.49)
+    ops = [NativeOps() for _ in range(world)]
+    rows = [slice(r * Tl, (r + 1) * Tl) for r in range(world)]
+    fwd_peers, bwd_peers = _local_peers(world, n), _local_peers(world, n)
+    for epoch in (1, 2):
+        a = (lo + span * torch.rand(shape, generator=gen, device="cuda")).to(dt)
+        b = torch.randn(shape, generator=gen, device="cuda").to(dt)
+        g = torch.randn(shape, generator=gen, device="cuda").to(dt)
+        _, tables, words = fwd_peers
+        hs, carries, prods = [], [], []
+        for r in range(world):
+            ar, br = a[:, rows[r]], b[:, rows[r]]
+            h, send, blocks = ops[r].local_forward(ar, br, continuation=r > 0)
+            carry = None
+            if r == 0:
+                native.seqpar_push(send[0], send[1], r, False, tables, words, epoch, short_waits=True)
+                prod = send[0].clone()
+            else:
+                prod = torch.full((n,), -1.0, device="cuda")
+                carry = native.seqpar_fixup_forward_from(ar, br, h, None, r, blocks[0], blocks[1], blocks[2],
+                                                         peer_tables=tables, peer_words=words, epoch=epoch,
+                                                         push=(send[1], None, prod))
+                assert torch.allclose(prod, send[0], rtol=1e-5, atol=1e-37), f"folded product of rank {r}"
+            hs.append(h); carries.append(carry); prods.append(prod)
+        h_all = torch.cat(hs, dim=1)
+        h_ref, _, _ = oracle.reference_values(a, b, None)
+        assert_parity(h_all, h_ref, tol, f"h, step {epoch}")
+        _, tables, words = bwd_peers
+        das, dbs = [None] * world, [None] * world
+        for r in reversed(range(world)):
+            ar, gr = a[:, rows[r]], g[:, rows[r]]
+            da, db, send, blocks = ops[r].local_backward(ar, hs[r], gr, continuation=r > 0, h_prev=carries[r], prod=prods[r])
+            if r == world - 1:
+                native.seqpar_push(prods[r], send[1], r, True, tables, words, epoch, short_waits=True)
+            else:
+                native.seqpar_fixup_backward_from(ar, hs[r], gr, da, db, None, r, carries[r], blocks[0], blocks[1], blocks[2],
+                                                  r > 0, peer_tables=tables, peer_words=words, epoch=epoch,
+                                                  push=(send[1], prods[r], None))
+            das[r], dbs[r] = da, db
+        da_ref, db_ref = oracle.scan_backward_f32(a.float().cpu().numpy(), h_all.float().cpu().numpy(),
+                                                  g.float().cpu().numpy())
+        assert_parity(torch.cat(dbs, dim=1), torch.from_numpy(db_ref), tol, f"dbeta, step {epoch}")
+        assert_parity(torch.cat(das, dim=1), torch.from_numpy(da_ref), tol, f"dalpha, step {epoch}")
+        pkg.check_status()
+
+
 @pytest.mark.parametrize("backward", [False, True])
 def test_carry_exchange_through_tables_played_on_one_gpu(backward):
     """fss_seqpar_push / fss_seqpar_compose_peer with the four ranks' tables in one GPU's memory: every

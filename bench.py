@@ -766,10 +766,13 @@ def main():
             torch.cuda.current_stream().wait_event(left)
 
         e_steps = max(3, min(args.steps, 20))
-        ms_e2e = stats(hs.timed(e2e_step, e_steps, 3, 3, 1, graphs=False))
+        # nine repeats: the host side of this box is shared, and a neighbour's burst of copies has been seen
+        # to slow two repeats in a row sevenfold; the median of nine rides that out, min and max are reported
+        e_repeats = 9
+        ms_e2e = stats(hs.timed(e2e_step, e_steps, 3, e_repeats, 1, graphs=False))
         sec = ms_e2e["median"] * 1e-3
         e2e = {"value": total_elems / sec, "unit": UNIT, "ms_per_step": ms_e2e["median"],
-               "ms_per_step_min": ms_e2e["min"], "ms_per_step_max": ms_e2e["max"], "steps": e_steps, "repeats": 3,
+               "ms_per_step_min": ms_e2e["min"], "ms_per_step_max": ms_e2e["max"], "steps": e_steps, "repeats": e_repeats,
                "h2d_bytes_per_step": 3 * tensor_bytes, "d2h_bytes_per_step": 3 * tensor_bytes,
                "h2d_gbs": 3 * tensor_bytes / sec / 1e9, "d2h_gbs": 3 * tensor_bytes / sec / 1e9,
                "aggregate_host_gbs_per_direction": world * 3 * tensor_bytes / sec / 1e9,

@@ -723,11 +723,13 @@ fixup_forward(Geometry g, View<const T> alpha, View<const T> beta, View<T> h, co
     float more[V], bs[V];
 #pragma unroll
     for (int i = 0; i < V; ++i) { more[i] = 1.0f; bs[i] = 0.0f; }
-    // the first block's share of the work that needs no carry
+    // The first block's share of the work that needs no carry.  The small table reads come first: the
+    // reduction pass floods the memory system, and the publishing CTAs -- whose few dependent loads
+    // everything else waits for -- get through faster while it has not started.
     if (j0 < g.NB) {
         if (has && j0 > 0) load_floats<V>(bs_col + (j0 - 1) * g.D, bs);
-        prefix_of_block(j0);
         block_range_product<V>(bp_col, g.D, 0, j0, has, sP, more);
+        prefix_of_block(j0);
     }
     {
         float carry[V];
@@ -820,8 +822,8 @@ fixup_backward(Geometry g, View<const T> alpha, View<const T> h, View<const T> g
     if (k0 < g.NB) {
         const int64_t j = g.NB - 1 - k0;
         if (has && j + 1 < g.NB) load_floats<V>(bs_col + (j + 1) * g.D, bs);
+        block_range_product<V>(bp_col, g.D, j + 1, g.NB, has, sP, more);      // light reads first, see fixup_forward
         prefix_of_block(j);
-        block_range_product<V>(bp_col, g.D, j + 1, g.NB, has, sP, more);
     }
     {
         float carry[V];

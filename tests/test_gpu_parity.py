@@ -578,18 +578,21 @@ def _local_peers(world, n):
     return bufs, tables, words
 
 
-@pytest.mark.parametrize("dtype,D", [("bf16", 256), ("f32", 256), ("bf16", 100)])
-def test_fixups_that_publish_their_own_pair_played_on_one_gpu(dtype, D):
+@pytest.mark.parametrize("dtype,D,Tl", [("bf16", 256, 1500), ("f32", 256, 1500), ("bf16", 100, 1500),
+                                        ("bf16", 20480, 300)])      # the last one: a fix-up grid larger than the GPU
+def test_fixups_that_publish_their_own_pair_played_on_one_gpu(dtype, D, Tl):
     """The peer-exchange step in which every rank's fix-up kernel publishes that rank's own pair
     (fss_carry_source.push_state) -- only the rank without a fix-up uses a push launch.  Four ranks
     played in dependency order on one GPU, two steps in a row (the second one waits for the
     acknowledgements of the first), forward and backward against the CPU checker's undivided scan.
-    Forward fix-ups fold the product from the block table and must hand back the scan's own product."""
+    Forward fix-ups fold the product from the block table and must hand back the scan's own product.
+    With D = 20480 the fix-up grid (160 CTAs) does not fit on the GPU at once: the call then sends the
+    pair with a push launch of its own before the fix-up."""
     pkg, native, _ = _mods()
     from fast_sequential_scan_b200.distributed import NativeOps
     dt = torch.bfloat16 if dtype == "bf16" else torch.float32
     tol = BF16_TOL if dtype == "bf16" else F32_TOL
-    world, B, Tl = 4, 2, 1500
+    world, B = 4, 2
     n = B * D
     gen = torch.Generator(device="cuda").manual_seed(41)
     shape = (B, world * Tl, D)

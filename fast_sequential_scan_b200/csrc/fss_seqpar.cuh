@@ -1,7 +1,8 @@
 // Sequence-parallel pieces: every rank scans its rows from a zero state, the per-rank
-// (product, state) vectors are gathered by the host (NCCL), and these kernels fold them and
-// re-scan the rows that the state arriving from the neighbouring rank still reaches.  The
-// reference never splits the sequence; this follows the chunk algebra of fss_chunked.cuh one
+// (product, state) pairs are exchanged -- by a collective of the host's choice, or through
+// peer-mapped tables that the kernels below write and poll themselves -- and the fix-up kernels
+// fold them and re-scan the rows that the state arriving from the neighbouring rank still reaches.
+// The reference never splits the sequence; this follows the chunk algebra of fss_chunked.cuh one
 // level up.
 #pragma once
 
@@ -39,8 +40,9 @@ __global__ void compose(int backward, int world, int rank, int64_t n,
 // NVSwitch).  The values travel as 8-byte cells {fp32 value, 32-bit epoch}: an aligned 64-bit store
 // arrives whole, so a cell that carries the epoch of the current exchange holds the value written
 // with it -- no flag word, no fence, no second round trip; the consumer simply polls (bounded) the
-// cells it needs.  For the 32 KB pairs of a long-context run the exchange then costs a small launch
-// on the producer's side where the library collective costs 20-50 microseconds.
+// cells it needs.  For the 32 KB pairs of a long-context run the exchange then costs a few
+// microseconds inside kernels that run anyway (the fix-up kernels publish their own rank's pair,
+// see publish_pair) where the library collective costs 20-50 microseconds.
 //
 // Rank q owns  table[q] = [world][2][n] cells  and  words[q] = world + 1 32-bit words:
 //   words[q][r]      epoch of the last exchange whose pair from rank q rank r has finished reading
@@ -59,6 +61,9 @@ constexpr int kPushThreads = 256;
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
     uint32_t v;
@@ -378,8 +383,10 @@ __device__ __forceinline__ void acknowledge_finish(const CarrySource &src, bool 
     if (count != gridDim.x * gridDim.y * gridDim.z) return;
     src.peers.words[src.rank][src.world] = 0;      // next used by the next consuming kernel on this stream
     const int lo = backward ? src.rank + 1 : 0, hi = backward ? src.world : src.rank;
+    // one system-wide fence orders this GPU's reads of the table before all the words that follow; a
+    // release per word would pay for the same fence once per writer (seven times on eight GPUs)
     __threadfence_system();
-    for (int r = lo; r < hi; ++r) st_release_sys(src.peers.words[r] + src.rank, src.epoch);
+    for (int r = lo; r < hi; ++r) st_relaxed_sys(src.peers.words[r] + src.rank, src.epoch);
 }
 
 // ------------------------------------------------------------------ fix-up
@@ -475,15 +482,17 @@ __device__ __forceinline__ bool publish_pair(const CarrySource &src, bool backwa
 #pragma unroll
     for (int i = 0; i < V; ++i) { prod[i] = 1.0f; state[i] = 0.0f; }
     if (has) load_floats<V>(src.push_state + idx, state);
+    // the readers must be done with the previous exchange before the slot is overwritten (a few
+    // threads look; in a training loop the word is there already, and the look hides behind the
+    // loads of the other warps below)
+    bool ok = true;
+    if ((int)threadIdx.x >= lo && (int)threadIdx.x < hi && src.epoch > 1)
+        ok = wait_epoch(src.peers.words[src.rank] + threadIdx.x, src.epoch - 1, src.max_spins);
     if (src.push_prod) {
         if (has) load_floats<V>(src.push_prod + idx, prod);
     } else {
         block_range_product<V, 8>(bp_col, D, 0, NB, has, scratch, prod);
     }
-    // the readers must be done with the previous exchange before the slot is overwritten
-    bool ok = true;
-    if ((int)threadIdx.x >= lo && (int)threadIdx.x < hi && src.epoch > 1)
-        ok = wait_epoch(src.peers.words[src.rank] + threadIdx.x, src.epoch - 1, src.max_spins);
     if (__syncthreads_or(!ok)) {
         if (threadIdx.x == 0) report_status(status, FSS_STATUS_EXCHANGE_TIMEOUT);
         return false;

@@ -33,6 +33,24 @@ def test_struct_layouts_match_the_header():
     assert ctypes.sizeof(_lib.ForwardState) == 40 and ctypes.sizeof(_lib.BackwardState) == 40
 
 
+def test_carry_source_and_flag_constants_match_the_header():
+    """Field order of fss_carry_source and the values of the FSS_FLAG_* / FSS_ALGO_* constants, read from the header text."""
+    from fast_sequential_scan_b200 import _lib
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    body = re.search(r"typedef struct fss_carry_source \{(.*?)\} fss_carry_source;", text, flags=re.S).group(1)
+    fields = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if decl:
+            fields += [re.sub(r"[^A-Za-z0-9_]", "", part.split()[-1]) for part in decl.split(",")]
+    assert fields == [name for name, _ in _lib.CarrySource._fields_]
+    assert ctypes.sizeof(_lib.CarrySource) == 72
+    defines = dict(re.findall(r"#define (FSS_(?:FLAG|ALGO)_[A-Z_]+) (0x[0-9a-fA-F]+|\d+)", text))
+    assert len(defines) >= 7
+    for name, value in defines.items():
+        assert getattr(_lib, name[4:]) == int(value, 0), f"{name}: header {value}, ctypes {getattr(_lib, name[4:])}"
+
+
 def test_error_strings_and_argument_checks_need_no_device():
     from fast_sequential_scan_b200 import _lib
     L = _lib.lib()

@@ -131,7 +131,8 @@ class NativeOps:
         algo = self._algo_for(alpha, beta)
         send, bp, bs, R = self._buffers("fwd", alpha, algo)
         h = torch.empty_like(alpha)
-        # with the peer exchange the product over the rows is folded by the push kernel (one launch less)
+        # with the peer exchange the product over the rows is folded from the block products by the kernel that
+        # publishes the pair (the fix-up, or the push launch of the rank without one): one launch less
         self._prod_pending = self.exchange == "peer" and D % 4 == 0
         native.forward_into(alpha, beta, h, algo=algo, continuation=continuation, h_last=send[1].view(B, D),
                             prod=None if self._prod_pending else send[0].view(B, D), block_prod=bp, block_state=bs,

@@ -11,8 +11,6 @@
 namespace fss {
 namespace seqpar {
 
-constexpr int kThreads = 128;
-
 // state' = P*state + C, with 0 absorbing an overflowed P (inf*0 would poison the chain)
 __device__ __forceinline__ float fold(float P, float state, float C) {
     return state == 0.0f ? C : fmaf(P, state, C);
@@ -78,16 +76,6 @@ __device__ __forceinline__ unsigned long long ld_cell(const unsigned long long *
     unsigned long long c;
     asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(c) : "l"(p) : "memory");
     return c;
-}
-// the value of a cell once it carries `epoch` (bounded poll); false = it never did
-__device__ __forceinline__ bool wait_cell(const unsigned long long *p, uint32_t epoch, uint32_t max_spins, float *out) {
-    uint32_t spins = 0;
-    for (;;) {
-        const unsigned long long c = ld_cell(p);
-        if ((uint32_t)(c >> 32) == epoch) { *out = __uint_as_float((uint32_t)c); return true; }
-        if (++spins >= max_spins) return false;
-        __nanosleep(32);
-    }
 }
 // true when *p has reached `want` (epochs only grow) within max_spins polls
 __device__ __forceinline__ bool wait_epoch(const uint32_t *p, uint32_t want, uint32_t max_spins) {

@@ -113,6 +113,39 @@ class OracleOps:
             run = run * bp[:, j].numpy()
 
 
+class FusedOracleOps(OracleOps):
+    """The same stand-in behind the interface of the ops that fold the exchanged table inside the fix-up
+    (``exchange_and_fixup_forward / _backward``, what ``NativeOps`` offers on a GPU): exercises that branch of
+    ``seqpar_forward`` / ``seqpar_backward`` -- argument order, the ``(carry, product)`` return, which rank
+    skips which fix-up -- on CPU ranks."""
+    calls = None
+
+    def exchange_and_fixup_forward(self, alpha, beta, h, send, prod, blocks, rank, world, group, mark):
+        from fast_sequential_scan_b200 import distributed as fd
+        self.calls = (self.calls or []) + ["fwd"]
+        pc = fd._gather(send, group, self, "fwd")
+        mark("fwd_gather")
+        kept = send[0].clone()
+        if rank == 0:
+            return None, kept
+        carry = self.compose(pc, rank, backward=False).reshape(alpha.shape[0], alpha.shape[2])
+        self.fixup_forward(alpha, beta, h, carry, blocks)
+        return carry, kept
+
+    def exchange_and_fixup_backward(self, alpha, h, grad, da, db, send, prod, h_prev, blocks, rank, world, continuation,
+                                    group, mark):
+        from fast_sequential_scan_b200 import distributed as fd
+        self.calls = (self.calls or []) + ["bwd"]
+        assert continuation == (rank > 0)
+        pc = fd._gather(send, group, self, "bwd")
+        mark("bwd_gather")
+        if rank == world - 1:
+            return None
+        u_in = self.compose(pc, rank, backward=True).reshape(alpha.shape[0], alpha.shape[2])
+        self.fixup_backward(alpha, h, grad, da, db, u_in, h_prev, blocks, continuation)
+        return u_in
+
+
 def _worker(rank, world, port, mode, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -126,15 +159,18 @@ def _worker(rank, world, port, mode, out_dir):
         g = torch.randn(B, T, D, generator=gen)
         h_ref = torch.from_numpy(oracle.scan_forward_f32(a.numpy(), b.numpy()))
         da_ref, db_ref = (torch.from_numpy(x) for x in oracle.scan_backward_f32(a.numpy(), h_ref.numpy(), g.numpy()))
-        if mode == "seqpar":
+        if mode in ("seqpar", "seqpar_fused"):
             rows = slice(rank * T // world, (rank + 1) * T // world)
             al = a[:, rows].clone().requires_grad_(True)
             bl = b[:, rows].clone().requires_grad_(True)
-            h = fd.seqpar_scan(al, bl, None, OracleOps())
+            ops = FusedOracleOps() if mode == "seqpar_fused" else OracleOps()
+            h = fd.seqpar_scan(al, bl, None, ops)
             h.backward(g[:, rows].clone())
             ok = (torch.allclose(h.detach(), h_ref[:, rows], rtol=1e-4, atol=1e-5)
                   and torch.allclose(bl.grad, db_ref[:, rows], rtol=1e-4, atol=1e-5)
                   and torch.allclose(al.grad, da_ref[:, rows], rtol=1e-4, atol=1e-5))
+            if mode == "seqpar_fused":
+                ok = ok and ops.calls == ["fwd", "bwd"]      # the fused branch ran, once per direction
         else:   # channel shards: no communication, each rank's slice equals the slice of the full result
             al, bl = fd.shard_channels(a, rank, world), fd.shard_channels(b, rank, world)
             assert al.data_ptr() == a[..., rank * (D // world):].data_ptr()      # a view, not a copy
@@ -155,7 +191,7 @@ def _free_port():
 
 
 @pytest.mark.parametrize("world", [2, 3])
-@pytest.mark.parametrize("mode", ["seqpar", "shards"])
+@pytest.mark.parametrize("mode", ["seqpar", "seqpar_fused", "shards"])
 def test_multi_rank_scan_matches_single_process(tmp_path, mode, world):
     if mode == "shards" and world == 3:
         world = 4      # 24 channels split evenly

@@ -34,7 +34,7 @@ __global__ void compose(int backward, int world, int rank, int64_t n,
 
 // ------------------------------------------------------------------ carry exchange through peer memory
 // Instead of a library all-gather, every rank can write its (product, state) pair straight into the
-// gather tables of all ranks of the box with plain stores to peer-mapped memory (NVLink /
+// gather tables of the ranks that need it with plain stores to peer-mapped memory (NVLink /
 // NVSwitch).  The values travel as 8-byte cells {fp32 value, 32-bit epoch}: an aligned 64-bit store
 // arrives whole, so a cell that carries the epoch of the current exchange holds the value written
 // with it -- no flag word, no fence, no second round trip; the consumer simply polls (bounded) the
@@ -87,7 +87,7 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t *p, uint32_t want, uin
     return true;
 }
 
-// prod, state: this rank's two [n] vectors (local).  Writes them as cells into slot `rank` of every table.
+// prod, state: this rank's two [n] vectors (local).  Writes them as cells into slot `rank` of its readers' tables.
 __global__ void __launch_bounds__(kPushThreads)
 peer_push(PeerTables peers, int backward, int world, int rank, int64_t n, const float *__restrict__ prod,
           const float *__restrict__ state, uint32_t epoch, int32_t *status, uint32_t max_spins) {

@@ -236,8 +236,9 @@ int fss_seqpar_compose(const fss_scan_ctx *ctx, int backward, int world, int ran
  * the first push of any rank).  peer_tables / peer_words are HOST arrays of `world` device pointers:
  * entry q is rank q's table / words as mapped in the calling process (entry `rank` is the caller's
  * own, local memory).
- * fss_seqpar_push writes this rank's pair (prod[n], state[n]) as cells into slot `rank` of every
- * table; exchange numbers (`epoch`) start at 1 and grow by one per exchange over the same tables.  A
+ * fss_seqpar_push writes this rank's pair (prod[n], state[n]) as cells into slot `rank` of the
+ * tables of the ranks that read it (forward: the later ranks; backward: the earlier ranks -- the
+ * others never look at the slot); exchange numbers (`epoch`) start at 1 and grow by one per exchange over the same tables.  A
  * cell that carries the current epoch is complete by itself, so there is no flag and no fence.
  * Before overwriting its slot the push waits until the readers of that slot (forward: later ranks;
  * backward: earlier ranks) have acknowledged exchange epoch-1.
